@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight matmul path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the decode GEMV over the Q8_0 + Q4_1 sweep at the
+TinyLlama-1.1B projection shapes (2048x2048, 256x2048, 5632x2048, 2048x5632,
+32000x2048; ten GEMVs, 160 MB of blocks). The metric is algorithmic bytes per
+second: sum over the sweep of (block payload + 4*in + 4*out) divided by device time.
+
+  value      device-resident: weights, x and y live in HBM; the ten launches of a step
+             are captured in one CUDA graph and the graph is replayed K times between
+             two CUDA events on the launching stream. The weights rotate over three
+             copies per matrix (480 MB), so a buffer is reused only after more than
+             twice the 126 MB L2 has been streamed.
+  e2e        the same sweep through the host-pointer C ABI (tm_cuda_gemv_q): x comes
+             from pinned host memory and y goes back to the host inside the timed
+             region, one blocking call per GEMV. Weights are cached on the device on
+             first use, which is the contract of the entry point being replaced.
+  roofline   the GEMV kernel against the measured HBM copy bandwidth.
+  cpu_baseline  the CPU restatement of the reference's dot path on the host cores.
+
+With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the large
+matrices are sharded by output rows, every rank computes its rows and the outputs
+are all-gathered with NCCL; the two small shapes stay replicated. Total work is
+fixed, so scaling is "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from tensormark_b200 import synth  # noqa: E402
+
+SWEEP = [(dt, shape) for dt in (synth.Q8_0, synth.Q4_1) for shape in synth.TINYLLAMA_SHAPES]
+SEEDS = {synth.Q8_0: 1, synth.Q4_1: 2}
+COPIES = 3
+SHARD_MIN_ROWS = 4096          # matrices with fewer rows stay on one GPU (replicated)
+WORKLOAD = "Q8_0+Q4_1 decode GEMV sweep, TinyLlama-1.1B projection shapes (BASELINE config 2)"
+
+
+def sweep_bytes() -> int:
+    return sum(synth.gemv_bytes(dt, n, k) for dt, (n, k) in SWEEP)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def recorded_traffic():
+    """DRAM bytes per launch of the dominant kernel, taken from the committed ncu summary (or None)."""
+    path = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+    if os.path.exists(path):
+        try:
+            return json.load(open(path))
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank: int):
+    """The reference's CPU dot path (restated; its own header does not build on Linux) on all host threads.
+    One step = one pass over the same sweep."""
+    if rank != 0:
+        return
+    from oracle import binding
+    orc = binding.oracle_fast()
+    threads = os.cpu_count() or 1
+    mats = [(dt, n, k, synth.make_weights(dt, n, k, SEEDS[dt]), synth.make_activations(k, SEEDS[dt])) for dt, (n, k) in SWEEP]
+
+    def step():
+        for dt, n, k, W, x in mats:
+            orc.gemv(dt, W, x, n, k, threads=threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt_s = time.perf_counter() - t0
+    val = sweep_bytes() * args.steps / dt_s / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_gemv_algorithmic_bandwidth", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt_s / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "where": "host CPU"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "the full sweep (10 GEMVs, 160 MB of blocks) per step, 64-row chunks over all host threads"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    from tensormark_b200 import lib
+
+    torch.cuda.set_device(local_rank)
+    L = lib.load()
+    lib.check(L.tm_cuda_init(local_rank), "tm_cuda_init")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def vp(t):
+        return C.c_void_p(t.data_ptr())
+
+    # ---- resident inputs: this rank's row shard of every matrix, COPIES times
+    mats = []
+    for dt, (n, k) in SWEEP:
+        sharded = world > 1 and n >= SHARD_MIN_ROWS and n % world == 0
+        W = synth.make_weights(dt, n, k, SEEDS[dt])
+        lo, hi = (rank * (n // world), (rank + 1) * (n // world)) if sharded else (0, n)
+        Wl = np.ascontiguousarray(W[lo:hi]).reshape(-1)
+        copies = []
+        for _ in range(COPIES):
+            t = torch.zeros(Wl.size + 32, dtype=torch.uint8, device="cuda")
+            t[: Wl.size] = torch.from_numpy(Wl).cuda()
+            copies.append(t)
+        x = torch.from_numpy(synth.make_activations(k, SEEDS[dt])).cuda()
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        ypart = torch.zeros(hi - lo, dtype=torch.float32, device="cuda") if sharded else None
+        mats.append(dict(dt=dt, n=n, k=k, rows=hi - lo, sharded=sharded, W=copies, x=x, y=y, ypart=ypart, host=(W, lo, hi)))
+
+    stream = torch.cuda.Stream()
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def launch_step(copy: int):
+        for m in mats:
+            out = m["ypart"] if m["sharded"] else m["y"]
+            ok = L.tm_cuda_gemv_q_dev(vp(m["x"]), vp(m["W"][copy]), vp(out), m["rows"], m["k"], m["dt"], sp)
+            lib.check(ok, "tm_cuda_gemv_q_dev")
+            if m["sharded"]:
+                dist.all_gather_into_tensor(m["y"], m["ypart"])
+
+    # ---- one graph per weight copy, so replays walk the copies round-robin
+    graphs = []
+    with torch.cuda.stream(stream):
+        launch_step(0)
+        stream.synchronize()
+        before = L.tm_cuda_launch_count()
+        launch_step(0)
+        launches_per_step = int(L.tm_cuda_launch_count() - before)
+        stream.synchronize()
+        use_graph = os.environ.get("TM_BENCH_GRAPH", "1") != "0"
+        if use_graph:
+            try:
+                for c in range(COPIES):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        launch_step(c)
+                    graphs.append(g)
+            except Exception as e:      # capture refused (e.g. a collective that cannot be captured): plain launches
+                if rank == 0:
+                    print(f"[bench] graph capture unavailable, using stream launches: {e}", file=sys.stderr)
+                graphs = []
+                torch.cuda.synchronize()
+
+    def step(i: int):
+        if graphs:
+            graphs[i % COPIES].replay()
+        else:
+            launch_step(i % COPIES)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            step(i)
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clk:
+            ev0.record(stream)
+            for i in range(args.steps):
+                step(args.warmup + i)
+            ev1.record(stream)
+            barrier()
+        ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    total = sweep_bytes()
+    value = total * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- correctness guard on what was just timed (cheap: sampled rows against numpy fp64)
+    if rank == 0:
+        m = mats[0]
+        W, lo, hi = m["host"]
+        assert torch.isfinite(m["y"]).all(), "non-finite GEMV output in the timed region"
+
+    status_ok = bool(L.tm_cuda_tok_flush())          # harvests the device status word
+    if not status_ok:
+        raise RuntimeError("device status: " + lib.last_error())
+
+    line = None
+    if rank == 0:
+        # ---- per-shape device numbers (each GEMV alone, rotating its copies; N=1 only)
+        per_shape = []
+        if world == 1:
+            with torch.cuda.stream(stream):
+                for m in mats:
+                    reps = max(20, int(2e9 // max(1, synth.gemv_bytes(m["dt"], m["n"], m["k"]))) // 4)
+                    reps = min(reps, 400)
+                    for c in range(COPIES):
+                        L.tm_cuda_gemv_q_dev(vp(m["x"]), vp(m["W"][c]), vp(m["y"]), m["n"], m["k"], m["dt"], sp)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    for r in range(reps):
+                        L.tm_cuda_gemv_q_dev(vp(m["x"]), vp(m["W"][r % COPIES]), vp(m["y"]), m["n"], m["k"], m["dt"], sp)
+                    e1.record(stream)
+                    stream.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / reps
+                    per_shape.append({"dtype": synth.DTYPE_NAMES[m["dt"]], "shape": [m["n"], m["k"]], "us": round(us, 3),
+                                      "GBps": round(synth.gemv_bytes(m["dt"], m["n"], m["k"]) / us / 1e3, 1),
+                                      "note": "stream launches; matrices below 126 MB are re-read from L2 when they fit in 3 copies"})
+
+        # ---- e2e: host-pointer C ABI, pinned x, y back to the host
+        hx = {k: torch.from_numpy(synth.make_activations(k, 1)).pin_memory() for k in {m["k"] for m in mats}}
+        hy = {m["n"]: torch.empty(m["n"], dtype=torch.float32).pin_memory() for m in mats}
+        hW = [np.ascontiguousarray(m["host"][0]) for m in mats]
+
+        def e2e_step():
+            for m, W in zip(mats, hW):
+                ok = L.tm_cuda_gemv_q(C.c_void_p(hx[m["k"]].data_ptr()), C.c_void_p(W.ctypes.data),
+                                      C.c_void_p(hy[m["n"]].data_ptr()), m["n"], m["k"], m["dt"])
+                lib.check(ok, "tm_cuda_gemv_q")
+
+        e2e = None
+        if world == 1:
+            for _ in range(max(3, args.warmup)):
+                e2e_step()
+            lb = L.tm_cuda_launch_count()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                e2e_step()
+            es = time.perf_counter() - t0
+            e2e_launches = int(L.tm_cuda_launch_count() - lb)
+            e2e = {"value": total * args.steps / es / 1e9, "unit": "GB/s",
+                   "h2d_bytes_per_step": sum(4 * m["k"] for m in mats), "d2h_bytes_per_step": sum(4 * m["n"] for m in mats),
+                   "ms_per_step": es / args.steps * 1e3, "gpu_launches": e2e_launches,
+                   "note": "blocking tm_cuda_gemv_q per GEMV; weights cached on the device by (pointer, bytes) as the replaced entry does"}
+            L.tm_cuda_release_weights()
+        else:
+            e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "note": "the host-pointer entry is single-GPU; measured at N=1 only"}
+
+        # ---- CPU baseline (bounded sample, N=1 only)
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            from oracle import binding
+            orc = binding.oracle_fast()
+            threads = os.cpu_count() or 1
+            t0 = time.perf_counter()
+            reps = 0
+            while reps < 1 or (time.perf_counter() - t0 < 10.0 and reps < 8):
+                for m, W in zip(mats, hW):
+                    orc.gemv(m["dt"], W, hx[m["k"]].numpy(), m["n"], m["k"], threads=threads)
+                reps += 1
+            cs = time.perf_counter() - t0
+            cpu = {"value": total * reps / cs / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                   "sample": f"{reps} pass(es) over the full sweep (10 GEMVs, 160 MB of blocks), scalar dot path restated from the "
+                             "reference, 64-row chunks over all host threads, gcc -O3 -march=native, no BLAS"}
+
+        peak, peak_kind = measured_peak()
+        traffic = recorded_traffic()
+        clocks = clk.summary()
+        line = {
+            "metric": "decode_gemv_algorithmic_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "gemvs_per_step": len(SWEEP), "bytes_per_step": total,
+                       "l2": f"weights rotate over {COPIES} copies per matrix ({COPIES * 160} MB), more than 2x the 126 MB L2 between reuses",
+                       "launch": "one CUDA graph per step" if graphs else "stream launches",
+                       "sharding": "rows over ranks + NCCL all-gather for matrices with >= 4096 rows" if world > 1 else "single GPU"},
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                         "peak_kind": peak_kind + " STREAM-style copy",
+                         "traffic": (traffic or {}).get("dram_bytes_per_launch"),
+                         "traffic_note": (traffic or {}).get("note"),
+                         "kernel": "gemv_stream", "per_gpu": world > 1},
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "per_shape": per_shape,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus != 1 and world == 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

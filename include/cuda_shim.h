@@ -1,0 +1,169 @@
+/* include/cuda_shim.h — C ABI of the B200 backend for TensorMark's quantized-weight
+ * matmul path.
+ *
+ * This is the drop-in boundary: the library (libtm_cuda.so) exports, for every
+ * entry point of the reference's Metal shim that lies on the quantized matmul /
+ * decode-chain path, a `tm_cuda_*` function with the same parameter list and the
+ * same meaning, plus a `tm_metal_*` alias so a caller written against the
+ * reference's weak-import declarations (tensormark/llama.h:35-152) links without
+ * change. Citations name the reference interface each entry replaces.
+ *
+ * Conventions kept from the reference:
+ *   - `bool` entries return false on any failure and bump tm_cuda_fallback_count()
+ *     (tensormark/metal.h:46-59, "a counter, not a print"). There is no CPU path
+ *     behind a false: the caller decides what to do.
+ *   - `void` token-lane encoders cannot report; where the reference throws a C++
+ *     exception across the C boundary (e.g. metal.h:3526, 4160) this library
+ *     latches a sticky error that makes the next tok_end / tok_flush /
+ *     tok_wait_pending return false. tm_cuda_last_error() names it.
+ *   - dtype codes are the container's (tensormark/tmq.h:48-60):
+ *     0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K, 6 Q6_K.
+ *   - Host-pointer entries are blocking and, like the reference's function-local
+ *     caches, not thread-safe: one caller thread per process.
+ *
+ * Entries ending in `_dev` take DEVICE pointers and a stream (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream) and never synchronize. They
+ * are what the token lane launches internally, exported so a resident caller (or
+ * a benchmark) can time the kernels without host copies.
+ */
+#ifndef TM_CUDA_SHIM_H
+#define TM_CUDA_SHIM_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TM_DT_Q8_0 0u
+#define TM_DT_Q4_0 1u
+#define TM_DT_F16  3u
+#define TM_DT_Q4_1 4u
+#define TM_DT_Q5_K 5u
+#define TM_DT_Q6_K 6u
+
+/* ---- library state ------------------------------------------------------- */
+/* Select the device for this process and create the lane stream. Called lazily
+ * by every other entry (the reference's ensure_init, metal.h:73-91). */
+bool tm_cuda_init(int device);
+/* Message of the most recent failure, "" when none. */
+const char* tm_cuda_last_error(void);
+/* Number of entries that returned false so far (metal.h:46-59 fallback_count). */
+unsigned long long tm_cuda_fallback_count(void);
+/* Number of kernels of this library launched so far in this process. */
+unsigned long long tm_cuda_launch_count(void);
+/* Number of multiprocessors of the selected device. */
+int tm_cuda_sm_count(void);
+
+/* ---- per-tensor projection, host pointers -------------------------------- */
+/* y[N] = W[N x K] . x[K], W Q4_0 blocks. Weights are cached on the device keyed
+ * by (pointer, bytes); x and y are copied per call. K % 32 != 0 -> false.
+ * Replaces tm_metal_q4_gemv (metal_shim.mm:17-20, metal.h:2058-2127); bound to
+ * tmllama::Q4Gemv (q4_projection_backend.h:7-8). */
+bool tm_cuda_q4_gemv(const float* x, const void* Wq, float* y, unsigned N, unsigned K);
+/* C[M x N] = A[M x K] . W^T, W Q4_0. Replaces tm_metal_sgemm_q4
+ * (metal_shim.mm:6-9, metal.h:1981-2052); bound to tmllama::Q4Gemm. */
+bool tm_cuda_sgemm_q4(const float* A, const void* Wq, float* C, unsigned M, unsigned N, unsigned K);
+/* Fused multi-tensor prefill: C is M x sum(Ns) row-major, part p occupying the
+ * columns after parts 0..p-1. Replaces tm_metal_q4_prefill (metal_shim.mm:11-15,
+ * metal.h:2133-2235). */
+bool tm_cuda_q4_prefill(const float* A, const void* const* Wqs, const unsigned* Ns, unsigned nparts,
+                        float* C, unsigned M, unsigned K);
+/* dtype-carrying forms of the three above (the reference's per-call entries are
+ * Q4_0-only; its token lane carries the dtype, metal_shim.mm:84-89). */
+bool tm_cuda_gemv_q(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype);
+bool tm_cuda_sgemm_q(const float* A, const void* W, float* C, unsigned M, unsigned N, unsigned K, unsigned dtype);
+/* out[N x K] fp32 = dequantized W; bit-exact against tmq::dequantize_row_*
+ * (quant.h:194-200, 267-277, 304-330, 338-365, 397-408). The fp32 form of
+ * q4_dequant_f32 (metal.h:1516-1562), for every block dtype. */
+bool tm_cuda_dequant(const void* W, float* out, unsigned N, unsigned K, unsigned dtype);
+/* Drop every cached weight copy made by the host-pointer entries. */
+void tm_cuda_release_weights(void);
+
+/* ---- device-pointer kernels ---------------------------------------------- */
+/* Bytes of an N x K tensor of `dtype`; 0 when K is not whole blocks (tmq.h:124-133). */
+size_t tm_cuda_weight_bytes(unsigned dtype, size_t N, size_t K);
+/* y = W x. W must be 16-byte aligned. (metal.h:3457-3480 tok_gemv, 3647-3669 tok_gemv_kq) */
+bool tm_cuda_gemv_q_dev(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype, void* stream);
+/* Segmented GEMV: N total rows over nseg segments; segment s covers seg_rows[s]
+ * rows whose blocks start seg_woff[s] bytes after W. One launch; every row is
+ * computed exactly as the unsegmented kernel computes it. nseg <= 16.
+ * (metal.h:3519-3556 tok_gemv_seg, 3585-3616 tok_gemv_seg_dt) */
+bool tm_cuda_gemv_seg_dev(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype,
+                          const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, void* stream);
+bool tm_cuda_dequant_dev(const void* W, float* out, unsigned N, unsigned K, unsigned dtype, void* stream);
+/* C[M x N] = A[M x K] . W^T on the tensor cores. `workspace` is device scratch of
+ * at least tm_cuda_sgemm_q_workspace(M, N, K, dtype) bytes, 256-byte aligned. */
+size_t tm_cuda_sgemm_q_workspace(unsigned M, unsigned N, unsigned K, unsigned dtype);
+bool tm_cuda_sgemm_q_dev(const float* A, const void* W, float* C, unsigned M, unsigned N, unsigned K,
+                         unsigned dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Decode glue on device pointers (the kernels behind the token lane). */
+bool tm_cuda_rmsnorm_dev(const float* x, const float* w, float* out, unsigned D, float eps, void* stream);
+bool tm_cuda_add_dev(float* a, const float* b, unsigned n, void* stream);
+bool tm_cuda_silu_mul_dev(float* g, const float* u, unsigned n, void* stream);
+bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream);
+
+/* ---- token lane (metal_shim.mm:22-152) ----------------------------------- */
+/* Slots are backend-owned grow-only device buffers addressed by small integers
+ * (metal.h:2262-2281). A slot may not grow between tok_begin and the matching
+ * end (metal.h:3135-3140): reserve packed outputs first. */
+bool tm_cuda_tok_begin(void);                                   /* metal.h:3074-3089 */
+bool tm_cuda_tok_flush(void);                                   /* metal.h:3109-3121 */
+bool tm_cuda_tok_end(int outslot, float* dst, unsigned n);      /* metal.h:3122-3127 */
+bool tm_cuda_tok_end_async(void);                               /* metal.h:3152-3158 */
+bool tm_cuda_tok_wait_pending(void);                            /* metal.h:3161-3190 */
+bool tm_cuda_tok_reserve(int slot, size_t bytes);               /* metal.h:3135-3140 */
+bool tm_cuda_tok_upload(int slot, size_t byte_off, const void* src, size_t bytes);   /* metal.h:3128-3134 */
+bool tm_cuda_tok_download(int slot, size_t byte_off, void* dst, size_t bytes);       /* metal.h:3141-3147 */
+/* K/V cache slots; offsets and counts are in ELEMENTS, the element type is half
+ * unless TM_CUDA_KV_HALF=0 (metal.h:3968-4014). */
+bool tm_cuda_tok_kv_reserve(int slot, size_t n);
+bool tm_cuda_tok_kv_upload(int slot, size_t elem_off, const float* src, size_t n);
+bool tm_cuda_tok_kv_download(int slot, size_t elem_off, float* dst, size_t n);
+/* Register a weight tensor; returns a handle >= 1000 (or -1) and the byte offset
+ * of the tensor inside the handle's buffer. With zero_copy != 0 the whole mapping
+ * [map_base, map_base+map_size) is made resident once and every tensor inside it
+ * shares one handle, as the reference's NoCopy buffer does (metal.h:3282-3337);
+ * "zero copy" on a discrete GPU is one aligned host-to-device copy of the mapping.
+ * The reference declares woff_out as a C++ reference; a pointer is the same ABI. */
+int tm_cuda_tok_wbuf(const void* tensor_ptr, size_t bytes, const void* map_base, size_t map_size,
+                     int zero_copy, uint64_t* woff_out);
+bool tm_cuda_tok_probe_copy(int srcslot, size_t src_off, int dstslot, unsigned n);   /* metal.h:3338-3351 */
+void tm_cuda_tok_gemv(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K);
+bool tm_cuda_tok_gemv_seg_supported(unsigned dtype);             /* metal.h:3513-3518 */
+void tm_cuda_tok_gemv_seg(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K,
+                          const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg);
+void tm_cuda_tok_gemv_seg_dt(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                             const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg);
+/* dtype in {0, 1, 4, 5, 6}: the reference has no Q8_0 GPU GEMV (llama.h:1264-1268);
+ * this backend serves it through the same entry. */
+void tm_cuda_tok_gemv_kq(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K,
+                         unsigned dtype);
+void tm_cuda_tok_embed_q4(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D);  /* metal.h:3227-3240 */
+void tm_cuda_tok_embed_kq(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype);
+void tm_cuda_tok_bias_qkv(int yslot, int biasslot, size_t bias_off, unsigned N);     /* metal.h:3672-3688 */
+void tm_cuda_tok_rmsnorm(int xslot, const void* w, int outslot, unsigned D, float eps);  /* metal.h:3722-3746 */
+void tm_cuda_tok_add(int a, int b, unsigned n);                                      /* metal.h:3747-3754 */
+void tm_cuda_tok_silu_mul(int g, size_t goff, int u, size_t uoff, unsigned n);       /* metal.h:3755-3765 */
+void tm_cuda_tok_rope_q(int qslot, unsigned H, unsigned dh, int pos, float theta);   /* metal.h:3950-3967 */
+void tm_cuda_tok_rope_k_cache(int ksrcslot, size_t ksrc_off, int cacheslot, unsigned KVH, unsigned dh,
+                              unsigned ctx, int pos, float theta);                   /* metal.h:4015-4034 */
+void tm_cuda_tok_v_cache(int vsrcslot, size_t vsrc_off, int cacheslot, unsigned KVH, unsigned dh,
+                         unsigned ctx, int pos);                                     /* metal.h:4035-4049 */
+void tm_cuda_tok_attn(int qslot, int kcslot, int vcslot, int probslot, int outslot, unsigned QD, unsigned H,
+                      unsigned KVH, unsigned dh, unsigned ctx, int allow, float scale, unsigned REP);  /* metal.h:4153-4275 */
+void tm_cuda_tok_argmax(int xslot, int tokslot, unsigned idx, unsigned n);           /* metal.h:3191-3200 */
+void tm_cuda_tok_sample(int xslot, int tokslot, unsigned idx, unsigned n, float inv_temp, unsigned seed);  /* metal.h:3201-3212 */
+unsigned tm_cuda_tok_peek(int tokslot, unsigned idx);                                /* metal.h:3216-3226 */
+/* Device address of a slot (NULL when unreserved); for resident callers and tests. */
+void* tm_cuda_tok_slot_ptr(int slot);
+/* The lane's stream as a cudaStream_t. */
+void* tm_cuda_tok_stream(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TM_CUDA_SHIM_H */

@@ -1,0 +1,16 @@
+// gemm.h — launcher of the tensor-core prefill GEMM (gemm.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace tmc {
+
+// Device scratch the GEMM needs for an M-token batch against an N x K tensor.
+size_t gemm_workspace_bytes(unsigned M, unsigned N, unsigned K);
+// C[m * ldc + n] = sum_k A[m][k] * W[n][k]  for m < M, n < N; ldc >= N.
+bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K,
+                 unsigned dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
+
+}  // namespace tmc

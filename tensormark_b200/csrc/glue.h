@@ -1,0 +1,38 @@
+// glue.h — launchers of the decode-chain glue kernels (glue.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace tmc {
+
+bool launch_rmsnorm(const float* x, const float* w, float* out, unsigned D, float eps, cudaStream_t st);
+bool launch_add(float* a, const float* b, unsigned n, cudaStream_t st);
+bool launch_silu_mul(float* g, const float* u, unsigned n, cudaStream_t st);
+bool launch_bias(float* y, const float* bias, unsigned n, cudaStream_t st);
+bool launch_copy_bytes(const uint8_t* src, uint8_t* dst, unsigned n, cudaStream_t st);
+// tbl: (cos, sin) float pairs, entry [pos * dh/2 + j]; tbl_entries = number of pairs
+bool launch_rope(float* q, unsigned heads, unsigned dh, int pos, const float* tbl, unsigned tbl_entries, cudaStream_t st);
+bool launch_rope_k_cache(const float* ksrc, void* cache, bool half_cache, unsigned KVH, unsigned dh, unsigned ctx, int pos,
+                         const float* tbl, unsigned tbl_entries, cudaStream_t st);
+bool launch_v_cache(const float* v, void* cache, bool half_cache, unsigned KVH, unsigned dh, unsigned ctx, int pos, cudaStream_t st);
+bool launch_f32_to_half(const float* src, void* dst, size_t n, cudaStream_t st);
+bool launch_half_to_f32(const void* src, float* dst, size_t n, cudaStream_t st);
+bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st);
+// scratch: two zero-initialised 64-bit words owned by the caller, re-armed by the kernel
+bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
+                   unsigned long long* scratch, cudaStream_t st);
+
+struct AttnPlan {
+    unsigned nsplit;        // 0: the scratch cannot hold even one split
+    unsigned chunk;         // positions per split
+    size_t part_floats;     // floats of partial outputs; the (max, sum) stats follow them
+};
+// scratch_bytes: size of the buffer that will receive partials and stats.
+AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t scratch_bytes);
+bool launch_attention(const float* q, const void* kc, const void* vc, bool half_cache, float* scratch, float* out,
+                      unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, float scale, unsigned REP,
+                      const AttnPlan& pl, cudaStream_t st);
+
+}  // namespace tmc

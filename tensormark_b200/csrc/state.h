@@ -1,0 +1,70 @@
+// state.h — process-wide state of the CUDA backend (one device, one lane).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdlib>
+#include <map>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "common.cuh"
+
+namespace tmc {
+
+struct Scratch {                 // grow-only device buffer
+    void* ptr = nullptr;
+    size_t cap = 0;
+    void* get(size_t bytes);     // nullptr when the allocation fails
+    void release();
+};
+
+struct Slot {                    // token-lane slot: backend-owned device buffer (tensormark/metal.h:2262-2281)
+    uint8_t* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct WeightBuf {               // registered weights: handle id = 1000 + index (metal.h:3282-3337)
+    uint8_t* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct State {
+    bool ready = false, verbose = false, kv_half = true;
+    int device = -1, sm_count = 0;
+    cudaStream_t stream = nullptr;
+    int* status_dev = nullptr;
+    std::string last_error;
+    unsigned long long fallbacks = 0, launches = 0;
+
+    // per-tensor host-pointer entries
+    std::map<std::pair<const void*, size_t>, uint8_t*> wcache;
+    Scratch io_x, io_y, io_big, io_a, gemm_ws;
+
+    // token lane
+    std::vector<Slot> slots;
+    std::vector<WeightBuf> wbufs;
+    std::map<const void*, std::pair<int, uint64_t>> wreg;      // tensor pointer -> (handle, byte offset)
+    const void* shared_base = nullptr;                          // host base of the mapping held by shared_id
+    int shared_id = -1;
+    std::map<const void*, float*> norm_w;                       // rmsnorm weights cached by host pointer
+    bool encoding = false;                                      // between tok_begin and the matching end
+    bool sticky = false;                                        // a void encoder failed since the last end
+    std::vector<cudaEvent_t> pending;                           // tok_end_async markers
+    float* rope_tbl = nullptr;                                  // (cos, sin) pairs [cap][dh/2]
+    unsigned rope_dh = 0, rope_cap = 0;
+    float rope_theta = 0.f;
+    unsigned* peek_host = nullptr;                              // pinned mirror for tok_peek
+};
+
+State& state();
+bool ensure_init(int device);
+bool harvest_status(const char* where);
+bool sync_stream(cudaStream_t st, const char* where);
+const uint8_t* cached_weights(const void* host, size_t bytes);
+SegTable one_segment(unsigned N);
+bool make_segments(SegTable& t, unsigned N, const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg);
+
+}  // namespace tmc

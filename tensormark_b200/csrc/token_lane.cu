@@ -1,0 +1,514 @@
+// token_lane.cu — the per-token decode lane of the C ABI.
+//
+// CUDA counterpart of the reference's "gpu2" token pipeline (tensormark/metal.h:
+// 2236-2300 slots, 3074-3190 begin/flush/end/async, 3282-3337 weight handles,
+// 3457-3765 GEMV and elementwise encoders, 3913-4275 rope table, K/V cache and
+// attention), behind the same entry points (tensormark/metal_shim.mm:22-152).
+//
+// Where Metal encodes dispatches into a command buffer and commits it, this lane
+// launches kernels on one CUDA stream: encode order is execution order, tok_end is
+// a stream synchronisation, tok_end_async records an event. Slots are device
+// buffers; weights are copied into device memory once per tensor (or once per
+// mapping for the zero-copy form) and addressed as (handle, byte offset).
+//
+// The void encoders cannot return an error. A bad argument latches a sticky
+// failure instead of throwing across the C boundary: nothing is launched for that
+// call and the next tok_end / tok_flush / tok_wait_pending returns false.
+#include "cuda_shim.h"
+#include "common.cuh"
+#include "glue.h"
+#include "state.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+namespace tmc {
+
+namespace {
+
+constexpr int kMaxSlots = 4096;          // plain slots are ids below the first weight handle
+constexpr int kFirstWeight = 1000;
+
+void latch(const char* fmt, ...) {
+    char buf[400];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    fail("%s", buf);
+    state().sticky = true;
+}
+
+// Device pointer of a slot that must already hold `bytes`; nullptr (and a latched
+// error) otherwise. A slot may be created, but not grown, while a token is encoded.
+uint8_t* slot_ptr(int sid, size_t bytes, const char* who) {
+    State& s = state();
+    if (sid < 0 || sid >= kFirstWeight) { latch("%s: slot id %d out of range", who, sid); return nullptr; }
+    if ((int)s.slots.size() <= sid) s.slots.resize((size_t)sid + 1);
+    Slot& sl = s.slots[sid];
+    if (sl.ptr && sl.bytes >= bytes) return sl.ptr;
+    if (sl.ptr && s.encoding) { latch("%s: slot %d must be reserved before token encoding (%zu > %zu bytes)", who, sid, bytes, sl.bytes); return nullptr; }
+    if (bytes == 0) { latch("%s: slot %d is empty", who, sid); return nullptr; }
+    uint8_t* p = nullptr;
+    const size_t want = (bytes + 255) / 256 * 256;
+    if (cudaMalloc(&p, want) != cudaSuccess) { cudaGetLastError(); latch("%s: slot %d allocation of %zu bytes failed", who, sid, want); return nullptr; }
+    cudaMemsetAsync(p, 0, want, s.stream);
+    if (sl.ptr) {
+        cudaMemcpyAsync(p, sl.ptr, sl.bytes, cudaMemcpyDeviceToDevice, s.stream);
+        cudaStreamSynchronize(s.stream);
+        cudaFree(sl.ptr);
+    }
+    sl.ptr = p; sl.bytes = want;
+    return p;
+}
+
+const uint8_t* weight_ptr(int wid, uint64_t woff, size_t bytes, const char* who) {
+    State& s = state();
+    const int i = wid - kFirstWeight;
+    if (i < 0 || i >= (int)s.wbufs.size() || !s.wbufs[i].ptr) { latch("%s: unknown weight handle %d", who, wid); return nullptr; }
+    if (woff > s.wbufs[i].bytes || bytes > s.wbufs[i].bytes - woff) { latch("%s: weight range [%llu, +%zu) outside handle %d (%zu bytes)", who, (unsigned long long)woff, bytes, wid, s.wbufs[i].bytes); return nullptr; }
+    return s.wbufs[i].ptr + woff;
+}
+
+// (cos, sin) table, built on the host with the reference's expression
+// (metal.h:3926-3941: inv = pow(theta, -2j/dh) in fp32, angle = (float)p * inv).
+// Grows geometrically; a rebuild waits for the lane so no kernel reads a freed table.
+bool ensure_rope(unsigned dh, unsigned need, float theta) {
+    State& s = state();
+    if (!dh || (dh & 1u)) { latch("rope: odd head dim %u", dh); return false; }
+    if (!need) need = 1;
+    const bool same = s.rope_tbl && s.rope_dh == dh && s.rope_theta == theta;
+    if (same && s.rope_cap >= need) return true;
+    unsigned cap = same ? s.rope_cap : 0;
+    while (cap < need) cap = cap ? cap * 2 : 64;
+    const unsigned half = dh / 2;
+    std::vector<float> tbl((size_t)cap * half * 2);
+    for (unsigned j = 0; j < half; ++j) {
+        const float inv = std::pow(theta, -2.0f * (float)j / (float)dh);
+        for (unsigned p = 0; p < cap; ++p) {
+            const float ang = (float)p * inv;
+            tbl[2 * ((size_t)p * half + j)] = std::cos(ang);
+            tbl[2 * ((size_t)p * half + j) + 1] = std::sin(ang);
+        }
+    }
+    float* d = nullptr;
+    if (cudaMalloc(&d, tbl.size() * 4) != cudaSuccess) { cudaGetLastError(); latch("rope: table allocation failed"); return false; }
+    cudaStreamSynchronize(s.stream);
+    cudaMemcpy(d, tbl.data(), tbl.size() * 4, cudaMemcpyHostToDevice);
+    if (s.rope_tbl) cudaFree(s.rope_tbl);
+    s.rope_tbl = d; s.rope_dh = dh; s.rope_cap = cap; s.rope_theta = theta;
+    return true;
+}
+
+size_t kv_elem() { return state().kv_half ? 2 : 4; }
+
+bool finish(const char* where) {
+    State& s = state();
+    const bool ok = sync_stream(s.stream, where);
+    const bool sticky = s.sticky;
+    s.sticky = false;
+    s.encoding = false;
+    if (sticky) { ++s.fallbacks; return false; }
+    return ok;
+}
+
+unsigned long long* choose_scratch() {
+    static unsigned long long* p = nullptr;
+    if (!p) {
+        if (cudaMalloc(&p, 16) != cudaSuccess) { cudaGetLastError(); p = nullptr; return nullptr; }
+        cudaMemset(p, 0, 16);
+    }
+    return p;
+}
+
+void gemv_common(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                 const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, const char* who) {
+    State& s = state();
+    if (!ensure_init(-1)) { s.sticky = true; return; }
+    const size_t row_bytes = weight_bytes(dtype, 1, K);
+    if (!row_bytes) { latch("%s: K=%u is not whole blocks of dtype %u", who, K, dtype); return; }
+    if (yoff % 4) { latch("%s: output byte offset %zu is not a multiple of 4", who, yoff); return; }
+    SegTable t;
+    if (!make_segments(t, N, seg_woff, seg_rows, nseg)) { s.sticky = true; return; }
+    // all segments live in the handle's buffer: express them relative to its base
+    const int i = wid - kFirstWeight;
+    if (i < 0 || i >= (int)s.wbufs.size() || !s.wbufs[i].ptr) { latch("%s: unknown weight handle %d", who, wid); return; }
+    for (unsigned k = 0; k < nseg; ++k)
+        if (t.woff[k] > s.wbufs[i].bytes || (size_t)seg_rows[k] * row_bytes > s.wbufs[i].bytes - t.woff[k]) {
+            latch("%s: segment %u lies outside weight handle %d", who, k, wid); return;
+        }
+    const float* x = (const float*)slot_ptr(xslot, (size_t)K * 4, who);
+    uint8_t* y = slot_ptr(yslot, yoff + (size_t)N * 4, who);
+    if (!x || !y) return;
+    if (!launch_gemv(x, s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream)) s.sticky = true;
+}
+
+}  // namespace
+
+}  // namespace tmc
+
+using namespace tmc;
+
+extern "C" {
+
+bool tm_cuda_tok_begin(void) {
+    if (!ensure_init(-1)) return false;
+    state().encoding = true;
+    return true;
+}
+bool tm_cuda_tok_flush(void) { return ensure_init(-1) && finish("tok_flush"); }
+bool tm_cuda_tok_end(int outslot, float* dst, unsigned n) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (n) {
+        if (!dst) return fail("tok_end: null destination");
+        const uint8_t* p = slot_ptr(outslot, (size_t)n * 4, "tok_end");
+        if (p && cudaMemcpyAsync(dst, p, (size_t)n * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) { check_launch("tok_end: download"); s.sticky = true; }
+    }
+    return finish("tok_end");
+}
+bool tm_cuda_tok_end_async(void) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    cudaEvent_t ev;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return check_launch("tok_end_async");
+    cudaEventRecord(ev, s.stream);
+    s.pending.push_back(ev);
+    s.encoding = false;
+    return true;
+}
+bool tm_cuda_tok_wait_pending(void) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    bool ok = true;
+    for (cudaEvent_t ev : s.pending) {
+        if (cudaEventSynchronize(ev) != cudaSuccess) { ok = false; fail("tok_wait_pending: %s", cudaGetErrorString(cudaGetLastError())); }
+        cudaEventDestroy(ev);
+    }
+    s.pending.clear();
+    return finish("tok_wait_pending") && ok;
+}
+bool tm_cuda_tok_reserve(int slot, size_t bytes) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (s.encoding) return fail("tok_reserve: not between tok_begin and the end of the token");
+    const bool before = s.sticky;
+    const bool ok = slot_ptr(slot, bytes, "tok_reserve") != nullptr;
+    if (!ok) s.sticky = before;            // a bool entry reports by its return value
+    return ok;
+}
+bool tm_cuda_tok_upload(int slot, size_t byte_off, const void* src, size_t bytes) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (!src && bytes) return fail("tok_upload: null source");
+    const bool before = s.sticky;
+    uint8_t* p = slot_ptr(slot, byte_off + bytes, "tok_upload");
+    if (!p) { s.sticky = before; return false; }
+    // Pageable host memory: the copy is staged before the call returns, so the
+    // caller may reuse `src` at once; it is still ordered after earlier lane work.
+    if (bytes && cudaMemcpyAsync(p + byte_off, src, bytes, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("tok_upload");
+    return true;
+}
+bool tm_cuda_tok_download(int slot, size_t byte_off, void* dst, size_t bytes) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (!dst && bytes) return fail("tok_download: null destination");
+    const bool before = s.sticky;
+    const uint8_t* p = slot_ptr(slot, byte_off + bytes, "tok_download");
+    if (!p) { s.sticky = before; return false; }
+    if (bytes && cudaMemcpyAsync(dst, p + byte_off, bytes, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("tok_download");
+    return sync_stream(s.stream, "tok_download");
+}
+bool tm_cuda_tok_kv_reserve(int slot, size_t n) { return ensure_init(-1) && tm_cuda_tok_reserve(slot, n * kv_elem()); }
+bool tm_cuda_tok_kv_upload(int slot, size_t elem_off, const float* src, size_t n) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (!s.kv_half) return tm_cuda_tok_upload(slot, elem_off * 4, src, n * 4);
+    if (!src && n) return fail("tok_kv_upload: null source");
+    const bool before = s.sticky;
+    uint8_t* p = slot_ptr(slot, (elem_off + n) * 2, "tok_kv_upload");
+    if (!p) { s.sticky = before; return false; }
+    if (!n) return true;
+    float* stage = (float*)s.io_big.get(n * 4);
+    if (!stage) return fail("tok_kv_upload: out of device memory");
+    if (cudaMemcpyAsync(stage, src, n * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("tok_kv_upload");
+    return launch_f32_to_half(stage, p + elem_off * 2, n, s.stream);
+}
+bool tm_cuda_tok_kv_download(int slot, size_t elem_off, float* dst, size_t n) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (!s.kv_half) return tm_cuda_tok_download(slot, elem_off * 4, dst, n * 4);
+    if (!dst && n) return fail("tok_kv_download: null destination");
+    const bool before = s.sticky;
+    const uint8_t* p = slot_ptr(slot, (elem_off + n) * 2, "tok_kv_download");
+    if (!p) { s.sticky = before; return false; }
+    if (!n) return true;
+    float* stage = (float*)s.io_big.get(n * 4);
+    if (!stage) return fail("tok_kv_download: out of device memory");
+    if (!launch_half_to_f32(p + elem_off * 2, stage, n, s.stream)) return false;
+    if (cudaMemcpyAsync(dst, stage, n * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("tok_kv_download");
+    return sync_stream(s.stream, "tok_kv_download");
+}
+
+int tm_cuda_tok_wbuf(const void* tensor_ptr, size_t bytes, const void* map_base, size_t map_size, int zero_copy,
+                     uint64_t* woff_out) {
+    if (woff_out) *woff_out = 0;
+    if (!ensure_init(-1) || !tensor_ptr || !bytes || !woff_out) { fail("tok_wbuf: bad arguments"); return -1; }
+    State& s = state();
+    auto it = s.wreg.find(tensor_ptr);
+    if (it != s.wreg.end()) { *woff_out = it->second.second; return it->second.first; }
+    if (zero_copy) {
+        const uintptr_t base = (uintptr_t)map_base, ptr = (uintptr_t)tensor_ptr;
+        if (!base || ptr < base || ptr - base > map_size || bytes > map_size - (ptr - base)) { fail("tok_wbuf: tensor outside the mapping"); return -1; }
+        if (s.shared_id < 0 || s.shared_base != map_base) {
+            // One resident copy of the whole mapping; tensor offsets are byte offsets into it.
+            uint8_t* d = nullptr;
+            if (cudaMalloc(&d, map_size + 32) != cudaSuccess) { cudaGetLastError(); fail("tok_wbuf: %zu bytes of device memory unavailable", map_size); return -1; }
+            if (cudaMemcpyAsync(d, map_base, map_size, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) { cudaFree(d); check_launch("tok_wbuf: upload"); return -1; }
+            cudaMemsetAsync(d + map_size, 0, 32, s.stream);
+            s.wbufs.push_back({d, map_size});
+            s.shared_id = kFirstWeight + (int)s.wbufs.size() - 1;
+            s.shared_base = map_base;
+        }
+        *woff_out = (uint64_t)(ptr - base);
+        s.wreg[tensor_ptr] = {s.shared_id, *woff_out};
+        return s.shared_id;
+    }
+    uint8_t* d = nullptr;
+    if (cudaMalloc(&d, bytes + 32) != cudaSuccess) { cudaGetLastError(); fail("tok_wbuf: %zu bytes of device memory unavailable", bytes); return -1; }
+    if (cudaMemcpyAsync(d, tensor_ptr, bytes, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) { cudaFree(d); check_launch("tok_wbuf: upload"); return -1; }
+    cudaMemsetAsync(d + bytes, 0, 32, s.stream);
+    s.wbufs.push_back({d, bytes});
+    const int id = kFirstWeight + (int)s.wbufs.size() - 1;
+    s.wreg[tensor_ptr] = {id, 0};
+    return id;
+}
+
+bool tm_cuda_tok_probe_copy(int srcslot, size_t src_off, int dstslot, unsigned n) {
+    if (!tm_cuda_tok_begin()) return false;
+    State& s = state();
+    const uint8_t* src = srcslot >= kFirstWeight ? weight_ptr(srcslot, src_off, n, "tok_probe_copy")
+                                                 : slot_ptr(srcslot, src_off + n, "tok_probe_copy");
+    if (src && srcslot < kFirstWeight) src += src_off;
+    s.encoding = false;                                  // the destination may be created here
+    uint8_t* dst = slot_ptr(dstslot, n, "tok_probe_copy");
+    s.encoding = true;
+    if (src && dst && !launch_copy_bytes(src, dst, n, s.stream)) s.sticky = true;
+    return tm_cuda_tok_end(dstslot, nullptr, 0);
+}
+
+void tm_cuda_tok_gemv(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K) {
+    gemv_common(xslot, wid, yslot, yoff, N, K, DT_Q4_0, &woff, &N, 1, "tok_gemv");
+}
+bool tm_cuda_tok_gemv_seg_supported(unsigned dtype) {
+    return dtype == DT_Q8_0 || dtype == DT_Q4_0 || dtype == DT_Q4_1 || dtype == DT_Q5_K || dtype == DT_Q6_K;
+}
+void tm_cuda_tok_gemv_seg(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K,
+                          const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg) {
+    gemv_common(xslot, wid, yslot, yoff, N, K, DT_Q4_0, seg_woff, seg_rows, nseg, "tok_gemv_seg");
+}
+void tm_cuda_tok_gemv_seg_dt(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                             const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg) {
+    if (!tm_cuda_tok_gemv_seg_supported(dtype)) { ensure_init(-1); fail("tok_gemv_seg_dt: no segmented GEMV for dtype %u", dtype); state().sticky = true; return; }
+    gemv_common(xslot, wid, yslot, yoff, N, K, dtype, seg_woff, seg_rows, nseg, "tok_gemv_seg_dt");
+}
+void tm_cuda_tok_gemv_kq(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype) {
+    if (!tm_cuda_tok_gemv_seg_supported(dtype)) { ensure_init(-1); fail("tok_gemv_kq: no GEMV for dtype %u", dtype); state().sticky = true; return; }
+    gemv_common(xslot, wid, yslot, yoff, N, K, dtype, &woff, &N, 1, "tok_gemv_kq");
+}
+
+void tm_cuda_tok_embed_kq(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const unsigned* tok = (const unsigned*)slot_ptr(tokslot, sizeof(unsigned) * ((size_t)idx + 1), "tok_embed");
+    float* x = (float*)slot_ptr(xslot, (size_t)D * 4, "tok_embed");
+    const uint8_t* W = weight_ptr(wid, woff, 0, "tok_embed");
+    if (!tok || !x || !W) return;
+    if (!launch_embed_row(tok, idx, W, x, D, dtype, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_embed_q4(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D) {
+    tm_cuda_tok_embed_kq(tokslot, idx, wid, woff, xslot, D, DT_Q4_0);
+}
+void tm_cuda_tok_bias_qkv(int yslot, int biasslot, size_t bias_off, unsigned N) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (bias_off % 4) { latch("tok_bias_qkv: byte offset %zu is not a multiple of 4", bias_off); return; }
+    float* y = (float*)slot_ptr(yslot, (size_t)N * 4, "tok_bias_qkv");
+    const uint8_t* b = slot_ptr(biasslot, bias_off + (size_t)N * 4, "tok_bias_qkv");
+    if (!y || !b) return;
+    if (!launch_bias(y, (const float*)(b + bias_off), N, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_rmsnorm(int xslot, const void* w, int outslot, unsigned D, float eps) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (!w || !D) { latch("tok_rmsnorm: bad arguments"); return; }
+    float* dw = nullptr;
+    auto it = s.norm_w.find(w);
+    if (it != s.norm_w.end()) dw = it->second;
+    else {
+        // copied once and cached by host pointer, like the reference (metal.h:3725-3735)
+        if (cudaMalloc(&dw, (size_t)D * 4) != cudaSuccess) { cudaGetLastError(); latch("tok_rmsnorm: weight allocation failed"); return; }
+        cudaMemcpyAsync(dw, w, (size_t)D * 4, cudaMemcpyHostToDevice, s.stream);
+        s.norm_w[w] = dw;
+    }
+    const float* x = (const float*)slot_ptr(xslot, (size_t)D * 4, "tok_rmsnorm");
+    float* out = (float*)slot_ptr(outslot, (size_t)D * 4, "tok_rmsnorm");
+    if (!x || !out) return;
+    if (!launch_rmsnorm(x, dw, out, D, eps, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_add(int a, int b, unsigned n) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    float* pa = (float*)slot_ptr(a, (size_t)n * 4, "tok_add");
+    const float* pb = (const float*)slot_ptr(b, (size_t)n * 4, "tok_add");
+    if (!pa || !pb) return;
+    if (!launch_add(pa, pb, n, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_silu_mul(int g, size_t goff, int u, size_t uoff, unsigned n) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (goff % 4 || uoff % 4) { latch("tok_silu_mul: byte offsets must be multiples of 4"); return; }
+    uint8_t* pg = slot_ptr(g, goff + (size_t)n * 4, "tok_silu_mul");
+    const uint8_t* pu = slot_ptr(u, uoff + (size_t)n * 4, "tok_silu_mul");
+    if (!pg || !pu) return;
+    if (!launch_silu_mul((float*)(pg + goff), (const float*)(pu + uoff), n, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_rope_q(int qslot, unsigned H, unsigned dh, int pos, float theta) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (!ensure_rope(dh, (unsigned)(pos > 0 ? pos + 1 : 1), theta)) return;
+    float* q = (float*)slot_ptr(qslot, (size_t)H * dh * 4, "tok_rope_q");
+    if (!q) return;
+    if (!launch_rope(q, H, dh, pos, s.rope_tbl, s.rope_cap * (dh / 2), s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_rope_k_cache(int ksrcslot, size_t ksrc_off, int cacheslot, unsigned KVH, unsigned dh, unsigned ctx,
+                              int pos, float theta) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (ksrc_off % 4) { latch("tok_rope_k_cache: byte offset must be a multiple of 4"); return; }
+    if (pos < 0 || (unsigned)pos >= ctx) { latch("tok_rope_k_cache: position %d outside the %u-row cache", pos, ctx); return; }
+    if (!ensure_rope(dh, ctx, theta)) return;
+    const uint8_t* k = slot_ptr(ksrcslot, ksrc_off + (size_t)KVH * dh * 4, "tok_rope_k_cache");
+    uint8_t* c = slot_ptr(cacheslot, kv_elem() * KVH * ctx * dh, "tok_rope_k_cache");
+    if (!k || !c) return;
+    if (!launch_rope_k_cache((const float*)(k + ksrc_off), c, s.kv_half, KVH, dh, ctx, pos, s.rope_tbl, s.rope_cap * (dh / 2), s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_v_cache(int vsrcslot, size_t vsrc_off, int cacheslot, unsigned KVH, unsigned dh, unsigned ctx, int pos) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (vsrc_off % 4) { latch("tok_v_cache: byte offset must be a multiple of 4"); return; }
+    if (pos < 0 || (unsigned)pos >= ctx) { latch("tok_v_cache: position %d outside the %u-row cache", pos, ctx); return; }
+    const uint8_t* v = slot_ptr(vsrcslot, vsrc_off + (size_t)KVH * dh * 4, "tok_v_cache");
+    uint8_t* c = slot_ptr(cacheslot, kv_elem() * KVH * ctx * dh, "tok_v_cache");
+    if (!v || !c) return;
+    if (!launch_v_cache((const float*)(v + vsrc_off), c, s.kv_half, KVH, dh, ctx, pos, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_attn(int qslot, int kcslot, int vcslot, int probslot, int outslot, unsigned QD, unsigned H,
+                      unsigned KVH, unsigned dh, unsigned ctx, int allow, float scale, unsigned REP) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    // the reference's argument check, metal.h:4157-4160
+    if (!H || !KVH || !dh || !ctx || allow <= 0 || (unsigned)allow > ctx || H % KVH || REP != H / KVH ||
+        (uint64_t)H * dh != QD || !std::isfinite(scale) || scale <= 0) {
+        latch("tok_attn: invalid decode attention dimensions or scale");
+        return;
+    }
+    const float* q = (const float*)slot_ptr(qslot, (size_t)QD * 4, "tok_attn");
+    const uint8_t* kc = slot_ptr(kcslot, kv_elem() * KVH * ctx * dh, "tok_attn");
+    const uint8_t* vc = slot_ptr(vcslot, kv_elem() * KVH * ctx * dh, "tok_attn");
+    float* out = (float*)slot_ptr(outslot, (size_t)QD * 4, "tok_attn");
+    // Split-K partials live in the probs slot, which the caller reserved for H*ctx floats.
+    float* probs = (float*)slot_ptr(probslot, (size_t)H * (dh + 2) * 4, "tok_attn");
+    if (!q || !kc || !vc || !out || !probs) return;
+    const AttnPlan pl = plan_attention(H, KVH, dh, ctx, (unsigned)allow, s.slots[probslot].bytes);
+    if (!pl.nsplit) { latch("tok_attn: probs slot too small for one split"); return; }
+    if (!launch_attention(q, kc, vc, s.kv_half, probs, out, H, KVH, dh, ctx, (unsigned)allow, scale, REP, pl, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_argmax(int xslot, int tokslot, unsigned idx, unsigned n) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, "tok_argmax");
+    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * ((size_t)idx + 1), "tok_argmax");
+    unsigned long long* sc = choose_scratch();
+    if (!x || !t || !sc) return;
+    if (!launch_choose(x, t, n, idx, 0.f, 0u, false, sc, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_sample(int xslot, int tokslot, unsigned idx, unsigned n, float inv_temp, unsigned seed) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, "tok_sample");
+    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * ((size_t)idx + 1), "tok_sample");
+    unsigned long long* sc = choose_scratch();
+    if (!x || !t || !sc) return;
+    if (!launch_choose(x, t, n, idx, inv_temp, seed, true, sc, s.stream)) s.sticky = true;
+}
+// Reads one token without waiting for the lane: a 4-byte copy on a second stream
+// (the reference polls shared memory with an acquire load, metal.h:3216-3226).
+unsigned tm_cuda_tok_peek(int tokslot, unsigned idx) {
+    if (!ensure_init(-1)) return 0xFFFFFFFFu;
+    State& s = state();
+    static cudaStream_t side = nullptr;
+    if (!side && cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) { check_launch("tok_peek"); return 0xFFFFFFFFu; }
+    if (!s.peek_host && cudaMallocHost(&s.peek_host, 64) != cudaSuccess) { check_launch("tok_peek"); return 0xFFFFFFFFu; }
+    if (tokslot < 0 || tokslot >= (int)s.slots.size() || !s.slots[tokslot].ptr ||
+        s.slots[tokslot].bytes < sizeof(unsigned) * ((size_t)idx + 1)) { fail("tok_peek: token slot %d too small", tokslot); return 0xFFFFFFFFu; }
+    if (cudaMemcpyAsync(s.peek_host, s.slots[tokslot].ptr + sizeof(unsigned) * (size_t)idx, 4, cudaMemcpyDeviceToHost, side) != cudaSuccess ||
+        cudaStreamSynchronize(side) != cudaSuccess) { check_launch("tok_peek"); return 0xFFFFFFFFu; }
+    return *s.peek_host;
+}
+void* tm_cuda_tok_slot_ptr(int slot) {
+    State& s = state();
+    return (slot >= 0 && slot < (int)s.slots.size()) ? s.slots[slot].ptr : nullptr;
+}
+void* tm_cuda_tok_stream(void) { return ensure_init(-1) ? (void*)state().stream : nullptr; }
+
+// glue on device pointers
+bool tm_cuda_rmsnorm_dev(const float* x, const float* w, float* out, unsigned D, float eps, void* stream) {
+    return ensure_init(-1) && launch_rmsnorm(x, w, out, D, eps, (cudaStream_t)stream);
+}
+bool tm_cuda_add_dev(float* a, const float* b, unsigned n, void* stream) { return ensure_init(-1) && launch_add(a, b, n, (cudaStream_t)stream); }
+bool tm_cuda_silu_mul_dev(float* g, const float* u, unsigned n, void* stream) { return ensure_init(-1) && launch_silu_mul(g, u, n, (cudaStream_t)stream); }
+bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream) {
+    if (!ensure_init(-1)) return false;
+    unsigned long long* sc = choose_scratch();
+    if (!sc) return fail("argmax: scratch allocation failed");
+    return launch_choose(x, out, n, 0, 0.f, 0u, false, sc, (cudaStream_t)stream);
+}
+
+// ---- the reference's symbol names (tensormark/metal_shim.mm:22-152) -------------------
+bool tm_metal_tok_begin(void) { return tm_cuda_tok_begin(); }
+bool tm_metal_tok_flush(void) { return tm_cuda_tok_flush(); }
+bool tm_metal_tok_end(int o, float* d, unsigned n) { return tm_cuda_tok_end(o, d, n); }
+bool tm_metal_tok_end_async(void) { return tm_cuda_tok_end_async(); }
+bool tm_metal_tok_wait_pending(void) { return tm_cuda_tok_wait_pending(); }
+bool tm_metal_tok_reserve(int s, size_t b) { return tm_cuda_tok_reserve(s, b); }
+bool tm_metal_tok_upload(int s, size_t o, const void* p, size_t b) { return tm_cuda_tok_upload(s, o, p, b); }
+bool tm_metal_tok_download(int s, size_t o, void* p, size_t b) { return tm_cuda_tok_download(s, o, p, b); }
+bool tm_metal_tok_kv_reserve(int s, size_t n) { return tm_cuda_tok_kv_reserve(s, n); }
+bool tm_metal_tok_kv_upload(int s, size_t o, const float* p, size_t n) { return tm_cuda_tok_kv_upload(s, o, p, n); }
+bool tm_metal_tok_kv_download(int s, size_t o, float* p, size_t n) { return tm_cuda_tok_kv_download(s, o, p, n); }
+int tm_metal_tok_wbuf(const void* t, size_t b, const void* mb, size_t ms, int z, uint64_t* w) { return tm_cuda_tok_wbuf(t, b, mb, ms, z, w); }
+bool tm_metal_tok_probe_copy(int a, size_t o, int d, unsigned n) { return tm_cuda_tok_probe_copy(a, o, d, n); }
+void tm_metal_tok_gemv(int x, int w, uint64_t wo, int y, size_t yo, unsigned N, unsigned K) { tm_cuda_tok_gemv(x, w, wo, y, yo, N, K); }
+bool tm_metal_tok_gemv_seg_supported(unsigned dt) { return tm_cuda_tok_gemv_seg_supported(dt); }
+void tm_metal_tok_gemv_seg(int x, int w, int y, size_t yo, unsigned N, unsigned K, const uint64_t* so, const unsigned* sr, unsigned ns) { tm_cuda_tok_gemv_seg(x, w, y, yo, N, K, so, sr, ns); }
+void tm_metal_tok_gemv_seg_dt(int x, int w, int y, size_t yo, unsigned N, unsigned K, unsigned dt, const uint64_t* so, const unsigned* sr, unsigned ns) { tm_cuda_tok_gemv_seg_dt(x, w, y, yo, N, K, dt, so, sr, ns); }
+void tm_metal_tok_gemv_kq(int x, int w, uint64_t wo, int y, size_t yo, unsigned N, unsigned K, unsigned dt) { tm_cuda_tok_gemv_kq(x, w, wo, y, yo, N, K, dt); }
+void tm_metal_tok_embed_q4(int t, unsigned i, int w, uint64_t wo, int x, unsigned D) { tm_cuda_tok_embed_q4(t, i, w, wo, x, D); }
+void tm_metal_tok_embed_kq(int t, unsigned i, int w, uint64_t wo, int x, unsigned D, unsigned dt) { tm_cuda_tok_embed_kq(t, i, w, wo, x, D, dt); }
+void tm_metal_tok_bias_qkv(int y, int b, size_t bo, unsigned N) { tm_cuda_tok_bias_qkv(y, b, bo, N); }
+void tm_metal_tok_rmsnorm(int x, const void* w, int o, unsigned D, float eps) { tm_cuda_tok_rmsnorm(x, w, o, D, eps); }
+void tm_metal_tok_add(int a, int b, unsigned n) { tm_cuda_tok_add(a, b, n); }
+void tm_metal_tok_silu_mul(int g, size_t go, int u, size_t uo, unsigned n) { tm_cuda_tok_silu_mul(g, go, u, uo, n); }
+void tm_metal_tok_rope_q(int q, unsigned H, unsigned dh, int pos, float th) { tm_cuda_tok_rope_q(q, H, dh, pos, th); }
+void tm_metal_tok_rope_k_cache(int k, size_t ko, int c, unsigned KVH, unsigned dh, unsigned ctx, int pos, float th) { tm_cuda_tok_rope_k_cache(k, ko, c, KVH, dh, ctx, pos, th); }
+void tm_metal_tok_v_cache(int v, size_t vo, int c, unsigned KVH, unsigned dh, unsigned ctx, int pos) { tm_cuda_tok_v_cache(v, vo, c, KVH, dh, ctx, pos); }
+void tm_metal_tok_attn(int q, int kc, int vc, int pr, int o, unsigned QD, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, int allow, float sc, unsigned REP) { tm_cuda_tok_attn(q, kc, vc, pr, o, QD, H, KVH, dh, ctx, allow, sc, REP); }
+void tm_metal_tok_argmax(int x, int t, unsigned i, unsigned n) { tm_cuda_tok_argmax(x, t, i, n); }
+void tm_metal_tok_sample(int x, int t, unsigned i, unsigned n, float it, unsigned sd) { tm_cuda_tok_sample(x, t, i, n, it, sd); }
+unsigned tm_metal_tok_peek(int t, unsigned i) { return tm_cuda_tok_peek(t, i); }
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+"""CPU: the host-side headers under include/, the GEMV lane maps, and the C ABI's symbol table."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+from tensormark_b200 import synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K]
+_f32p = C.POINTER(C.c_float)
+
+
+def _build(tmp, src, out, extra=()):
+    path = os.path.join(tmp, out)
+    subprocess.run(["g++", "-std=c++23", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-pthread",
+                    "-I" + os.path.join(ROOT, "include"), *extra, "-o", path, os.path.join(ROOT, "tests", "host", src)],
+                   check=True)
+    return C.CDLL(path)
+
+
+@pytest.fixture(scope="module")
+def hc(tmp_path_factory):
+    lib = _build(str(tmp_path_factory.mktemp("hc")), "host_contracts.cpp", "libhc.so")
+    lib.hc_dequant.argtypes = [C.c_uint, C.c_void_p, _f32p, C.c_size_t]
+    lib.hc_fp16_to_fp32.restype = C.c_float
+    lib.hc_fp16_to_fp32.argtypes = [C.c_uint16]
+    lib.hc_fp32_to_fp16.restype = C.c_uint16
+    lib.hc_fp32_to_fp16.argtypes = [C.c_float]
+    lib.hc_weight_bytes.restype = C.c_size_t
+    lib.hc_weight_bytes.argtypes = [C.c_uint, C.c_size_t, C.c_size_t]
+    lib.hc_pool_gemv.argtypes = [C.c_uint, C.c_void_p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+    return lib
+
+
+@pytest.fixture(scope="module")
+def lanes(tmp_path_factory):
+    lib = _build(str(tmp_path_factory.mktemp("lanes")), "lane_emul.cpp", "liblanes.so")
+    lib.lane_emul_gemv.argtypes = [C.c_int, C.c_void_p, _f32p, _f32p, C.c_uint, C.c_uint]
+    return lib
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_header_dequant_matches_golden(hc, golden, dt):
+    name = synth.DTYPE_NAMES[dt]
+    blocks = np.ascontiguousarray(golden[f"{name}_blocks"])
+    n = blocks.shape[0] * synth.BLOCK_ELEMS[dt]
+    out = np.empty(n, np.float32)
+    assert hc.hc_dequant(dt, blocks.ctypes.data, out.ctypes.data_as(_f32p), n)
+    assert np.array_equal(out.view(np.uint32), golden[f"{name}_dequant_bits"])
+
+
+def test_header_fp16_and_geometry(hc, golden):
+    fin = golden["fp32_to_fp16_in_bits"].view(np.float32)
+    got = np.array([hc.hc_fp32_to_fp16(float(v)) for v in fin], dtype=np.uint16)
+    assert np.array_equal(got, golden["fp32_to_fp16_out"])
+    want = golden["fp16_to_fp32_bits"]
+    for h in list(range(0, 2048)) + list(range(0x7bf0, 0x7c00)) + list(range(0x8000, 0x8400)):
+        assert np.float32(hc.hc_fp16_to_fp32(h)).view(np.uint32) == want[h]
+    for dt in DTYPES:
+        assert hc.hc_weight_bytes(dt, 7, 512) == synth.weight_bytes(dt, 7, 512)
+    assert hc.hc_weight_bytes(synth.Q6_K, 7, 96) == 0          # not whole super-blocks
+    out = np.empty(96, np.float32)
+    assert hc.hc_dequant(synth.Q6_K, out.ctypes.data, out.ctypes.data_as(_f32p), 96) == 0
+
+
+def test_projection_strategy_contract(hc):
+    assert hc.hc_strategy_selftest() == 0
+
+
+@pytest.mark.parametrize("dt", [synth.Q4_0, synth.Q5_K])
+def test_gemv_pool_rows(hc, orc, dt):
+    n, k = 200, 512                         # 200 rows: three full 64-row chunks and a ragged one
+    W = synth.make_weights(dt, n, k, seed=8)
+    x = synth.make_activations(k, seed=9)
+    y = np.zeros(n, np.float32)
+    used = hc.hc_pool_gemv(dt, W.ctypes.data, x.ctypes.data_as(_f32p), y.ctypes.data_as(_f32p), n, k, 3)
+    assert used == 3
+    y64, yabs = orc.gemv_f64(dt, W, x, n, k)
+    assert np.all(np.abs(y - y64) <= 1e-5 * yabs)
+
+
+@pytest.mark.parametrize("dt,shapes", [
+    (synth.Q4_0, [(5, 2048), (3, 5632), (3, 96), (2, 32)]),
+    (synth.Q8_0, [(5, 2048), (3, 5632), (2, 32)]),
+    (synth.Q4_1, [(5, 2048), (3, 5632), (2, 160)]),
+    (synth.Q5_K, [(4, 4096), (2, 14336), (3, 256), (2, 768)]),
+    (synth.Q6_K, [(4, 4096), (2, 14336), (3, 2048), (2, 256), (2, 5632)]),
+])
+def test_gemv_lane_maps_on_cpu(lanes, orc, dt, shapes):
+    """The kernel's lane decomposition, replayed on the CPU, against the fp64 reference.
+    Tolerance: 1e-3 * sum|w x| is the path's bar; the lane arithmetic itself stays below 2e-6."""
+    for n, k in shapes:
+        W = synth.make_weights(dt, n, k, seed=11)
+        x = synth.make_activations(k, seed=12)
+        y = np.zeros(n, np.float32)
+        assert lanes.lane_emul_gemv(dt, W.ctypes.data, x.ctypes.data_as(_f32p), y.ctypes.data_as(_f32p), n, k)
+        y64, yabs = orc.gemv_f64(dt, W, x, n, k)
+        assert np.all(np.abs(y - y64) <= 2e-6 * yabs), (synth.DTYPE_NAMES[dt], n, k)
+
+
+def _declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in sorted(os.listdir(inc)):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            names.update(re.findall(r"\b(tm_cuda_\w+)\s*\(", text))
+    return names
+
+
+def test_c_abi_exports_every_declared_symbol():
+    """Loads the library (no device needed for dlopen) and resolves every entry point the headers declare,
+    plus the reference's tm_metal_* names for the same entries."""
+    from tensormark_b200 import lib
+    if not os.path.exists(lib.LIB_PATH):
+        from tensormark_b200 import build
+        build.build()
+    L = lib.load()
+    declared = _declared_symbols()
+    assert len(declared) >= 50
+    for name in declared:
+        assert hasattr(L, name), name
+    assert declared == set(lib.SIGNATURES), declared ^ set(lib.SIGNATURES)
+    metal = ["tm_metal_q4_gemv", "tm_metal_sgemm_q4", "tm_metal_q4_prefill", "tm_metal_tok_begin", "tm_metal_tok_end",
+             "tm_metal_tok_gemv", "tm_metal_tok_gemv_seg", "tm_metal_tok_gemv_seg_dt", "tm_metal_tok_gemv_kq",
+             "tm_metal_tok_wbuf", "tm_metal_tok_attn", "tm_metal_tok_argmax", "tm_metal_tok_rmsnorm", "tm_metal_tok_peek"]
+    for name in metal:
+        assert hasattr(L, name), name
+    # pure host arithmetic works without a device
+    assert L.tm_cuda_weight_bytes(1, 2048, 2048) == 2048 * 64 * 18
+    assert L.tm_cuda_weight_bytes(6, 4, 100) == 0

@@ -14,8 +14,10 @@
 //   * A warp task is a group of R consecutive rows times one step of the row
 //     (2048 or 1024 weights); the lane's activations for that step are loaded into
 //     registers once and reused for the R rows.
-//   * x is staged once per CTA into swizzled shared memory together with its
-//     per-32-block sums (used to strip code offsets and zero points).
+//   * x is staged once per CTA into shared memory as block floating point (a scale and
+//     three int8 planes per 32 activations, see gemv_lanes.cuh) in the byte layout
+//     the lanes consume, together with the plain fp32 sums that carry zero points
+//     and mins; the inner loop is then integer dot products (dp4a) on the code bytes.
 //   * Rows are summed over lanes with shuffles in a fixed order, so a row's
 //     result does not depend on the grid, on R, or on whether it was reached
 //     through a segment table: the segmented launch is bit-identical to separate
@@ -31,11 +33,13 @@
 #include "common.cuh"
 #include "gemv_lanes.cuh"
 
+#include <cstdlib>
+
 namespace tmc {
 
 namespace {
 
-constexpr int kWarps = 8;          // warps per CTA
+constexpr int kMaxWarps = 16;       // warps per CTA: 16 (512 threads x 128 registers fill the register file) or 8
 constexpr int kMaxStages = 8;      // ring depth per warp is chosen at launch, 2..kMaxStages
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a copy that has not landed in 2 s never will
 
@@ -44,7 +48,7 @@ struct GemvParams {
     const float* x;
     float* y;
     uint32_t N, K, row_bytes;
-    uint32_t stages;
+    uint32_t stages, rows_per_warp;
     SegTable seg;
     int* status;
 };
@@ -103,27 +107,31 @@ template <int DT> __device__ __forceinline__ int lane_valid(int lane, int units_
     }
 }
 
-// Shared memory: [x: padded K floats, swizzled float4 slots][xsum: padded K/32][mbarriers][stages]
-template <int DT, int R>
-__global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream(const GemvParams p) {
+// Shared memory: [x units: one per lane and step][mbarriers][stages]
+//
+// Work split: the rows are cut into one contiguous range per warp of the grid
+// (rows_per_warp = ceil(N / warps)), so every warp streams one contiguous piece of
+// the tensor and the ranges differ by at most one row. A warp walks its range in
+// groups of R rows; a group times one step of the row is one ring item.
+template <int DT, int R, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const GemvParams p) {
     using L = Lane<DT>;
     constexpr int ROWCAP = L::STEP_BYTES;                  // multiple of 16
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nchunks = (p.K + L::STEP_W - 1) / L::STEP_W;
-    const uint32_t kpad = nchunks * L::STEP_W;
-    float4* xs4 = reinterpret_cast<float4*>(smem);
-    float* xsum = reinterpret_cast<float*>(smem + (size_t)kpad * 4);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kpad * 4 + (size_t)(kpad / 32) * 4);
+    const uint32_t nunits = nchunks * 32u;
+    uint32_t* units = reinterpret_cast<uint32_t*>(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (((size_t)nunits * L::XW * 4 + 127) / 128) * 128);
     const uint32_t S = p.stages;
-    uint8_t* stages = reinterpret_cast<uint8_t*>(bars) + ((kWarps * kMaxStages * 8 + 127) / 128) * 128;
+    uint8_t* stages = reinterpret_cast<uint8_t*>(bars) + ((kMaxWarps * kMaxStages * 8 + 127) / 128) * 128;
     uint64_t* mybar = bars + warp * kMaxStages;
     uint8_t* mystage = stages + (size_t)warp * S * R * ROWCAP;
 
-    const uint32_t ngroups = (p.N + R - 1) / R;
-    const uint32_t gwarp = blockIdx.x * kWarps + warp, nwarps = gridDim.x * kWarps;
-    const uint32_t mygroups = ngroups > gwarp ? (ngroups - gwarp + nwarps - 1) / nwarps : 0;
-    const uint32_t items = mygroups * nchunks;
+    const uint32_t gwarp = blockIdx.x * kWarps + warp;
+    const uint32_t row_lo = min(p.N, gwarp * p.rows_per_warp), row_hi = min(p.N, row_lo + p.rows_per_warp);
+    const uint32_t ngroups = (row_hi - row_lo + R - 1) / R;
+    const uint32_t items = ngroups * nchunks;
 
     if (lane == 0) {
         for (uint32_t s = 0; s < S; ++s) mbar_init(&mybar[s], 1);
@@ -131,20 +139,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream(const GemvParams p
     }
     __syncwarp();
 
-    // item t -> (row group, chunk); lane 0 posts the R row copies of the item into ring slot `slot`
-    auto issue = [&](uint32_t t, uint32_t slot) {
-        const uint32_t g = gwarp + (t / nchunks) * nwarps, c = t % nchunks;
-        const uint32_t off = c * (uint32_t)L::STEP_BYTES;
+    // Issue cursor (same value in every lane): next item = rows [irow, irow+R) x step ic.
+    uint32_t irow = row_lo, ic = 0, issued = 0;
+    auto issue = [&](uint32_t slot) {
+        const uint32_t rows = min((uint32_t)R, row_hi - irow);
+        const uint32_t off = ic * (uint32_t)L::STEP_BYTES;
         const uint32_t bytes = min((uint32_t)L::STEP_BYTES, p.row_bytes - off);
-        uint64_t* bar = &mybar[slot];
-        uint8_t* dst = mystage + (size_t)slot * R * ROWCAP;
-        uint32_t rows = min((uint32_t)R, p.N - g * R);
-        mbar_expect_tx(bar, rows * bytes);
-        for (uint32_t r = 0; r < rows; ++r)
-            bulk_g2s(dst + r * ROWCAP, row_ptr(p, g * R + r) + off, bytes, bar);
+        if (lane == 0) mbar_expect_tx(&mybar[slot], rows * bytes);
+        if ((uint32_t)lane < rows)                          // one row copy per lane, issued in parallel
+            bulk_g2s(mystage + ((size_t)slot * R + lane) * ROWCAP, row_ptr(p, irow + lane) + off, bytes, &mybar[slot]);
+        if (++ic == nchunks) { ic = 0; irow += R; }
+        ++issued;
     };
-    if (lane == 0)
-        for (uint32_t t = 0; t < items && t < S; ++t) issue(t, t);
+    for (uint32_t s = 0; s < S && issued < items; ++s) issue(s);
 
     // Everything above touches only weights. x may be written by the preceding
     // kernel in the stream: wait for it here, and let the next kernel start its own
@@ -152,20 +159,63 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream(const GemvParams p
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // ---- stage x (swizzled) and its 32-block sums --------------------------
-    const float4* xg4 = reinterpret_cast<const float4*>(p.x);
-    for (uint32_t q = threadIdx.x; q < kpad / 4; q += blockDim.x) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (q * 4 < p.K) v = __ldcg(xg4 + q);                // K is a multiple of 32
-        xs4[x_slot(q)] = v;
-    }
-    for (uint32_t b = threadIdx.x; b < kpad / 32; b += blockDim.x) {
-        float s = 0.f;
-        if (b * 32 < p.K) {
+    // ---- stage x: block floating point planes in the lanes' byte layout -------
+    // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
+    // the run sums come from three shuffle stages, the plane bytes leave as packed stores.
+    // A warp stages four blocks per pass and two passes are interleaved.
+    {
+        constexpr int B = 2;
+        const uint32_t nblk = p.K / 32, li = lane & 7u, sub = lane >> 3;
+        const float4* xg4 = reinterpret_cast<const float4*>(p.x);
+        for (uint32_t b0 = warp * (4 * B); b0 < nblk; b0 += kWarps * (4 * B)) {
+            float4 v[B];
+            float am[B], s8[B], s16[B], s32[B];
+            bool bad[B];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { const float4 v = __ldcg(xg4 + b * 8 + i); s += (v.x + v.y) + (v.z + v.w); }
+            for (int j = 0; j < B; ++j) {
+                const uint32_t b = b0 + 4 * j + sub;
+                v[j] = b < nblk ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+                am[j] = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+                const float any_nan = (v[j].x + v[j].y) + (v[j].z + v[j].w);         // NaN if any element is NaN
+                bad[j] = !(am[j] <= 3.0e38f) || any_nan != any_nan;
+                s8[j] = (v[j].x + v[j].y) + (v[j].z + v[j].w);
+            }
+#pragma unroll
+            for (int o = 1; o <= 4; o <<= 1)
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    am[j] = fmaxf(am[j], __shfl_xor_sync(0xffffffffu, am[j], o));
+                    bad[j] = bad[j] || __shfl_xor_sync(0xffffffffu, (int)bad[j], o);
+                }
+            if (L::NEEDS_SUMS) {
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    s8[j] += __shfl_xor_sync(0xffffffffu, s8[j], 1);                  // 8 activations
+                    s16[j] = s8[j] + __shfl_xor_sync(0xffffffffu, s8[j], 2);          // 16
+                    s32[j] = s16[j] + __shfl_xor_sync(0xffffffffu, s16[j], 4);        // 32
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < B; ++j) s16[j] = s32[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                const uint32_t b = b0 + 4 * j + sub;
+                if (b < nblk) {
+                    float inv;
+                    const float sc = block_scale(am[j], bad[j], inv);
+                    int8_t q0[kPlanes], q1[kPlanes], q2[kPlanes], q3[kPlanes];
+                    quantize_elem(v[j].x, inv, q0); quantize_elem(v[j].y, inv, q1);
+                    quantize_elem(v[j].z, inv, q2); quantize_elem(v[j].w, inv, q3);
+#pragma unroll
+                    for (int t = 0; t < kPlanes; ++t)
+                        L::store_quad(units, b * 32 + 4 * li, t,
+                                      (uint32_t)(uint8_t)q0[t] | ((uint32_t)(uint8_t)q1[t] << 8) |
+                                      ((uint32_t)(uint8_t)q2[t] << 16) | ((uint32_t)(uint8_t)q3[t] << 24));
+                    L::scalars(units, b, (int)(4 * li), (int)li, sc, s8[j], s16[j], s32[j]);
+                }
+            }
         }
-        xsum[b] = s;
     }
     __syncthreads();
 
@@ -173,39 +223,64 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream(const GemvParams p
     typename L::X xr;
     float acc[R];
     bool dead = false;
-    uint32_t slot = 0, phase = 0, k = 0, c = 0;
+    uint32_t slot = 0, phase = 0, c = 0, row0 = row_lo;
     for (uint32_t t = 0; t < items; ++t) {
         if (c == 0) {
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r] = 0.f;
         }
-        if (nchunks > 1 || t == 0) L::load_x(xr, xs4, xsum, (int)c, lane);
+        if (nchunks > 1 || t == 0) load_x_unit<DT>(xr, units, c * 32u + (uint32_t)lane);
         if (!mbar_wait(&mybar[slot], phase)) { dead = true; break; }
         const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - c * L::STEP_W);
         const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
         const uint8_t* st = mystage + (size_t)slot * R * ROWCAP;
+        const uint32_t rows = min((uint32_t)R, row_hi - row0);
         if (L::LANE_UNITS == 2 ? valid > 0 : true) {
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const uint8_t* rowp = st + r * ROWCAP + (L::LANE_UNITS == 2 ? lane * L::LANE_BYTES : 0);
-                acc[r] += L::dot(rowp, xr, lane, valid);
+                if ((uint32_t)r < rows) {                   // warp-uniform: rows past the range were never copied
+                    const uint8_t* rowp = st + r * ROWCAP + (L::LANE_UNITS == 2 ? lane * L::LANE_BYTES : 0);
+                    acc[r] += L::dot(rowp, xr, lane, valid);
+                }
             }
         }
         __syncwarp();                                       // every lane is done with this stage
-        if (lane == 0 && t + S < items) issue(t + S, slot);
+        if (issued < items) issue(slot);
         if (++slot == S) { slot = 0; phase ^= 1u; }
-        if (c + 1 == nchunks) {
-            const uint32_t row0 = (gwarp + k * nwarps) * R;
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                float v = acc[r];
-#pragma unroll
-                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == r && row0 + r < p.N) p.y[row0 + r] = v;
+        if (++c == nchunks) {
+            // Sum over lanes. The butterfly order (xor 16, 8, 4, 2, 1) is the same for every
+            // R, so a row's bits do not depend on how rows were grouped; with R > 1 the first
+            // stages also fold the R rows onto disjoint lanes to save shuffles.
+            float v;
+            int my_row;
+            if constexpr (R == 4) {
+                const bool h16 = lane & 16, h8 = lane & 8;
+                float k0 = h16 ? acc[2] : acc[0], k1 = h16 ? acc[3] : acc[1];
+                const float s0 = h16 ? acc[0] : acc[2], s1 = h16 ? acc[1] : acc[3];
+                k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+                k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+                v = h8 ? k1 : k0;
+                const float sv = h8 ? k0 : k1;
+                v += __shfl_xor_sync(0xffffffffu, sv, 8);
+                my_row = (h16 ? 2 : 0) + (h8 ? 1 : 0);
+            } else if constexpr (R == 2) {
+                const bool h16 = lane & 16;
+                v = h16 ? acc[1] : acc[0];
+                const float sv = h16 ? acc[0] : acc[1];
+                v += __shfl_xor_sync(0xffffffffu, sv, 16);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                my_row = h16 ? 1 : 0;
+            } else {
+                v = acc[0];
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                my_row = 0;
             }
-            c = 0; ++k;
-        } else {
-            ++c;
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) p.y[row0 + my_row] = v;
+            c = 0; row0 += R;
         }
     }
     if (dead) {
@@ -217,9 +292,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_stream(const GemvParams p
         }
     }
 }
-
-// Rows beyond N inside a group are never copied; their lanes multiply stale stage
-// bytes and the result is dropped at the store, so nothing there needs clearing.
 
 // ---- generic kernel: any alignment, byte loads, one warp per row --------------
 template <int DT>
@@ -318,64 +390,92 @@ constexpr size_t kSmemLimit = 227 * 1024;
 // Bytes of shared memory outside the stage rings.
 template <int DT> size_t stream_fixed_smem(unsigned K) {
     using L = Lane<DT>;
-    const size_t nchunks = (K + L::STEP_W - 1) / L::STEP_W, kpad = nchunks * L::STEP_W;
-    return kpad * 4 + kpad / 32 * 4 + ((kWarps * kMaxStages * 8 + 127) / 128) * 128 + 128;
+    const size_t nchunks = (K + L::STEP_W - 1) / L::STEP_W;
+    return ((nchunks * 32 * L::XW * 4 + 127) / 128) * 128 + ((kMaxWarps * kMaxStages * 8 + 127) / 128) * 128 + 128;
 }
 // Deepest ring (<= kMaxStages) that fits next to x; 0 when not even two stages fit.
-template <int DT> unsigned stream_stages(unsigned K, int R) {
+template <int DT> unsigned stream_stages(unsigned K, int R, int warps, unsigned ctas_per_sm) {
     using L = Lane<DT>;
-    const size_t fixed = stream_fixed_smem<DT>(K), per = (size_t)kWarps * R * L::STEP_BYTES;
-    if (fixed + 2 * per > kSmemLimit) return 0;
-    const size_t s = (kSmemLimit - fixed) / per;
+    const size_t fixed = stream_fixed_smem<DT>(K), per = (size_t)warps * R * L::STEP_BYTES;
+    const size_t limit = ctas_per_sm > 1 ? (kSmemLimit + 1024) / ctas_per_sm - 1024 : kSmemLimit;   // 1 KB per CTA is reserved by the system
+    if (fixed + 2 * per > limit) return 0;
+    const size_t s = (limit - fixed) / per;
     return (unsigned)(s > (size_t)kMaxStages ? kMaxStages : s);
 }
 
-template <int DT, int R>
-bool launch_stream_r(GemvParams p, cudaStream_t st) {
+int env_int(const char* name, int dflt) {
+    const char* e = std::getenv(name);
+    return e && *e ? std::atoi(e) : dflt;
+}
+
+template <int DT, int R, int kWarps>
+bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, cudaStream_t st) {
     using L = Lane<DT>;
-    p.stages = stream_stages<DT>(p.K, R);
+    p.stages = stages;
     const size_t smem = stream_fixed_smem<DT>(p.K) + (size_t)p.stages * kWarps * R * L::STEP_BYTES;
     static bool attr_set = false;
+    static const bool pdl = env_int("TM_GEMV_PDL", 1) != 0;     // A/B knob: 0 launches without programmatic serialization
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemv_stream<DT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemv_stream<DT, R, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit) != cudaSuccess)
             return fail("gemv: cannot raise the dynamic shared memory limit");
         attr_set = true;
     }
-    const unsigned ngroups = (p.N + R - 1) / R;
-    unsigned grid = (ngroups + kWarps - 1) / kWarps;
-    const unsigned sms = (unsigned)device_sm_count();
-    if (grid > sms) grid = sms;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, gemv_stream<DT, R>, p) != cudaSuccess) return check_launch("gemv_stream");
+    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, gemv_stream<DT, R, kWarps>, p) != cudaSuccess) return check_launch("gemv_stream");
     note_launch();
     return true;
 }
 
 template <int DT>
-bool launch_dt(const GemvParams& p, bool aligned, cudaStream_t st) {
+bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
     using L = Lane<DT>;
     if (aligned) {
-        // Rows per warp task: 4 when that still gives every warp of the machine a
-        // task, fewer for short matrices so the rows spread over more SMs.
-        const unsigned warps = (unsigned)device_sm_count() * kWarps;
-        int R = 4;
-        if ((p.N + 3) / 4 < warps) R = 2;
-        if ((p.N + 1) / 2 < warps) R = 1;
-        while (R > 1 && stream_stages<DT>(p.K, R) < 3) R >>= 1;
-        if (stream_stages<DT>(p.K, R) >= 2) {
+        const unsigned sms = (unsigned)device_sm_count();
+        static const int force_r = env_int("TM_GEMV_R", 0), force_s = env_int("TM_GEMV_STAGES", 0),
+                         force_w = env_int("TM_GEMV_WARPS", 0);
+        // One 16-warp CTA per SM; matrices too short to give every one of those warps a row use
+        // 8-warp CTAs (more CTAs share the staging of x, and they leave half of the register file
+        // to the next kernel of the stream). TM_GEMV_WARPS overrides.
+        int warps_cta = p.N >= 16u * sms ? 16 : 8;
+        if (force_w == 8 || force_w == 16) warps_cta = force_w;
+        const unsigned ctas_per_sm = 1;
+        unsigned grid = (p.N + warps_cta - 1) / warps_cta;
+        if (grid > sms * ctas_per_sm) grid = sms * ctas_per_sm;
+        const unsigned warps = grid * warps_cta;
+        p.rows_per_warp = (p.N + warps - 1) / warps;
+        // Rows per ring item: as many as the warp's range offers (x registers are reused
+        // across them), at most 4, and few enough that at least two stages fit.
+        int R = p.rows_per_warp >= 4 ? 4 : p.rows_per_warp >= 2 ? 2 : 1;
+        if (force_r == 1 || force_r == 2 || force_r == 4) R = force_r;
+        while (R > 1 && stream_stages<DT>(p.K, R, warps_cta, ctas_per_sm) < 2) R >>= 1;
+        unsigned S = stream_stages<DT>(p.K, R, warps_cta, ctas_per_sm);
+        if (S >= 2) {
+            // No deeper than the warp has items, and by default no deeper than 3: the ring only
+            // has to cover the DRAM latency, and a small footprint helps kernels overlap.
+            const unsigned items = ((p.rows_per_warp + R - 1) / R) * ((p.K + L::STEP_W - 1) / L::STEP_W);
+            unsigned cap = force_s >= 2 ? (unsigned)force_s : 3u;
+            if (cap > (unsigned)kMaxStages) cap = kMaxStages;
+            if (S > cap) S = cap;
+            if (S > items) S = items < 1 ? 1 : items;
+            if (warps_cta == 16) {
+                switch (R) {
+                    case 4: return launch_stream_r<DT, 4, 16>(p, S, grid, st);
+                    case 2: return launch_stream_r<DT, 2, 16>(p, S, grid, st);
+                    default: return launch_stream_r<DT, 1, 16>(p, S, grid, st);
+                }
+            }
             switch (R) {
-                case 4: return launch_stream_r<DT, 4>(p, st);
-                case 2: return launch_stream_r<DT, 2>(p, st);
-                default: return launch_stream_r<DT, 1>(p, st);
+                case 4: return launch_stream_r<DT, 4, 8>(p, S, grid, st);
+                case 2: return launch_stream_r<DT, 2, 8>(p, S, grid, st);
+                default: return launch_stream_r<DT, 1, 8>(p, S, grid, st);
             }
         }
     }
-    (void)sizeof(L);
     const unsigned rows_per_cta = 8;
     gemv_generic<DT><<<(p.N + rows_per_cta - 1) / rows_per_cta, rows_per_cta * 32, 0, st>>>(p);
     note_launch();

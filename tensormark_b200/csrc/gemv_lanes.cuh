@@ -2,25 +2,35 @@
 //
 // One warp consumes one "step" of a weight row at a time: a contiguous run of
 // blocks staged in shared memory by a bulk copy. Each format fixes how the 32
-// lanes divide a step (STEP_W weights, STEP_BYTES bytes), which activations a
-// lane keeps in registers for that step (struct X, loaded once and reused for
-// every row of the warp's row group), and how the lane turns its bytes into a
-// partial dot product (dot()).
+// lanes divide a step (STEP_W weights, STEP_BYTES bytes), what a lane keeps in
+// registers about the activations of its slice (an "x unit" of XW 32-bit words,
+// staged once per CTA and reused for every row), and how the lane turns its bytes
+// into a partial dot product (dot()).
 //
-// Decoding never converts integers: a code byte is moved by one PRMT into the
-// mantissa of a constant (128.0f for codes below 128, 32768.0f for full bytes),
-// which yields the float (OFFSET + code) exactly. Products are accumulated with
-// packed FFMA2 and the offset (plus the format's zero point) is removed once per
-// block with the block's activation sum:  sum (code-zp)*x = sum f*x - (OFF+zp)*X.
-// The added rounding error is below 1e-5 of sum|w*x| for every format here,
-// against the path's 1e-3 tolerance. Q8_0 bytes would need OFFSET 32768 (~500x
-// the mean code), so its offset is subtracted exactly before the multiply.
+// Arithmetic. The integer codes of a block are never converted one by one. The
+// activations of every 32-block are re-expressed once per kernel as block floating
+// point: a scale s = max|x|/127 and three signed 8-bit planes with
+//     x[i] ~= s * (a1[i] + a2[i]/128 + a3[i]/16384),   error <= 2^-22 * max|x|,
+// which is the precision of an fp32 product chain. A block's dot product is then
+// three exact integer dot products sum(code * a_t) on the dp4a unit (four
+// multiply-adds per instruction, the code bytes used as they lie in the block),
+// combined in fp32, multiplied by the fp16 block scale and added to the row's fp32
+// accumulator: exact within a block, fp32 across blocks, like the reference's
+// per-block partial sums (tensormark/llama.h:1877-1895). Zero points and mins are
+// applied with the true fp32 sums of x, so nothing depends on the planes' rounding
+// beyond the 2^-22 above. NaN or infinite activations poison the block scale and
+// therefore the output, as a floating-point chain would.
 //
-// Everything in this header is __host__ __device__ so the lane maps can be run
-// lane by lane on a CPU against the checker before a GPU ever sees them.
+// The x planes are laid out to mirror the BYTE positions of the weight block a lane
+// reads (scale bytes are matched by zero activation bytes), so a lane never
+// realigns or repacks weight words: load, mask nibbles if the format has them,
+// dp4a.
 //
-// Layouts decoded here are the serialized blocks of tensormark/quant.h:35-49 and
-// 214-245; the GPU kernels they replace are the cooperative-row GEMVs of
+// Everything here is __host__ __device__: the test-suite replays the lane maps on a
+// CPU against the checker before a GPU ever runs them.
+//
+// Layouts decoded are the serialized blocks of tensormark/quant.h:35-49 and
+// 214-245; the GPU kernels replaced are the cooperative-row GEMVs of
 // tensormark/metal.h:359-440 (Q4_0), 641-679 (Q4_1), 708-754 (Q5_K), 775-822 (Q6_K).
 #pragma once
 
@@ -41,17 +51,9 @@ struct uint4 { unsigned x, y, z, w; };
 
 namespace tmc {
 
+constexpr int kPlanes = 3;
+
 // ---- primitives with host emulation ----------------------------------------
-TM_HD uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-#if defined(__CUDA_ARCH__)
-    return __byte_perm(a, b, sel);
-#else
-    const uint64_t v = ((uint64_t)b << 32) | a;
-    uint32_t r = 0;
-    for (int k = 0; k < 4; ++k) r |= (uint32_t)((v >> (8 * ((sel >> (4 * k)) & 7))) & 0xff) << (8 * k);
-    return r;
-#endif
-}
 TM_HD float as_float(uint32_t u) {
 #if defined(__CUDA_ARCH__)
     return __uint_as_float(u);
@@ -59,18 +61,11 @@ TM_HD float as_float(uint32_t u) {
     float f; memcpy(&f, &u, 4); return f;
 #endif
 }
-TM_HD float2 fma2(float2 a, float2 b, float2 c) {
+TM_HD uint32_t as_uint(float f) {
 #if defined(__CUDA_ARCH__)
-    return __ffma2_rn(a, b, c);
+    return __float_as_uint(f);
 #else
-    float2 r; r.x = fmaf(a.x, b.x, c.x); r.y = fmaf(a.y, b.y, c.y); return r;
-#endif
-}
-TM_HD float2 add2(float2 a, float2 b) {
-#if defined(__CUDA_ARCH__)
-    return __fadd2_rn(a, b);
-#else
-    float2 r; r.x = a.x + b.x; r.y = a.y + b.y; return r;
+    uint32_t u; memcpy(&u, &f, 4); return u;
 #endif
 }
 TM_HD float fma1(float a, float b, float c) {
@@ -88,8 +83,7 @@ TM_HD float half_to_float(uint32_t h) {
     if (e == 31u) return as_float(s | 0x7f800000u | (m << 13));
     if (e != 0u) return as_float(s | ((e + 112u) << 23) | (m << 13));
     const float mag = (float)m * 0x1p-24f;
-    uint32_t b; memcpy(&b, &mag, 4);
-    return as_float(s | b);
+    return as_float(s | as_uint(mag));
 #endif
 }
 TM_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t sh) {   // sh in {0, 16}
@@ -99,17 +93,47 @@ TM_HD uint32_t funnel_r(uint32_t lo, uint32_t hi, uint32_t sh) {   // sh in {0, 
     return sh ? ((lo >> sh) | (hi << (32 - sh))) : lo;
 #endif
 }
-
-// float (128 + byte B of a), valid for bytes below 128
-template <int B> TM_HD float code128(uint32_t a) { return as_float(prmt(a, 0x43000000u, 0x7054u | (B << 8))); }
-// float (32768 + byte B of a), any byte
-template <int B> TM_HD float code32768(uint32_t a) { return as_float(prmt(a, 0x47000000u, 0x7604u | (B << 4))); }
-
-// Activations live in shared memory as float4 slots, XOR-swizzled so that the 8
-// lanes of a quarter warp that read 64-byte-strided runs hit different banks.
-TM_HD uint32_t x_slot(uint32_t q) { return q ^ ((q >> 4) & 7u); }
-
-TM_HD float2 mk2(float a, float b) { float2 r; r.x = a; r.y = b; return r; }
+// c + sum of four (unsigned byte of a) * (signed byte of b)
+TM_HD int dp4a_us(uint32_t a, uint32_t b, int c) {
+#if defined(__CUDA_ARCH__)
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+#else
+    for (int k = 0; k < 4; ++k) c += (int)((a >> (8 * k)) & 0xff) * (int)(int8_t)((b >> (8 * k)) & 0xff);
+    return c;
+#endif
+}
+// c + sum of four (signed byte of a) * (signed byte of b)
+TM_HD int dp4a_ss(uint32_t a, uint32_t b, int c) {
+#if defined(__CUDA_ARCH__)
+    return __dp4a((int)a, (int)b, c);
+#else
+    for (int k = 0; k < 4; ++k) c += (int)(int8_t)((a >> (8 * k)) & 0xff) * (int)(int8_t)((b >> (8 * k)) & 0xff);
+    return c;
+#endif
+}
+TM_HD float ld_x(const float* p) {
+#if defined(__CUDA_ARCH__)
+    return __ldcg(p);           // x is produced by the preceding kernel: read it through L2
+#else
+    return *p;
+#endif
+}
+TM_HD int round_int(float v) {
+#if defined(__CUDA_ARCH__)
+    return __float2int_rn(v);
+#else
+    return (int)lrintf(v);
+#endif
+}
+// S1 + S2/128 + S3/16384 in fp32 (each S_t is an exact integer below 2^24)
+TM_HD float planes_to_float(const int* S) {
+    float f = (float)S[0];
+    if (kPlanes > 1) f = fma1((float)S[1], 1.0f / 128.0f, f);
+    if (kPlanes > 2) f = fma1((float)S[2], 1.0f / 16384.0f, f);
+    return f;
+}
 
 // 8 bytes from an address that is 2-byte but maybe not 4-byte aligned.
 TM_HD uint2 load8(const uint8_t* p) {
@@ -126,7 +150,7 @@ TM_HD uint2 load8(const uint8_t* p) {
 #endif
     return r;
 }
-TM_HD uint4 load16a(const uint8_t* p) {                    // 16-byte aligned
+TM_HD uint4 load16a(const void* p) {                       // 16-byte aligned
 #if defined(__CUDA_ARCH__)
     return *(const uint4*)p;
 #else
@@ -141,167 +165,225 @@ TM_HD uint32_t load4a(const uint8_t* p) {
 #endif
 }
 
-constexpr uint32_t kLo = 0x0F0F0F0Fu;
+constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
 
-// ---------------------------------------------------------------------------
-// 32-weight block formats: a lane owns two consecutive blocks (64 weights).
-// ---------------------------------------------------------------------------
-struct X64 {
-    float2 v[32];     // the lane's 64 activations, in element order
-    float bs[2];      // activation sums of its two 32-blocks
-};
-
-// chunk = index of this step inside the row; xs4 = swizzled activations;
-// xsum = per-32-block activation sums (zero padded to whole steps).
-TM_HD void load_x64(X64& x, const float4* xs4, const float* xsum, int chunk, int lane) {
-    const uint32_t q0 = (uint32_t)chunk * 512u + (uint32_t)lane * 16u;
+// ---- block floating point of 32 activations ----------------------------------
+// Block scale from the block's max |x| (and whether the block holds NaN/inf):
+// x ~= s * (a[0] + a[1]/128 + a[2]/16384). A poisoned block gets s = NaN so every
+// output that touches it is NaN; a block of zeros (or of values too small to
+// scale) gets s = 0.
+TM_HD float block_scale(float amax, bool bad, float& inv) {
+    if (bad) { inv = 0.f; return as_float(0x7fc00000u); }
+    if (!(amax >= 1.0e-30f)) { inv = 0.f; return 0.f; }
+    inv = 127.0f / amax;
+    return amax * (1.0f / 127.0f);                          // s * inv == 1 to within 2^-23, far below the plane truncation
+}
+// The kPlanes signed bytes of one activation under its block's inverse scale.
+TM_HD void quantize_elem(float v, float inv, int8_t* a) {
+    float r = inv == 0.f ? 0.f : v * inv;                   // inv is 0 for empty and for poisoned blocks
+    r = r > 127.f ? 127.f : (r < -127.f ? -127.f : r);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float4 t = xs4[x_slot(q0 + i)];
-        x.v[2 * i] = mk2(t.x, t.y);
-        x.v[2 * i + 1] = mk2(t.z, t.w);
+    for (int t = 0; t < kPlanes; ++t) {
+        const int q = round_int(r);
+        a[t] = (int8_t)q;
+        r = (r - (float)q) * 128.0f;                        // exact: |r - q| <= 0.5 and the factor is a power of two
     }
-    x.bs[0] = xsum[chunk * 64 + 2 * lane];
-    x.bs[1] = xsum[chunk * 64 + 2 * lane + 1];
+}
+
+// two zero bytes at an even byte offset of the x-unit area
+TM_HD void zero2(uint32_t* units, uint32_t byte_off) {
+    *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(units) + byte_off) = 0;
 }
 
 template <int DT> struct Lane;
 
-// ---- Q4_0: 18-byte blocks, interleaved nibbles, w = (n - 8) * d --------------
-template <> struct Lane<1> {
-    static constexpr int STEP_W = 2048, STEP_BYTES = 1152, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 36;
-    using X = X64;
-    static TM_HD void load_x(X& x, const float4* xs4, const float* xsum, int chunk, int lane) { load_x64(x, xs4, xsum, chunk, lane); }
+// =============================================================================
+// 32-weight block formats: a lane owns two consecutive blocks (64 weights) per step;
+// an x unit covers the same two blocks.
+// =============================================================================
 
-    template <int P0, int XB>
-    static TM_HD float block(const uint32_t* lo, const uint32_t* hi, const X& x, float d, float bsum) {
-        float2 a0 = mk2(0.f, 0.f), a1 = mk2(0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-            const int Pa = P0 + j, Pb = P0 + j + 1;
-            // byte Pa holds elements 2j (low nibble) and 2j+1 (high nibble)
-            a0 = fma2(mk2(byte128(lo, Pa), byte128(hi, Pa)), x.v[XB + j], a0);
-            a1 = fma2(mk2(byte128(lo, Pb), byte128(hi, Pb)), x.v[XB + j + 1], a1);
-        }
-        const float S = (a0.x + a0.y) + (a1.x + a1.y);
-        return d * fma1(-136.f, bsum, S);
-    }
-    // 128 + byte P of the word array (P is a compile-time constant after unrolling)
-    static TM_HD float byte128(const uint32_t* w, int P) {
-        switch (P & 3) {
-            case 0: return code128<0>(w[P >> 2]);
-            case 1: return code128<1>(w[P >> 2]);
-            case 2: return code128<2>(w[P >> 2]);
-            default: return code128<3>(w[P >> 2]);
-        }
-    }
-    // p: the lane's 36 bytes (4-byte aligned); nvalid: how many of its blocks exist (1 or 2)
-    static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
-        (void)lane;
-        uint32_t w[9], lo[9], hi[9];
-#pragma unroll
-        for (int i = 0; i < 9; ++i) { w[i] = load4a(p + 4 * i); lo[i] = w[i] & kLo; hi[i] = (w[i] >> 4) & kLo; }
-        float acc = block<2, 0>(lo, hi, x, half_to_float(w[0] & 0xffffu), x.bs[0]);
-        if (nvalid > 1) acc += block<20, 16>(lo, hi, x, half_to_float(w[4] >> 16), x.bs[1]);
-        return acc;
-    }
-};
-
-// ---- Q8_0: 34-byte blocks, w = q * d -----------------------------------------
+// ---- Q8_0: 34-byte blocks [d:2][q:32], w = q * d --------------------------------
+// Lane bytes: 68 = 17 words. Block A's codes sit at unit bytes 2..33, block B's at
+// 36..67 (its scale at 34..35). x unit: plane t words [17t, 17t+17) mirror those byte
+// positions (zeros under the scale bytes); [51] = sA, [52] = sB.
 template <> struct Lane<0> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 2176, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 68;
-    using X = X64;
-    static TM_HD void load_x(X& x, const float4* xs4, const float* xsum, int chunk, int lane) { load_x64(x, xs4, xsum, chunk, lane); }
+    static constexpr int XW = 60;                           // words per x unit; this stride is bank-conflict free for 16-byte loads
+    static constexpr bool NEEDS_SUMS = false;               // no zero point, no min: the plain sums of x are not used
+    struct X { uint32_t w[XW]; };
 
-    static TM_HD float byte32768(const uint32_t* w, int P) {
-        switch (P & 3) {
-            case 0: return code32768<0>(w[P >> 2]);
-            case 1: return code32768<1>(w[P >> 2]);
-            case 2: return code32768<2>(w[P >> 2]);
-            default: return code32768<3>(w[P >> 2]);
-        }
+    // byte offset, inside the x-unit area, of plane t of activation e
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t b = e >> 5, i = e & 31u;
+        return (b >> 1) * (XW * 4u) + 68u * (uint32_t)t + ((b & 1u) ? 36u : 2u) + i;
     }
-    template <int P0, int XB>
-    static TM_HD float block(const uint32_t* u, const X& x, float d) {
-        float2 a0 = mk2(0.f, 0.f), a1 = mk2(0.f, 0.f);
-        const float2 off = mk2(-32896.f, -32896.f);          // 32768 + the 128 of the sign flip
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-            a0 = fma2(add2(mk2(byte32768(u, P0 + i), byte32768(u, P0 + i + 1)), off), x.v[XB + i / 2], a0);
-            a1 = fma2(add2(mk2(byte32768(u, P0 + i + 2), byte32768(u, P0 + i + 3)), off), x.v[XB + i / 2 + 1], a1);
-        }
-        return d * ((a0.x + a0.y) + (a1.x + a1.y));
+    // plane bytes of four consecutive activations e0..e0+3 (e0 % 4 == 0), packed low byte first
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        uint8_t* p = reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t);      // 2 mod 4
+        *reinterpret_cast<uint16_t*>(p) = (uint16_t)packed;
+        *reinterpret_cast<uint16_t*>(p + 2) = (uint16_t)(packed >> 16);
+    }
+    // per-32-block scalars; `lane` = first element held by the caller (it passes the sums of the runs that
+    // start there), `zl` = the caller's index 0..7 among the threads staging this block
+    static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
+        (void)s8; (void)s16; (void)s32;
+        if (lane == 0) units[(b >> 1) * XW + 51 + (b & 1u)] = as_uint(s);
+        // the two bytes of every plane image that lie under this block's fp16 scale must read as zero
+        if (zl < kPlanes) zero2(units, (b >> 1) * (XW * 4u) + 68u * (uint32_t)zl + ((b & 1u) ? 34u : 0u));
     }
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
         (void)lane;
-        uint32_t w[17], u[17];
+        uint32_t w[17];
 #pragma unroll
-        for (int i = 0; i < 17; ++i) { w[i] = load4a(p + 4 * i); u[i] = w[i] ^ 0x80808080u; }
-        float acc = block<2, 0>(u, x, half_to_float(w[0] & 0xffffu));
-        if (nvalid > 1) acc += block<36, 16>(u, x, half_to_float(w[8] >> 16));
+        for (int i = 0; i < 17; ++i) w[i] = load4a(p + 4 * i);
+        int SA[kPlanes], SB[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) {
+            int a = 0, b = 0;
+#pragma unroll
+            for (int i = 0; i < 9; ++i) a = dp4a_ss(w[i], x.w[17 * t + i], a);
+#pragma unroll
+            for (int i = 9; i < 17; ++i) b = dp4a_ss(w[i], x.w[17 * t + i], b);
+            SA[t] = a; SB[t] = b;
+        }
+        float acc = half_to_float(w[0] & 0xffffu) * (as_float(x.w[51]) * planes_to_float(SA));
+        if (nvalid > 1) acc = fma1(half_to_float(w[8] >> 16), as_float(x.w[52]) * planes_to_float(SB), acc);
         return acc;
     }
 };
 
-// ---- Q4_1: 20-byte blocks, split nibbles, w = n * d + m -----------------------
+// ---- Q4_0: 18-byte blocks [d:2][qs:16], byte j = elements 2j (low) | 2j+1 (high), w = (n-8)*d
+// Lane bytes: 36 = 9 words. x unit: per plane t an "even" 9-word image (element 2j under
+// byte j) at [18t, 18t+9) and an "odd" image (element 2j+1) at [18t+9, 18t+18);
+// [54] = sA, [55] = sB, [56] = sum(xA), [57] = sum(xB).
+template <> struct Lane<1> {
+    static constexpr int STEP_W = 2048, STEP_BYTES = 1152, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 36;
+    static constexpr int XW = 60;
+    static constexpr bool NEEDS_SUMS = true;
+    struct X { uint32_t w[XW]; };
+
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t b = e >> 5, i = e & 31u;
+        return (b >> 1) * (XW * 4u) + 4u * (18u * (uint32_t)t + 9u * (i & 1u)) + ((b & 1u) ? 20u : 2u) + (i >> 1);
+    }
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        uint8_t* p = reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t);      // even image, even offset
+        *reinterpret_cast<uint16_t*>(p) = (uint16_t)((packed & 0xffu) | ((packed >> 8) & 0xff00u));          // elements e0, e0+2
+        *reinterpret_cast<uint16_t*>(p + 36) = (uint16_t)(((packed >> 8) & 0xffu) | ((packed >> 16) & 0xff00u));  // e0+1, e0+3
+    }
+    static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
+        (void)s8; (void)s16;
+        if (lane == 0) { units[(b >> 1) * XW + 54 + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + 56 + (b & 1u)] = as_uint(s32); }
+        // zero the bytes under this block's fp16 scale in the even and odd image of every plane
+        if (zl < 2 * kPlanes) zero2(units, (b >> 1) * (XW * 4u) + 36u * (uint32_t)zl + ((b & 1u) ? 18u : 0u));
+    }
+    static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
+        (void)lane;
+        uint32_t lo[9], hi[9], w0 = 0, w4 = 0;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) {
+            const uint32_t w = load4a(p + 4 * i);
+            if (i == 0) w0 = w;
+            if (i == 4) w4 = w;
+            lo[i] = w & kLo;
+            hi[i] = w & kHi;                                 // 16 * high nibble: removed by one shift per block
+        }
+        int SA[kPlanes], SB[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) {
+            int al = 0, ah = 0, bl = 0, bh = 0;
+#pragma unroll
+            for (int i = 0; i < 5; ++i) { al = dp4a_us(lo[i], x.w[18 * t + i], al); ah = dp4a_us(hi[i], x.w[18 * t + 9 + i], ah); }
+#pragma unroll
+            for (int i = 5; i < 9; ++i) { bl = dp4a_us(lo[i], x.w[18 * t + i], bl); bh = dp4a_us(hi[i], x.w[18 * t + 9 + i], bh); }
+            SA[t] = al + (ah >> 4);
+            SB[t] = bl + (bh >> 4);
+        }
+        float acc = half_to_float(w0 & 0xffffu) * fma1(as_float(x.w[54]), planes_to_float(SA), -8.f * as_float(x.w[56]));
+        if (nvalid > 1)
+            acc = fma1(half_to_float(w4 >> 16), fma1(as_float(x.w[55]), planes_to_float(SB), -8.f * as_float(x.w[57])), acc);
+        return acc;
+    }
+};
+
+// ---- Q4_1: 20-byte blocks [d:2][m:2][qs:16], byte j = elements j (low) | j+16 (high), w = n*d + m
+// Lane bytes: 40 = 10 words. x unit: per block b and plane t a "low" 4-word image at
+// [24b + 8t, +4) and a "high" image at [24b + 8t + 4, +4); [48] = sA, [49] = sB,
+// [50] = sum(xA), [51] = sum(xB).
 template <> struct Lane<4> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 1280, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 40;
-    using X = X64;
-    static TM_HD void load_x(X& x, const float4* xs4, const float* xsum, int chunk, int lane) { load_x64(x, xs4, xsum, chunk, lane); }
+    static constexpr int XW = 52;
+    static constexpr bool NEEDS_SUMS = true;
+    struct X { uint32_t w[XW]; };
 
-    template <int XB>
-    static TM_HD float block(const uint32_t* w, const X& x, float bsum) {
-        float2 a0 = mk2(0.f, 0.f), a1 = mk2(0.f, 0.f);
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t b = e >> 5, i = e & 31u;
+        return (b >> 1) * (XW * 4u) + 4u * (24u * (b & 1u) + 8u * (uint32_t)t + 4u * (i >> 4)) + (i & 15u);
+    }
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
+    }
+    static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
+        (void)zl;
+        (void)s8; (void)s16;
+        if (lane == 0) { units[(b >> 1) * XW + 48 + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + 50 + (b & 1u)] = as_uint(s32); }
+    }
+    template <int B>
+    static TM_HD float block(const uint8_t* p, const X& x) {
+        const uint32_t hdr = load4a(p + 20 * B);
+        uint32_t lo[4], hi[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {                       // word k: bytes 4k..4k+3
-            const uint32_t lo = w[1 + k] & kLo, hi = (w[1 + k] >> 4) & kLo;
-            a0 = fma2(mk2(code128<0>(lo), code128<1>(lo)), x.v[XB + 2 * k], a0);
-            a1 = fma2(mk2(code128<2>(lo), code128<3>(lo)), x.v[XB + 2 * k + 1], a1);
-            a0 = fma2(mk2(code128<0>(hi), code128<1>(hi)), x.v[XB + 8 + 2 * k], a0);
-            a1 = fma2(mk2(code128<2>(hi), code128<3>(hi)), x.v[XB + 8 + 2 * k + 1], a1);
+        for (int i = 0; i < 4; ++i) { const uint32_t w = load4a(p + 20 * B + 4 + 4 * i); lo[i] = w & kLo; hi[i] = w & kHi; }
+        int S[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) {
+            int l = 0, h = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { l = dp4a_us(lo[i], x.w[24 * B + 8 * t + i], l); h = dp4a_us(hi[i], x.w[24 * B + 8 * t + 4 + i], h); }
+            S[t] = l + (h >> 4);
         }
-        const float S = (a0.x + a0.y) + (a1.x + a1.y);
-        const float d = half_to_float(w[0] & 0xffffu), m = half_to_float(w[0] >> 16);
-        return fma1(d, fma1(-128.f, bsum, S), m * bsum);
+        const float d = half_to_float(hdr & 0xffffu), m = half_to_float(hdr >> 16);
+        return fma1(d * as_float(x.w[48 + B]), planes_to_float(S), m * as_float(x.w[50 + B]));
     }
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
         (void)lane;
-        uint32_t w[10];
-#pragma unroll
-        for (int i = 0; i < 10; ++i) w[i] = load4a(p + 4 * i);
-        float acc = block<0>(w, x, x.bs[0]);
-        if (nvalid > 1) acc += block<16>(w + 5, x, x.bs[1]);
+        float acc = block<0>(p, x);
+        if (nvalid > 1) acc += block<1>(p, x);
         return acc;
     }
 };
 
-// ---------------------------------------------------------------------------
-// Q5_K: 176-byte super-blocks of 256. Eight lanes share a super-block; lane i
-// takes group g = i/2 (64 weights: sub-blocks 2g and 2g+1) and byte half q = i%2:
-// bytes 16q..16q+15 of the group's qs, i.e. 16 weights of each sub-block.
-// ---------------------------------------------------------------------------
+// =============================================================================
+// Q5_K: 176-byte super-blocks of 256. Eight lanes share a super-block; lane i takes
+// group g = i/2 (64 weights: sub-blocks 2g and 2g+1) and byte half q = i%2: bytes
+// 16q..16q+15 of the group's qs, i.e. a run of 16 weights in each sub-block.
+// x unit: run0 plane t at [4t, 4t+4), run1 plane t at [12+4t, +4); [24] = scale of
+// sub-block 2g, [25] = scale of 2g+1, [26] = sum(x run0), [27] = sum(x run1).
+// =============================================================================
 template <> struct Lane<5> {
     static constexpr int STEP_W = 1024, STEP_BYTES = 704, UNIT_W = 256, LANE_UNITS = 1, LANE_BYTES = 0;
-    struct X {
-        float2 v[16];   // [0..7] run of sub-block 2g, [8..15] run of sub-block 2g+1
-        float s0, s1;   // sums of the two runs
-    };
-    static TM_HD void load_x(X& x, const float4* xs4, const float* xsum, int chunk, int lane) {
-        (void)xsum;
-        const uint32_t S = (uint32_t)chunk * 4u + (uint32_t)(lane >> 3);
-        const uint32_t g = (uint32_t)(lane & 7) >> 1, q = (uint32_t)lane & 1u;
-        const uint32_t q0 = 64u * S + 16u * g + 4u * q;
-        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float4 a = xs4[x_slot(q0 + e)];
-            const float4 b = xs4[x_slot(q0 + 8 + e)];
-            x.v[2 * e] = mk2(a.x, a.y); x.v[2 * e + 1] = mk2(a.z, a.w);
-            x.v[8 + 2 * e] = mk2(b.x, b.y); x.v[8 + 2 * e + 1] = mk2(b.z, b.w);
-            s0 += (a.x + a.y) + (a.z + a.w);
-            s1 += (b.x + b.y) + (b.z + b.w);
+    static constexpr int XW = 28;
+    static constexpr bool NEEDS_SUMS = true;
+    struct X { uint32_t w[XW]; };
+
+    // 32-block b of the row = sub-block (b % 8) of super-block b / 8; unit = 8*S + 2*g + q
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t S = e >> 8, w = e & 255u, g = w >> 6, half = (w >> 5) & 1u, l = w & 31u;
+        const uint32_t u = 8u * S + 2u * g + (l >> 4);
+        return u * (XW * 4u) + 4u * (12u * half + 4u * (uint32_t)t) + (l & 15u);
+    }
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
+    }
+    static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
+        (void)zl;
+        (void)s8; (void)s32;
+        const uint32_t S = b >> 3, j = b & 7u, g = j >> 1, half = j & 1u;
+        if ((lane & 15) == 0) {                              // lanes 0 and 16 hold the sums of the two 16-runs
+            const uint32_t u = 8u * S + 2u * g + (uint32_t)(lane >> 4);
+            units[u * XW + 24 + half] = as_uint(s);
+            units[u * XW + 26 + half] = as_uint(s16);
         }
-        x.s0 = s0; x.s1 = s1;
     }
     // p: start of the warp's row chunk (16-byte aligned); nvalid: super-blocks present in it
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
@@ -325,59 +407,67 @@ template <> struct Lane<5> {
         }
         const uint32_t wq[4] = {qs.x, qs.y, qs.z, qs.w};
         const uint32_t wh[4] = {qh.x, qh.y, qh.z, qh.w};
-        float2 a0 = mk2(0.f, 0.f), a1 = mk2(0.f, 0.f);
+        uint32_t c0[4], c1[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const uint32_t t = wh[e] >> (2u * g);
-            const uint32_t c0 = (wq[e] & kLo) | ((t << 4) & 0x10101010u);
-            const uint32_t c1 = ((wq[e] >> 4) & kLo) | ((t << 3) & 0x10101010u);
-            a0 = fma2(mk2(code128<0>(c0), code128<1>(c0)), x.v[2 * e], a0);
-            a0 = fma2(mk2(code128<2>(c0), code128<3>(c0)), x.v[2 * e + 1], a0);
-            a1 = fma2(mk2(code128<0>(c1), code128<1>(c1)), x.v[8 + 2 * e], a1);
-            a1 = fma2(mk2(code128<2>(c1), code128<3>(c1)), x.v[8 + 2 * e + 1], a1);
+            c0[e] = (wq[e] & kLo) | ((t << 4) & 0x10101010u);
+            c1[e] = ((wq[e] >> 4) & kLo) | ((t << 3) & 0x10101010u);
         }
-        const float S0 = fma1(-128.f, x.s0, a0.x + a0.y);
-        const float S1 = fma1(-128.f, x.s1, a1.x + a1.y);
+        int S0[kPlanes], S1[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) {
+            int a = 0, b = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a = dp4a_us(c0[e], x.w[4 * t + e], a); b = dp4a_us(c1[e], x.w[12 + 4 * t + e], b); }
+            S0[t] = a; S1[t] = b;
+        }
         const float d = half_to_float(hdr.x & 0xffffu), dmin = half_to_float(hdr.x >> 16);
-        const float pos = fma1(sc[0], S0, sc[1] * S1);
-        const float neg = fma1(mn[0], x.s0, mn[1] * x.s1);
+        const float pos = fma1(sc[0] * as_float(x.w[24]), planes_to_float(S0), sc[1] * as_float(x.w[25]) * planes_to_float(S1));
+        const float neg = fma1(mn[0], as_float(x.w[26]), mn[1] * as_float(x.w[27]));
         return fma1(d, pos, -(dmin * neg));
     }
 };
 
-// ---------------------------------------------------------------------------
+// =============================================================================
 // Q6_K: 210-byte super-blocks of 256, only 2-byte aligned. Four lanes share a
-// super-block; lane i takes l in [8i, 8i+8) of both 128-halves: for each half
-// 8 bytes of ql[l], 8 of ql[l+32], 8 of qh[l] -> 4 runs of 8 weights (elements
-// l + 32j), each run inside one 16-weight sub-block with its own int8 scale.
-// ---------------------------------------------------------------------------
+// super-block; lane i takes l in [8i, 8i+8) of both 128-halves: for each half 8 bytes
+// of ql[l], 8 of ql[l+32], 8 of qh[l] -> 4 runs of 8 weights (elements l + 32j), each
+// run inside one 16-weight sub-block with its own int8 scale.
+// x unit: run r = 4h + j: plane t words at [6r + 2t, +2); [48 + r] = scale of the
+// 32-block holding the run, [56 + r] = sum(x) over the run.
+// =============================================================================
 template <> struct Lane<6> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 1680, UNIT_W = 256, LANE_UNITS = 1, LANE_BYTES = 0;
-    struct X {
-        float2 v[32];   // run (h, j) at v[4*(4h+j) .. +3]
-        float s8[8];    // sum of each run
-    };
-    static TM_HD void load_x(X& x, const float4* xs4, const float* xsum, int chunk, int lane) {
-        (void)xsum;
-        const uint32_t S = (uint32_t)chunk * 8u + (uint32_t)(lane >> 2);
-        const uint32_t i = (uint32_t)lane & 3u;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {                       // r = 4h + j
-            const uint32_t q0 = 64u * S + 8u * (uint32_t)r + 2u * i;
-            const float4 a = xs4[x_slot(q0)];
-            const float4 b = xs4[x_slot(q0 + 1)];
-            x.v[4 * r] = mk2(a.x, a.y); x.v[4 * r + 1] = mk2(a.z, a.w);
-            x.v[4 * r + 2] = mk2(b.x, b.y); x.v[4 * r + 3] = mk2(b.z, b.w);
-            x.s8[r] = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+    static constexpr int XW = 68;
+    static constexpr bool NEEDS_SUMS = true;
+    struct X { uint32_t w[XW]; };
+
+    // 32-block b of the row = run r = b % 8 of super-block b / 8; unit = 4*S + (l / 8)
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t S = e >> 8, w = e & 255u, r = w >> 5, l = w & 31u;
+        const uint32_t u = 4u * S + (l >> 3);
+        return u * (XW * 4u) + 4u * (6u * r + 2u * (uint32_t)t) + (l & 7u);
+    }
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
+    }
+    static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
+        (void)zl;
+        (void)s16; (void)s32;
+        const uint32_t S = b >> 3, r = b & 7u;
+        if ((lane & 7) == 0) {                               // lanes 0, 8, 16, 24 hold the sums of the four 8-runs
+            const uint32_t u = 4u * S + (uint32_t)(lane >> 3);
+            units[u * XW + 48 + r] = as_uint(s);
+            units[u * XW + 56 + r] = as_uint(s8);
         }
     }
-    static TM_HD float run(uint32_t c0, uint32_t c1, const X& x, int r) {
-        float2 a = mk2(0.f, 0.f);
-        a = fma2(mk2(code128<0>(c0), code128<1>(c0)), x.v[4 * r], a);
-        a = fma2(mk2(code128<2>(c0), code128<3>(c0)), x.v[4 * r + 1], a);
-        a = fma2(mk2(code128<0>(c1), code128<1>(c1)), x.v[4 * r + 2], a);
-        a = fma2(mk2(code128<2>(c1), code128<3>(c1)), x.v[4 * r + 3], a);
-        return fma1(-160.f, x.s8[r], a.x + a.y);            // 128 offset + zero point 32
+    static TM_HD float run_dot(uint32_t c0, uint32_t c1, const X& x, int r, float sc) {
+        int S[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) S[t] = dp4a_us(c1, x.w[6 * r + 2 * t + 1], dp4a_us(c0, x.w[6 * r + 2 * t], 0));
+        // codes carry a zero point of 32: sum (c - 32) x = s * S - 32 * sum(x)
+        return sc * fma1(as_float(x.w[48 + r]), planes_to_float(S), -32.f * as_float(x.w[56 + r]));
     }
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
         const int sb = lane >> 2;
@@ -395,14 +485,26 @@ template <> struct Lane<6> {
             const uint32_t c10 = (L1.x & kLo) | ((Hh.x << 2) & 0x30303030u), c11 = (L1.y & kLo) | ((Hh.y << 2) & 0x30303030u);
             const uint32_t c20 = ((L0.x >> 4) & kLo) | (Hh.x & 0x30303030u), c21 = ((L0.y >> 4) & kLo) | (Hh.y & 0x30303030u);
             const uint32_t c30 = ((L1.x >> 4) & kLo) | ((Hh.x >> 2) & 0x30303030u), c31 = ((L1.y >> 4) & kLo) | ((Hh.y >> 2) & 0x30303030u);
-            acc = fma1((float)sc[0], run(c00, c01, x, 4 * h + 0), acc);
-            acc = fma1((float)sc[2], run(c10, c11, x, 4 * h + 1), acc);
-            acc = fma1((float)sc[4], run(c20, c21, x, 4 * h + 2), acc);
-            acc = fma1((float)sc[6], run(c30, c31, x, 4 * h + 3), acc);
+            acc += run_dot(c00, c01, x, 4 * h + 0, (float)sc[0]);
+            acc += run_dot(c10, c11, x, 4 * h + 1, (float)sc[2]);
+            acc += run_dot(c20, c21, x, 4 * h + 2, (float)sc[4]);
+            acc += run_dot(c30, c31, x, 4 * h + 3, (float)sc[6]);
         }
         const uint32_t dh = (uint32_t)B[208] | ((uint32_t)B[209] << 8);
         return half_to_float(dh) * acc;
     }
 };
+
+// Copy the lane's x unit from shared memory into registers (16-byte loads).
+template <int DT>
+TM_HD void load_x_unit(typename Lane<DT>::X& x, const uint32_t* units, uint32_t u) {
+    constexpr int XW = Lane<DT>::XW;
+    const uint32_t* src = units + (size_t)u * XW;
+#pragma unroll
+    for (int i = 0; i < XW / 4; ++i) {
+        const uint4 v = load16a(src + 4 * i);
+        x.w[4 * i] = v.x; x.w[4 * i + 1] = v.y; x.w[4 * i + 2] = v.z; x.w[4 * i + 3] = v.w;
+    }
+}
 
 }  // namespace tmc

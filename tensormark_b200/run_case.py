@@ -1,0 +1,100 @@
+"""Run one kernel of the path on a chosen shape, a few times, and print its timing.
+
+    python -m tensormark_b200.run_case --op gemv --dtype Q8_0 --n 32000 --k 2048 --reps 5 --copies 3
+    python -m tensormark_b200.run_case --op gemm --dtype Q4_0 --m 2000 --n 5632 --k 2048 --reps 3
+    python -m tensormark_b200.run_case --op dequant --dtype Q6_K --n 4096 --k 4096
+
+A small, self-contained driver for profilers and for tuning: it creates seeded synthetic
+inputs on the device, launches the kernel through the C ABI on one stream and reports the
+CUDA-event time per launch together with the algorithmic GB/s or TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+
+import numpy as np
+
+from . import lib, synth
+
+NAMES = {v: k for k, v in synth.DTYPE_NAMES.items()}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=["gemv", "gemm", "dequant"], default="gemv")
+    ap.add_argument("--dtype", default="Q8_0", choices=sorted(NAMES))
+    ap.add_argument("--m", type=int, default=2000)
+    ap.add_argument("--n", type=int, default=32000)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--copies", type=int, default=1, help="distinct weight copies to rotate over")
+    ap.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph (no host launch cost)")
+    args = ap.parse_args()
+
+    import torch
+    torch.cuda.set_device(0)
+    L = lib.load()
+    lib.check(L.tm_cuda_init(0), "tm_cuda_init")
+    dt = NAMES[args.dtype]
+    n, k, m = args.n, args.k, args.m
+    W = synth.make_weights(dt, n, k, seed=1).reshape(-1)
+    Ws = []
+    for _ in range(args.copies):
+        t = torch.zeros(W.size + 32, dtype=torch.uint8, device="cuda")
+        t[: W.size] = torch.from_numpy(W).cuda()
+        Ws.append(t)
+    stream = torch.cuda.Stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    vp = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+
+    if args.op == "gemv":
+        x = torch.from_numpy(synth.make_activations(k, 1)).cuda()
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        run = lambda i: lib.check(L.tm_cuda_gemv_q_dev(vp(x), vp(Ws[i % len(Ws)]), vp(y), n, k, dt, sp), "gemv")  # noqa: E731
+        work, unit = synth.gemv_bytes(dt, n, k) / 1e9, "GB/s"
+    elif args.op == "dequant":
+        out = torch.zeros(n * k, dtype=torch.float32, device="cuda")
+        run = lambda i: lib.check(L.tm_cuda_dequant_dev(vp(Ws[i % len(Ws)]), vp(out), n, k, dt, sp), "dequant")  # noqa: E731
+        work, unit = (synth.weight_bytes(dt, n, k) + 4.0 * n * k) / 1e9, "GB/s"
+    else:
+        A = torch.from_numpy(synth.make_activations((m, k), 4)).cuda()
+        Cm = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        need = L.tm_cuda_sgemm_q_workspace(m, n, k, dt)
+        ws = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+        base = C.c_void_p((ws.data_ptr() + 255) // 256 * 256)
+        run = lambda i: lib.check(L.tm_cuda_sgemm_q_dev(vp(A), vp(Ws[i % len(Ws)]), vp(Cm), m, n, k, dt, base, need, sp), "gemm")  # noqa: E731
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            run(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if args.graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(args.reps):
+                    run(i)
+            g.replay()
+            stream.synchronize()
+            e0.record(stream)
+            g.replay()
+            e1.record(stream)
+        else:
+            e0.record(stream)
+            for i in range(args.reps):
+                run(i)
+            e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.reps
+    lib.check(L.tm_cuda_tok_flush(), "device status")
+    print(json.dumps({"op": args.op, "dtype": args.dtype, "m": m if args.op == "gemm" else None, "n": n, "k": k,
+                      "us_per_launch": round(us, 3), "rate": round(work / (us * 1e-6), 2), "unit": unit,
+                      "launches": int(L.tm_cuda_launch_count())}))
+
+
+if __name__ == "__main__":
+    main()

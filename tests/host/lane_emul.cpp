@@ -4,8 +4,9 @@
 // bytes and which activations a lane touches is pure index arithmetic that can be
 // wrong without any GPU being involved. This harness replays that arithmetic lane
 // by lane with the host versions of the same inline functions: it stages x exactly
-// as the kernel does (swizzled float4 slots, per-32-block sums), walks the steps of
-// each row, and adds the 32 lane partials in the kernel's butterfly order. The test
+// as the kernel does (block floating point planes scattered into the lanes' x
+// units), walks the steps of each row, and adds the 32 lane partials in the kernel's
+// butterfly order. The test
 // suite compares the result with the CPU checker, so a wrong lane map is caught
 // before the kernel is ever launched.
 #include "../../tensormark_b200/csrc/gemv_lanes.cuh"
@@ -19,18 +20,25 @@ using namespace tmc;
 template <int DT>
 static void emul(const uint8_t* W, const float* x, float* y, unsigned N, unsigned K, unsigned row_bytes) {
     using L = Lane<DT>;
-    const unsigned nchunks = (K + L::STEP_W - 1) / L::STEP_W, kpad = nchunks * L::STEP_W;
-    std::vector<float4> xs4(kpad / 4);
-    std::vector<float> xsum(kpad / 32, 0.f);
-    for (unsigned q = 0; q < kpad / 4; ++q) {
-        float4 v = {0.f, 0.f, 0.f, 0.f};
-        if (q * 4 < K) { v.x = x[4 * q]; v.y = x[4 * q + 1]; v.z = x[4 * q + 2]; v.w = x[4 * q + 3]; }
-        xs4[x_slot(q)] = v;
-    }
+    const unsigned nchunks = (K + L::STEP_W - 1) / L::STEP_W, nunits = nchunks * 32;
+    // x units exactly as the kernel stages them: zero fill, then per 32-block the scale, the
+    // run sums and every activation's plane bytes
+    std::vector<uint32_t> units((size_t)nunits * L::XW, 0u);
     for (unsigned b = 0; b < K / 32; ++b) {
-        float s = 0.f;
-        for (int i = 0; i < 8; ++i) { const float* v = x + b * 32 + 4 * i; s += (v[0] + v[1]) + (v[2] + v[3]); }
-        xsum[b] = s;
+        float v[32], amax = 0.f;
+        bool bad = false;
+        for (int i = 0; i < 32; ++i) { v[i] = x[b * 32 + i]; const float a = fabsf(v[i]); bad = bad || !(a <= 3.0e38f); amax = a > amax ? a : amax; }
+        float inv;
+        const float sc = block_scale(amax, bad, inv);
+        float s8[4], s16[2], s32;
+        for (int g = 0; g < 4; ++g) { float t = 0.f; for (int i = 0; i < 8; ++i) t += v[8 * g + i]; s8[g] = t; }
+        s16[0] = s8[0] + s8[1]; s16[1] = s8[2] + s8[3]; s32 = s16[0] + s16[1];
+        for (int lane = 0; lane < 32; ++lane) {
+            int8_t q[kPlanes];
+            quantize_elem(v[lane], inv, q);
+            for (int t = 0; t < kPlanes; ++t) reinterpret_cast<int8_t*>(units.data())[L::plane_byte(b * 32 + lane, t)] = q[t];
+            L::scalars(units.data(), b, lane, (lane & 3) ? 99 : lane / 4, sc, s8[lane / 8], s16[lane / 16], s32);
+        }
     }
     // a stage as the kernel sees it: 16-byte aligned, garbage beyond the valid bytes
     std::vector<uint8_t> stage_raw(L::STEP_BYTES + 64, 0xA5);
@@ -42,12 +50,12 @@ static void emul(const uint8_t* W, const float* x, float* y, unsigned N, unsigne
             std::fill(stage, stage + L::STEP_BYTES, 0xA5);
             memcpy(stage, W + (size_t)row * row_bytes + off, bytes);
             const unsigned wchunk = std::min<unsigned>(L::STEP_W, K - c * L::STEP_W);
-            const int units = (int)(wchunk / L::UNIT_W);
+            const int nu = (int)(wchunk / L::UNIT_W);
             for (int lane = 0; lane < 32; ++lane) {
                 typename L::X xr;
-                L::load_x(xr, xs4.data(), xsum.data(), (int)c, lane);
-                int valid = units;
-                if (L::LANE_UNITS == 2) { valid = std::max(0, std::min(2, units - 2 * lane)); if (!valid) continue; }
+                load_x_unit<DT>(xr, units.data(), c * 32 + lane);
+                int valid = nu;
+                if (L::LANE_UNITS == 2) { valid = std::max(0, std::min(2, nu - 2 * lane)); if (!valid) continue; }
                 lane_acc[lane] += L::dot(stage + (L::LANE_UNITS == 2 ? lane * L::LANE_BYTES : 0), xr, lane, valid);
             }
         }

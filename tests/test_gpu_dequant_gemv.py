@@ -17,6 +17,14 @@ DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K]
 TOL = 1e-3      # relative to sum_k |w_k x_k| per output, the bar the path is judged by
 
 
+def same_bits(got: np.ndarray, want: np.ndarray) -> bool:
+    """Bit-for-bit equality; a NaN must be a NaN on both sides (its payload is the multiplier hardware's
+    choice: x86 propagates the operand's payload, the GPU returns the canonical quiet NaN)."""
+    g, w = got.view(np.uint32), want.view(np.uint32)
+    gn, wn = (g & 0x7fffffff) > 0x7f800000, (w & 0x7fffffff) > 0x7f800000
+    return bool(np.array_equal(gn, wn) and np.array_equal(g[~gn], w[~wn]))
+
+
 def _dequant_dev(cuda, torch, dt, blocks, n, k):
     W = dev_bytes(torch, blocks)
     out = torch.empty(n * k, dtype=torch.float32, device="cuda")
@@ -32,7 +40,9 @@ def test_dequant_bit_exact_vs_golden(cuda, torch_mod, golden, dt):
     be = synth.BLOCK_ELEMS[dt]
     # present the blocks as rows of one block each so special-scale blocks are covered too
     got = _dequant_dev(cuda, torch_mod, dt, blocks, blocks.shape[0], be)
-    assert np.array_equal(got.view(np.uint32), golden[f"{name}_dequant_bits"])
+    want = golden[f"{name}_dequant_bits"]
+    assert same_bits(got, want)
+    assert ((want & 0x7fffffff) > 0x7f800000).sum() > 0          # the fixture really holds NaN scales
 
 
 @pytest.mark.parametrize("dt", DTYPES)

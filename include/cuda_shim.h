@@ -105,6 +105,14 @@ bool tm_cuda_rmsnorm_dev(const float* x, const float* w, float* out, unsigned D,
 bool tm_cuda_add_dev(float* a, const float* b, unsigned n, void* stream);
 bool tm_cuda_silu_mul_dev(float* g, const float* u, unsigned n, void* stream);
 bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream);
+/* GQA split-K decode attention for one token (metal.h:2739-2859, host side 4153-4222): q is
+ * [H][dh] fp32, kc/vc are [KVH][ctx][dh] caches (half when kv_half != 0, else fp32), positions
+ * [0, allow) are attended, out is [H][dh]. `scratch` receives the per-split partial outputs and
+ * softmax statistics; it must hold at least tm_cuda_attn_decode_scratch(...) bytes. */
+size_t tm_cuda_attn_decode_scratch(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow);
+bool tm_cuda_attn_decode_dev(const float* q, const void* kc, const void* vc, float* scratch, size_t scratch_bytes,
+                             float* out, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow,
+                             float scale, int kv_half, void* stream);
 
 /* ---- token lane (metal_shim.mm:22-152) ----------------------------------- */
 /* Slots are backend-owned grow-only device buffers addressed by small integers

@@ -478,6 +478,24 @@ bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream)
     return launch_choose(x, out, n, 0, 0.f, 0u, false, sc, (cudaStream_t)stream);
 }
 
+size_t tm_cuda_attn_decode_scratch(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow) {
+    if (!ensure_init(-1) || !H || !KVH || !dh || !allow) return 0;
+    const AttnPlan pl = plan_attention(H, KVH, dh, ctx, allow, (size_t)1 << 40);
+    return (size_t)pl.nsplit * H * (dh + 2) * sizeof(float);
+}
+bool tm_cuda_attn_decode_dev(const float* q, const void* kc, const void* vc, float* scratch, size_t scratch_bytes,
+                             float* out, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow,
+                             float scale, int kv_half, void* stream) {
+    if (!ensure_init(-1)) return false;
+    if (!q || !kc || !vc || !scratch || !out) return fail("attn_decode: null pointer");
+    if (!H || !KVH || !dh || !ctx || !allow || allow > ctx || H % KVH || !std::isfinite(scale) || scale <= 0)
+        return fail("attn_decode: invalid decode attention dimensions or scale");
+    const AttnPlan pl = plan_attention(H, KVH, dh, ctx, allow, scratch_bytes);
+    if (!pl.nsplit) return fail("attn_decode: scratch of %zu bytes cannot hold one split", scratch_bytes);
+    return launch_attention(q, kc, vc, kv_half != 0, scratch, out, H, KVH, dh, ctx, allow, scale, H / KVH, pl,
+                            (cudaStream_t)stream);
+}
+
 // ---- the reference's symbol names (tensormark/metal_shim.mm:22-152) -------------------
 bool tm_metal_tok_begin(void) { return tm_cuda_tok_begin(); }
 bool tm_metal_tok_flush(void) { return tm_cuda_tok_flush(); }

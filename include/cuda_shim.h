@@ -113,6 +113,20 @@ size_t tm_cuda_attn_decode_scratch(unsigned H, unsigned KVH, unsigned dh, unsign
 bool tm_cuda_attn_decode_dev(const float* q, const void* kc, const void* vc, float* scratch, size_t scratch_bytes,
                              float* out, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow,
                              float scale, int kv_half, void* stream);
+/* The same attention for callers that cannot allocate device memory. It has no counterpart in
+ * the reference; it exists for hosts that have given all free device memory to their own pool
+ * (so a cudaMalloc for scratch would fail) or that cannot afford cudaMalloc's device-wide
+ * synchronisation on their token path. The split-K scratch is a static array inside the library,
+ * TM_CUDA_ATTN_STATIC_SCRATCH_BYTES per GPU, held from library load to process exit; the call
+ * performs no cudaMalloc/cudaFree and uses no allocating routine. Shapes whose scratch would not
+ * fit are refused (false, tm_cuda_last_error() says how many bytes were needed). The first call on
+ * a device looks up the array's device address: make that call before any stream capture starts.
+ * Every call shares the one array, so calls that may overlap on the GPU (different streams,
+ * different threads) race with each other; within one stream, back-to-back calls are safe. */
+#define TM_CUDA_ATTN_STATIC_SCRATCH_BYTES (512u * 1024u)
+bool tm_cuda_attn_decode_static_dev(const float* q, const void* kc, const void* vc, float* out, unsigned H,
+                                    unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, float scale,
+                                    int kv_half, void* stream);
 
 /* ---- token lane (metal_shim.mm:22-152) ----------------------------------- */
 /* Slots are backend-owned grow-only device buffers addressed by small integers

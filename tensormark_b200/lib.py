@@ -41,6 +41,7 @@ SIGNATURES = {
     "tm_cuda_argmax_dev": (C.c_bool, [_vp, _vp, _u, _vp]),
     "tm_cuda_attn_decode_scratch": (_sz, [_u, _u, _u, _u, _u]),
     "tm_cuda_attn_decode_dev": (C.c_bool, [_vp, _vp, _vp, _vp, _sz, _vp, _u, _u, _u, _u, _u, C.c_float, C.c_int, _vp]),
+    "tm_cuda_attn_decode_static_dev": (C.c_bool, [_vp, _vp, _vp, _vp, _u, _u, _u, _u, _u, C.c_float, C.c_int, _vp]),
     "tm_cuda_tok_begin": (C.c_bool, []),
     "tm_cuda_tok_flush": (C.c_bool, []),
     "tm_cuda_tok_end": (C.c_bool, [C.c_int, _vp, _u]),

@@ -180,6 +180,35 @@ void tm_cuda_tok_attn(int qslot, int kcslot, int vcslot, int probslot, int outsl
 void tm_cuda_tok_argmax(int xslot, int tokslot, unsigned idx, unsigned n);           /* metal.h:3191-3200 */
 void tm_cuda_tok_sample(int xslot, int tokslot, unsigned idx, unsigned n, float inv_temp, unsigned seed);  /* metal.h:3201-3212 */
 unsigned tm_cuda_tok_peek(int tokslot, unsigned idx);                                /* metal.h:3216-3226 */
+/* ---- chain forms (no counterpart in the reference's shim; they serve its greedy chain,
+ * llama.h:6047-6165, without one host round trip per token) --------------------------------
+ * A "chain state" is two ints in a slot: {position, token index}. The entries below read it on
+ * the device, so ONE captured graph of a token's launches is replayed for every token:
+ * embed(tok[index]) -> layers at `position` -> argmax -> tok[index+1] -> advance. */
+/* GEMV with optional fusions: x_op 0 = plain, 1 = RMSNorm(x; norm_w, eps) applied while x is
+ * staged, 2 = silu(x) * x2 (x2 at x2slot/x2off); accumulate != 0 adds the result to y (residual).
+ * Segments as tok_gemv_seg_dt. */
+void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                            int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate);
+/* rope(q) in place + rope(k) -> K cache + v -> V cache for the packed q|k|v slot, one launch. */
+void tm_cuda_tok_qkv_post_at(int qkvslot, int kcslot, int vcslot, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
+                             float theta, int stateslot);
+void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int outslot, unsigned QD, unsigned H,
+                         unsigned KVH, unsigned dh, unsigned ctx, float scale, unsigned REP, int stateslot);
+/* tok[index + 1] = argmax(x[0..n)); the token slot holds max_tokens entries. */
+void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot);
+/* x = row tok[index] of the embedding table. */
+void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
+                          int stateslot);
+void tm_cuda_tok_advance(int stateslot);                         /* position += 1, index += 1 */
+/* Capture the launches encoded between begin and end into a CUDA graph (returns its id, -1 on
+ * failure) and replay it. Slots, weight handles and norm weights must exist before the capture. */
+bool tm_cuda_tok_graph_begin(void);
+int tm_cuda_tok_graph_end(void);
+bool tm_cuda_tok_graph_launch(int id, unsigned times);
+void tm_cuda_tok_graph_destroy(int id);
+
 /* Device address of a slot (NULL when unreserved); for resident callers and tests. */
 void* tm_cuda_tok_slot_ptr(int slot);
 /* The lane's stream as a cudaStream_t. */

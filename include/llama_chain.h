@@ -1,0 +1,300 @@
+// include/llama_chain.h — host driver of the GPU decode chain over the token lane.
+//
+// The decode-lane slice of the reference's model runtime, kept to what the quantized matmul
+// path needs (tensormark/llama.h): the slot table (1245-1250), weight registration
+// (ensure_gpu_weights 1594-1641), gpu_token_prologue (5716-5770), encode_gpu_token (5774-5930,
+// same op order, same fused q|k|v and gate|up segments), forward_gpu_one (5931-5980) and the
+// greedy chain API gpu_chain_begin / poll / end / generate_greedy_gpu (6047-6173). Method names,
+// argument meaning and error behaviour follow the reference: failures throw std::runtime_error /
+// std::invalid_argument, chains need n >= 1 and must fit the context, tokens never leave the GPU
+// between the steps of a chain.
+//
+// Two lanes produce the same tokens:
+//   * reference lane: one entry per op through tm_cuda_tok_* exactly as the reference encodes
+//     them through tm_metal_tok_* (position passed by value, one host call per op);
+//   * graph lane (default for chains): the per-token sequence is encoded ONCE with the chain forms
+//     of include/cuda_shim.h (position and token index live in a device "chain state"), captured
+//     in a CUDA graph, and replayed per token. RMSNorm and SiLU*up ride in the staging of the
+//     following GEMV, the residual adds in the epilogue of the o / down GEMVs, and rope(q),
+//     rope(k)->cache and v->cache are one launch: 7 launches per layer instead of 14.
+//
+// Scope: dense Llama-style layers, block-quantized projections (Q8_0/Q4_0/Q4_1/Q5_K/Q6_K),
+// GQA attention, greedy choice. Tokenizers, sampling front ends, hybrid/GDN layers, speculative
+// decoding and KV paging are outside this path.
+#pragma once
+
+#include "cuda_shim.h"
+
+#include <cmath>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace tmllama {
+
+struct CudaLlamaLayer {
+    const void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    const float *rms1 = nullptr, *rms2 = nullptr;              // D floats each (host)
+};
+
+struct CudaLlamaDesc {
+    int L = 0, D = 0, H = 0, KVH = 0, dh = 0, F = 0, V = 0, ctx = 0;
+    float theta = 10000.f, eps = 1e-5f;
+    unsigned dt_proj = TM_DT_Q4_0, dt_head = TM_DT_Q6_K, dt_embed = TM_DT_Q4_0;
+    const void* embed = nullptr;                               // V x D blocks
+    const void* head = nullptr;                                // V x D blocks
+    const float* rmsf = nullptr;                               // final norm weights
+    const CudaLlamaLayer* layers = nullptr;
+    // When every tensor lies inside one host mapping (an mmap'd .tmq), name it here: the mapping is
+    // made resident once and all tensors share one weight handle, which is what lets q|k|v and
+    // gate|up run as one segmented GEMV each (tensormark/llama.h:5852-5881). Null: one copy per tensor.
+    const void* map_base = nullptr;
+    size_t map_size = 0;
+};
+
+class CudaLlama {
+public:
+    enum {
+        SLOT_X = 0, SLOT_H = 1, SLOT_QKV = 2, SLOT_AO = 3, SLOT_H2 = 4, SLOT_H2S = 5, SLOT_GU = 6, SLOT_DN = 7,
+        SLOT_XF = 8, SLOT_LOGITS = 9, SLOT_PROBS = 10, SLOT_TOK = 11, SLOT_BIAS = 12, SLOT_STATE = 13,
+        SLOT_KC = 100, SLOT_VC = 200
+    };
+
+    explicit CudaLlama(const CudaLlamaDesc& d) : d_(d), layers_(d.layers, d.layers + d.L) {
+        if (d.L <= 0 || d.D <= 0 || d.H <= 0 || d.KVH <= 0 || d.dh <= 0 || d.F <= 0 || d.V <= 0 || d.ctx <= 0 ||
+            d.H % d.KVH || (d.dh & 1) || !d.embed || !d.head || !d.rmsf || !d.layers)
+            throw std::invalid_argument("llama: invalid model description");
+        if (d.L >= 100) throw std::invalid_argument("llama: the slot table holds at most 99 layers");
+        if (!tm_cuda_init(-1)) throw std::runtime_error(std::string("cuda: ") + tm_cuda_last_error());
+        logits_.resize((size_t)d.V);
+    }
+    ~CudaLlama() {
+        if (graph_ >= 0) tm_cuda_tok_graph_destroy(graph_);
+    }
+    CudaLlama(const CudaLlama&) = delete;
+    CudaLlama& operator=(const CudaLlama&) = delete;
+
+    int seen = 0;                                              // tokens in the cache = next position
+    const std::vector<float>& logits() const { return logits_; }
+    void set_graph_lane(bool on) { use_graph_ = on; }
+
+    // Register every projection once (tensormark/llama.h:1594-1641) and size the packed slots and
+    // the K/V caches (5716-5748). Idempotent.
+    void gpu_token_prologue() {
+        if (ready_) return;
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh;
+        auto reg = [&](const void* p, unsigned dt, int rows, int cols) {
+            Handle h{};
+            const size_t bytes = tm_cuda_weight_bytes(dt, (size_t)rows, (size_t)cols);
+            if (!bytes) throw std::invalid_argument("llama: tensor shape is not whole blocks");
+            h.id = tm_cuda_tok_wbuf(p, bytes, d_.map_base, d_.map_size, d_.map_base ? 1 : 0, &h.woff);
+            if (h.id < 0) throw std::runtime_error(std::string("cuda: weight registration failed: ") + tm_cuda_last_error());
+            return h;
+        };
+        w_.resize((size_t)d_.L);
+        for (int l = 0; l < d_.L; ++l) {
+            const CudaLlamaLayer& s = layers_[(size_t)l];
+            Registered& r = w_[(size_t)l];
+            r.q = reg(s.q, d_.dt_proj, QD, d_.D); r.k = reg(s.k, d_.dt_proj, KVD, d_.D); r.v = reg(s.v, d_.dt_proj, KVD, d_.D);
+            r.o = reg(s.o, d_.dt_proj, d_.D, QD);
+            r.gate = reg(s.gate, d_.dt_proj, d_.F, d_.D); r.up = reg(s.up, d_.dt_proj, d_.F, d_.D);
+            r.down = reg(s.down, d_.dt_proj, d_.D, d_.F);
+        }
+        embed_ = reg(d_.embed, d_.dt_embed, d_.V, d_.D);
+        head_ = reg(d_.head, d_.dt_head, d_.V, d_.D);
+        const size_t D4 = (size_t)d_.D * 4;
+        bool ok = tm_cuda_tok_reserve(SLOT_X, D4) && tm_cuda_tok_reserve(SLOT_H, D4) && tm_cuda_tok_reserve(SLOT_H2, D4) &&
+                  tm_cuda_tok_reserve(SLOT_H2S, D4) && tm_cuda_tok_reserve(SLOT_DN, D4) && tm_cuda_tok_reserve(SLOT_XF, D4) &&
+                  tm_cuda_tok_reserve(SLOT_QKV, (size_t)(QD + 2 * KVD) * 4) && tm_cuda_tok_reserve(SLOT_AO, (size_t)QD * 4) &&
+                  tm_cuda_tok_reserve(SLOT_GU, (size_t)2 * d_.F * 4) && tm_cuda_tok_reserve(SLOT_LOGITS, (size_t)d_.V * 4) &&
+                  tm_cuda_tok_reserve(SLOT_PROBS, (size_t)d_.H * d_.ctx * 4) && tm_cuda_tok_reserve(SLOT_STATE, 64);
+        if (!ok) throw std::runtime_error("cuda: packed slot reservation failed");
+        const size_t kv = (size_t)d_.KVH * d_.ctx * d_.dh;
+        for (int l = 0; l < d_.L; ++l)
+            if (!tm_cuda_tok_kv_reserve(SLOT_KC + l, kv) || !tm_cuda_tok_kv_reserve(SLOT_VC + l, kv))
+                throw std::runtime_error("cuda: KV cache slot reservation failed");
+        ready_ = true;
+    }
+
+    // One token's kernels from the first layer norm through lm_head, reference op order
+    // (tensormark/llama.h:5818-5924): x in SLOT_X, logits land in SLOT_LOGITS.
+    void encode_gpu_token(int pos) {
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh, REP = d_.H / d_.KVH;
+        const float scale = 1.f / std::sqrt((float)d_.dh);
+        const unsigned dt = d_.dt_proj;
+        for (int l = 0; l < d_.L; ++l) {
+            const Registered& r = w_[(size_t)l];
+            const CudaLlamaLayer& s = layers_[(size_t)l];
+            tm_cuda_tok_rmsnorm(SLOT_X, s.rms1, SLOT_H, (unsigned)d_.D, d_.eps);
+            if (same_buffer(r.q, r.k, r.v)) {
+                const uint64_t woff[3] = {r.q.woff, r.k.woff, r.v.woff};
+                const unsigned rows[3] = {(unsigned)QD, (unsigned)KVD, (unsigned)KVD};
+                tm_cuda_tok_gemv_seg_dt(SLOT_H, r.q.id, SLOT_QKV, 0, (unsigned)(QD + 2 * KVD), (unsigned)d_.D, dt, woff, rows, 3);
+            } else {
+                tm_cuda_tok_gemv_kq(SLOT_H, r.q.id, r.q.woff, SLOT_QKV, 0, (unsigned)QD, (unsigned)d_.D, dt);
+                tm_cuda_tok_gemv_kq(SLOT_H, r.k.id, r.k.woff, SLOT_QKV, (size_t)QD * 4, (unsigned)KVD, (unsigned)d_.D, dt);
+                tm_cuda_tok_gemv_kq(SLOT_H, r.v.id, r.v.woff, SLOT_QKV, (size_t)(QD + KVD) * 4, (unsigned)KVD, (unsigned)d_.D, dt);
+            }
+            tm_cuda_tok_rope_q(SLOT_QKV, (unsigned)d_.H, (unsigned)d_.dh, pos, d_.theta);
+            tm_cuda_tok_rope_k_cache(SLOT_QKV, (size_t)QD * 4, SLOT_KC + l, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, pos, d_.theta);
+            tm_cuda_tok_v_cache(SLOT_QKV, (size_t)(QD + KVD) * 4, SLOT_VC + l, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, pos);
+            tm_cuda_tok_attn(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)QD, (unsigned)d_.H, (unsigned)d_.KVH,
+                             (unsigned)d_.dh, (unsigned)d_.ctx, pos + 1, scale, (unsigned)REP);
+            tm_cuda_tok_gemv_kq(SLOT_AO, r.o.id, r.o.woff, SLOT_H2, 0, (unsigned)d_.D, (unsigned)QD, dt);
+            tm_cuda_tok_add(SLOT_X, SLOT_H2, (unsigned)d_.D);
+            tm_cuda_tok_rmsnorm(SLOT_X, s.rms2, SLOT_H2S, (unsigned)d_.D, d_.eps);
+            tm_cuda_tok_gemv_kq(SLOT_H2S, r.gate.id, r.gate.woff, SLOT_GU, 0, (unsigned)d_.F, (unsigned)d_.D, dt);
+            tm_cuda_tok_gemv_kq(SLOT_H2S, r.up.id, r.up.woff, SLOT_GU, (size_t)d_.F * 4, (unsigned)d_.F, (unsigned)d_.D, dt);
+            tm_cuda_tok_silu_mul(SLOT_GU, 0, SLOT_GU, (size_t)d_.F * 4, (unsigned)d_.F);
+            tm_cuda_tok_gemv_kq(SLOT_GU, r.down.id, r.down.woff, SLOT_DN, 0, (unsigned)d_.D, (unsigned)d_.F, dt);
+            tm_cuda_tok_add(SLOT_X, SLOT_DN, (unsigned)d_.D);
+        }
+        tm_cuda_tok_rmsnorm(SLOT_X, d_.rmsf, SLOT_XF, (unsigned)d_.D, d_.eps);
+        tm_cuda_tok_gemv_kq(SLOT_XF, head_.id, head_.woff, SLOT_LOGITS, 0, (unsigned)d_.V, (unsigned)d_.D, d_.dt_head);
+    }
+
+    // Chain form of the same token: position and token index come from SLOT_STATE on the device,
+    // norms / SiLU / residuals are folded into the GEMVs. Encoded once and captured.
+    void encode_chain_token(unsigned max_tokens) {
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh, REP = d_.H / d_.KVH;
+        const float scale = 1.f / std::sqrt((float)d_.dh);
+        const unsigned dt = d_.dt_proj;
+        tm_cuda_tok_embed_at(SLOT_TOK, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed, max_tokens, SLOT_STATE);
+        for (int l = 0; l < d_.L; ++l) {
+            const Registered& r = w_[(size_t)l];
+            const CudaLlamaLayer& s = layers_[(size_t)l];
+            const unsigned qkv_rows[3] = {(unsigned)QD, (unsigned)KVD, (unsigned)KVD};
+            if (same_buffer(r.q, r.k, r.v)) {
+                const uint64_t woff[3] = {r.q.woff, r.k.woff, r.v.woff};
+                tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms1, d_.eps, r.q.id, SLOT_QKV, 0, (unsigned)(QD + 2 * KVD), (unsigned)d_.D, dt, woff, qkv_rows, 3, 0);
+            } else {
+                const Handle* hs[3] = {&r.q, &r.k, &r.v};
+                size_t yoff = 0;
+                for (int i = 0; i < 3; ++i) {
+                    tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms1, d_.eps, hs[i]->id, SLOT_QKV, yoff, qkv_rows[i], (unsigned)d_.D, dt, &hs[i]->woff, &qkv_rows[i], 1, 0);
+                    yoff += (size_t)qkv_rows[i] * 4;
+                }
+            }
+            tm_cuda_tok_qkv_post_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, (unsigned)d_.H, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, d_.theta, SLOT_STATE);
+            tm_cuda_tok_attn_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)QD, (unsigned)d_.H, (unsigned)d_.KVH,
+                                (unsigned)d_.dh, (unsigned)d_.ctx, scale, (unsigned)REP, SLOT_STATE);
+            const unsigned Dn = (unsigned)d_.D, Fn = (unsigned)d_.F;
+            tm_cuda_tok_gemv_fused(SLOT_AO, 0, 0, 0, 0, nullptr, 0.f, r.o.id, SLOT_X, 0, Dn, (unsigned)QD, dt, &r.o.woff, &Dn, 1, 1);
+            if (same_buffer(r.gate, r.up, r.up)) {
+                const uint64_t woff[2] = {r.gate.woff, r.up.woff};
+                const unsigned rows[2] = {Fn, Fn};
+                tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.gate.id, SLOT_GU, 0, 2 * Fn, Dn, dt, woff, rows, 2, 0);
+            } else {
+                tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.gate.id, SLOT_GU, 0, Fn, Dn, dt, &r.gate.woff, &Fn, 1, 0);
+                tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.up.id, SLOT_GU, (size_t)Fn * 4, Fn, Dn, dt, &r.up.woff, &Fn, 1, 0);
+            }
+            tm_cuda_tok_gemv_fused(SLOT_GU, 0, 2, SLOT_GU, (size_t)Fn * 4, nullptr, 0.f, r.down.id, SLOT_X, 0, Dn, Fn, dt, &r.down.woff, &Dn, 1, 1);
+        }
+        const unsigned Vn = (unsigned)d_.V;
+        tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, 0, Vn, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vn, 1, 0);
+        tm_cuda_tok_argmax_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE);
+        tm_cuda_tok_advance(SLOT_STATE);
+    }
+
+    // One forward at position `seen`: logits of that token (tensormark/llama.h:5931-5980).
+    std::vector<float>& forward_gpu_one(int tok) {
+        if (tok < 0 || tok >= d_.V) throw std::invalid_argument("llama: token id out of range");
+        if (seen >= d_.ctx) throw std::invalid_argument("llama: context is full");
+        gpu_token_prologue();
+        const unsigned t = (unsigned)tok;
+        if (!tm_cuda_tok_upload(SLOT_TOK, 0, &t, sizeof t)) throw std::runtime_error("cuda: token upload failed");
+        if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
+        tm_cuda_tok_embed_kq(SLOT_TOK, 0, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed);
+        encode_gpu_token(seen);
+        if (!tm_cuda_tok_end(SLOT_LOGITS, logits_.data(), (unsigned)d_.V))
+            throw std::runtime_error(std::string("cuda: token execution failed: ") + tm_cuda_last_error());
+        seen += 1;
+        return logits_;
+    }
+
+    // Greedy chain (tensormark/llama.h:6047-6165): feeds `first` at the current position and
+    // chooses n tokens on the GPU, chosen tokens 0..n-2 being fed by the following steps.
+    void gpu_chain_begin(int first, int n) {
+        if (n <= 0) throw std::invalid_argument("llama: chain needs n >= 1");
+        if (first < 0 || first >= d_.V) throw std::invalid_argument("llama: token id out of range");
+        if (seen + n > d_.ctx) throw std::invalid_argument("llama: chain exceeds context");
+        if (chain_n_) throw std::runtime_error("llama: chain already running");
+        gpu_token_prologue();
+        const unsigned cap = (unsigned)d_.ctx + 1;
+        std::vector<unsigned> toks((size_t)cap, 0xFFFFFFFFu);
+        toks[0] = (unsigned)first;
+        if (!tm_cuda_tok_reserve(SLOT_TOK, sizeof(unsigned) * (size_t)cap) ||
+            !tm_cuda_tok_upload(SLOT_TOK, 0, toks.data(), sizeof(unsigned) * (size_t)cap))
+            throw std::runtime_error("cuda: token slot upload failed");
+        if (use_graph_) {
+            const int st[2] = {seen, 0};
+            if (!tm_cuda_tok_upload(SLOT_STATE, 0, st, sizeof st)) throw std::runtime_error("cuda: chain state upload failed");
+            if (graph_ < 0) {
+                // the first token runs eagerly (it also creates every cached resource), the rest replay its capture
+                if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
+                encode_chain_token(cap);
+                if (!tm_cuda_tok_flush()) throw std::runtime_error(std::string("cuda: chain token failed: ") + tm_cuda_last_error());
+                if (!tm_cuda_tok_graph_begin()) throw std::runtime_error("cuda: graph capture failed");
+                encode_chain_token(cap);
+                graph_ = tm_cuda_tok_graph_end();
+                if (graph_ < 0) throw std::runtime_error(std::string("cuda: graph capture failed: ") + tm_cuda_last_error());
+                if (n > 1 && !tm_cuda_tok_graph_launch(graph_, (unsigned)(n - 1))) throw std::runtime_error("cuda: graph launch failed");
+            } else if (!tm_cuda_tok_graph_launch(graph_, (unsigned)n)) {
+                throw std::runtime_error("cuda: graph launch failed");
+            }
+        } else {
+            for (int i = 0; i < n; ++i) {
+                if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
+                tm_cuda_tok_embed_kq(SLOT_TOK, (unsigned)i, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed);
+                encode_gpu_token(seen + i);
+                tm_cuda_tok_argmax(SLOT_LOGITS, SLOT_TOK, (unsigned)(i + 1), (unsigned)d_.V);
+                if (!tm_cuda_tok_end_async()) throw std::runtime_error("cuda: token commit failed");
+            }
+        }
+        chain_n_ = n; chain_seen0_ = seen;
+    }
+    // Chosen token i as soon as it has landed, -1 while pending.
+    int gpu_chain_poll(int i) const {
+        if (i < 0 || i >= chain_n_) return -1;
+        const unsigned t = tm_cuda_tok_peek(SLOT_TOK, (unsigned)(i + 1));
+        return t == 0xFFFFFFFFu ? -1 : (int)t;
+    }
+    // The n chosen tokens (the last one not yet fed). keep >= 0: the caller stopped at chosen
+    // token `keep`; the cache position becomes seen0 + keep + 1.
+    std::vector<int> gpu_chain_end(int keep = -1) {
+        std::vector<int> out;
+        if (!chain_n_) return out;
+        if (!tm_cuda_tok_wait_pending()) throw std::runtime_error(std::string("cuda: chained token execution failed: ") + tm_cuda_last_error());
+        std::vector<unsigned> toks((size_t)chain_n_);
+        if (!tm_cuda_tok_download(SLOT_TOK, sizeof(unsigned), toks.data(), sizeof(unsigned) * (size_t)chain_n_) ||
+            !tm_cuda_tok_download(SLOT_LOGITS, 0, logits_.data(), sizeof(float) * (size_t)d_.V))
+            throw std::runtime_error("cuda: chained result download failed");
+        out.assign(toks.begin(), toks.end());
+        seen = keep < 0 ? chain_seen0_ + chain_n_ : chain_seen0_ + keep + 1;
+        chain_n_ = 0;
+        return out;
+    }
+    // n forwards (first + n-1 chosen tokens); returns the n-1 chosen tokens that were fed.
+    std::vector<int> generate_greedy_gpu(int first, int n) {
+        gpu_chain_begin(first, n);
+        std::vector<int> t = gpu_chain_end();
+        t.pop_back();
+        return t;
+    }
+
+private:
+    struct Handle { int id = -1; uint64_t woff = 0; };
+    struct Registered { Handle q, k, v, o, gate, up, down; };
+    static bool same_buffer(const Handle& a, const Handle& b, const Handle& c) { return a.id == b.id && b.id == c.id; }
+
+    CudaLlamaDesc d_;
+    std::vector<CudaLlamaLayer> layers_;
+    std::vector<Registered> w_;
+    Handle embed_, head_;
+    std::vector<float> logits_;
+    bool ready_ = false, use_graph_ = true;
+    int graph_ = -1, chain_n_ = 0, chain_seen0_ = 0;
+};
+
+}  // namespace tmllama

@@ -16,6 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtm_cuda.so")
+CHAIN_LIB = os.path.join(HERE, "libtm_chain.so")
 
 NVCC_FLAGS = [
     "-std=c++20", "-O3", "-lineinfo",
@@ -78,6 +79,16 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    # the C++ host driver of the decode chain, behind a flat C surface
+    chain_src = os.path.join(HERE, "host", "chain_capi.cpp")
+    chain_deps = [chain_src, os.path.join(INCLUDE, "llama_chain.h"), os.path.join(INCLUDE, "cuda_shim.h"), LIB]
+    if force or _stale(CHAIN_LIB, chain_deps):
+        cmd = ["g++", "-std=c++23", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I" + INCLUDE, "-o", CHAIN_LIB,
+               chain_src, "-L" + HERE, "-ltm_cuda", "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("host driver build failed")
     return LIB
 
 

@@ -1,0 +1,94 @@
+"""ctypes view of libtm_chain.so: the C++ decode-chain driver (include/llama_chain.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libtm_chain.so")
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m tensormark_b200.build`")
+        L = C.CDLL(LIB_PATH)
+        L.tmchain_error.restype = C.c_char_p
+        L.tmchain_create.restype = C.c_void_p
+        L.tmchain_create.argtypes = [C.POINTER(C.c_int), C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t]
+        L.tmchain_destroy.argtypes = [C.c_void_p]
+        L.tmchain_seen.argtypes = [C.c_void_p]
+        L.tmchain_set_seen.argtypes = [C.c_void_p, C.c_int]
+        L.tmchain_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.tmchain_greedy.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.tmchain_chain_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.tmchain_chain_poll.argtypes = [C.c_void_p, C.c_int]
+        L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+        _lib = L
+    return _lib
+
+
+class Chain:
+    """A model on the GPU decode lane. `weights` is the dict synth.make_llama returns (kept alive here:
+    registrations are keyed by host address)."""
+
+    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True):
+        self.L, self.cfg, self.weights = load(), cfg, weights
+        icfg = (C.c_int * 11)(cfg["L"], cfg["D"], cfg["H"], cfg["KVH"], cfg["dh"], cfg["F"], cfg["V"], cfg["ctx"],
+                              cfg["dt_proj"], cfg["dt_head"], cfg["dt_embed"])
+        ptrs = []
+        for l in range(cfg["L"]):
+            for n in ("q", "k", "v", "o", "gate", "up", "down", "rms1", "rms2"):
+                ptrs.append(weights[f"l{l}.{n}"].ctypes.data)
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        blob = weights["blob"]
+        self.h = self.L.tmchain_create(icfg, cfg["theta"], cfg["eps"], weights["embed"].ctypes.data, weights["head"].ctypes.data,
+                                       weights["rmsf"].ctypes.data, arr,
+                                       blob.ctypes.data if shared_mapping else None, blob.nbytes if shared_mapping else 0)
+        if not self.h:
+            raise RuntimeError(self.L.tmchain_error().decode())
+
+    def _check(self, ok):
+        if not ok:
+            raise RuntimeError(self.L.tmchain_error().decode())
+
+    @property
+    def seen(self) -> int:
+        return self.L.tmchain_seen(self.h)
+
+    @seen.setter
+    def seen(self, v: int):
+        self.L.tmchain_set_seen(self.h, v)
+
+    def forward(self, tok: int) -> np.ndarray:
+        logits = np.empty(self.cfg["V"], np.float32)
+        self._check(self.L.tmchain_forward(self.h, int(tok), logits.ctypes.data))
+        return logits
+
+    def greedy(self, first: int, n: int, graph: bool = True):
+        out = np.empty(n, np.int32)
+        logits = np.empty(self.cfg["V"], np.float32)
+        self._check(self.L.tmchain_greedy(self.h, int(first), n, out.ctypes.data, logits.ctypes.data, int(graph)))
+        return out, logits
+
+    def chain_begin(self, first: int, n: int, graph: bool = True):
+        self._check(self.L.tmchain_chain_begin(self.h, int(first), n, int(graph)))
+
+    def chain_poll(self, i: int) -> int:
+        return self.L.tmchain_chain_poll(self.h, i)
+
+    def chain_end(self, n: int, keep: int = -1) -> np.ndarray:
+        out = np.empty(n, np.int32)
+        got = self.L.tmchain_chain_end(self.h, keep, out.ctypes.data, n)
+        self._check(got >= 0)
+        return out[:got]
+
+    def close(self):
+        if self.h:
+            self.L.tmchain_destroy(self.h)
+            self.h = None

@@ -36,8 +36,14 @@ struct SegTable {                           // rows [row_end[s-1], row_end[s]) s
 };
 
 // ---- kernel launchers (one per .cu) -----------------------------------------
+struct GemvFuse {                           // optional fusions of the decode chain
+    unsigned x_op;                          // 0 none, 1 rmsnorm (x2 = weights, eps), 2 silu(x) * x2
+    const float* x2;
+    float eps;
+    bool accumulate;                        // y[row] += dot instead of y[row] = dot
+};
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
-                 const SegTable& seg, cudaStream_t st);
+                 const SegTable& seg, cudaStream_t st, const GemvFuse* fuse = nullptr);
 bool launch_dequant(const uint8_t* W, float* out, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);
 bool launch_dequant_half(const uint8_t* W, void* out_half, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);
 

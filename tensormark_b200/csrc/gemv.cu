@@ -49,6 +49,11 @@ struct GemvParams {
     float* y;
     uint32_t N, K, row_bytes;
     uint32_t stages, rows_per_warp;
+    // optional fusions (decode chain): a transform of x while it is staged, and y += instead of y =
+    const float* x2;            // x_op 1: rmsnorm weights; x_op 2: the "up" vector
+    float eps;
+    uint32_t x_op;              // 0 plain, 1 x*rsqrt(mean(x^2)+eps)*x2, 2 silu(x)*x2
+    uint32_t accumulate;
     SegTable seg;
     int* status;
 };
@@ -163,10 +168,31 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
     // the run sums come from three shuffle stages, the plane bytes leave as packed stores.
     // A warp stages four blocks per pass and two passes are interleaved.
+    float norm_inv = 1.f;
+    if (p.x_op == 1u) {
+        // RMSNorm folded into the staging: every CTA needs all of x anyway, so each one
+        // recomputes the (cheap) sum of squares instead of a separate kernel writing a normed copy.
+        __shared__ float red[kWarps];
+        const float4* xg = reinterpret_cast<const float4*>(p.x);
+        float ss = 0.f;
+        for (uint32_t i = threadIdx.x; i < p.K / 4; i += blockDim.x) {
+            const float4 t = __ldcg(xg + i);
+            ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) tot += red[w];
+        norm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+    }
     {
         constexpr int B = 2;
         const uint32_t nblk = p.K / 32, li = lane & 7u, sub = lane >> 3;
         const float4* xg4 = reinterpret_cast<const float4*>(p.x);
+        const float4* x24 = reinterpret_cast<const float4*>(p.x2);
         for (uint32_t b0 = warp * (4 * B); b0 < nblk; b0 += kWarps * (4 * B)) {
             float4 v[B];
             float am[B], s8[B], s16[B], s32[B];
@@ -175,6 +201,16 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
             for (int j = 0; j < B; ++j) {
                 const uint32_t b = b0 + 4 * j + sub;
                 v[j] = b < nblk ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.x_op != 0u && b < nblk) {
+                    const float4 w2 = __ldcg(x24 + b * 8 + li);
+                    if (p.x_op == 1u) {
+                        v[j].x = v[j].x * norm_inv * w2.x; v[j].y = v[j].y * norm_inv * w2.y;
+                        v[j].z = v[j].z * norm_inv * w2.z; v[j].w = v[j].w * norm_inv * w2.w;
+                    } else {
+                        v[j].x = v[j].x / (1.0f + expf(-v[j].x)) * w2.x; v[j].y = v[j].y / (1.0f + expf(-v[j].y)) * w2.y;
+                        v[j].z = v[j].z / (1.0f + expf(-v[j].z)) * w2.z; v[j].w = v[j].w / (1.0f + expf(-v[j].w)) * w2.w;
+                    }
+                }
                 am[j] = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
                 const float any_nan = (v[j].x + v[j].y) + (v[j].z + v[j].w);         // NaN if any element is NaN
                 bad[j] = !(am[j] <= 3.0e38f) || any_nan != any_nan;
@@ -279,7 +315,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
             v += __shfl_xor_sync(0xffffffffu, v, 4);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
             v += __shfl_xor_sync(0xffffffffu, v, 1);
-            if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) p.y[row0 + my_row] = v;
+            if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) {
+                if (p.accumulate) v += p.y[row0 + my_row];          // residual add folded into the store
+                p.y[row0 + my_row] = v;
+            }
             c = 0; row0 += R;
         }
     }
@@ -375,17 +414,40 @@ template <> __device__ float generic_row<6>(const uint8_t* r, const float* x, ui
 
 template <int DT>
 __global__ void __launch_bounds__(256) gemv_generic(const GemvParams p) {
+    extern __shared__ __align__(16) float xs[];            // transformed x, only when a fused transform is requested
+    __shared__ float red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* x = p.x;
+    if (p.x_op != 0u) {
+        float inv = 1.f;
+        if (p.x_op == 1u) {
+            float ss = 0.f;
+            for (uint32_t i = threadIdx.x; i < p.K; i += blockDim.x) { const float t = p.x[i]; ss = fmaf(t, t, ss); }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+            inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+        }
+        for (uint32_t i = threadIdx.x; i < p.K; i += blockDim.x) {
+            const float t = p.x[i];
+            xs[i] = p.x_op == 1u ? t * inv * p.x2[i] : t / (1.0f + expf(-t)) * p.x2[i];
+        }
+        __syncthreads();
+        x = xs;
+    }
+    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= p.N) return;
-    float v = generic_row<DT>(row_ptr(p, row), p.x, p.K, lane);
+    float v = generic_row<DT>(row_ptr(p, row), x, p.K, lane);
 #pragma unroll
     for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) p.y[row] = v;
+    if (lane == 0) p.y[row] = p.accumulate ? p.y[row] + v : v;
 }
 
-constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemLimit = 227 * 1024 - 256;          // dynamic part; the kernel also has a few static words
 
 // Bytes of shared memory outside the stage rings.
 template <int DT> size_t stream_fixed_smem(unsigned K) {
@@ -477,7 +539,15 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         }
     }
     const unsigned rows_per_cta = 8;
-    gemv_generic<DT><<<(p.N + rows_per_cta - 1) / rows_per_cta, rows_per_cta * 32, 0, st>>>(p);
+    const size_t xsmem = p.x_op ? (size_t)p.K * 4 : 0;
+    if (xsmem > 48 * 1024) {
+        static bool attr = false;
+        if (!attr && cudaFuncSetAttribute(gemv_generic<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return fail("gemv: cannot raise the dynamic shared memory limit");
+        attr = true;
+        if (xsmem > 200 * 1024) return fail("gemv: K=%u is too long for the unaligned fused form", p.K);
+    }
+    gemv_generic<DT><<<(p.N + rows_per_cta - 1) / rows_per_cta, rows_per_cta * 32, xsmem, st>>>(p);
     note_launch();
     return check_launch("gemv_generic");
 }
@@ -485,7 +555,7 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
 }  // namespace
 
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
-                 const SegTable& seg, cudaStream_t st) {
+                 const SegTable& seg, cudaStream_t st, const GemvFuse* fuse) {
     const unsigned be = block_elems(dtype);
     if (!be || dtype == DT_F16) return fail("gemv: dtype %u is not a block format", dtype);
     if (!x || !W || !y) return fail("gemv: null pointer");
@@ -498,6 +568,11 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     p.W = W; p.x = x; p.y = y; p.N = N; p.K = K;
     p.row_bytes = (K / be) * block_bytes(dtype);
     p.seg = seg; p.status = device_status_word();
+    p.x2 = nullptr; p.eps = 0.f; p.x_op = 0; p.accumulate = 0;
+    if (fuse) {
+        if (fuse->x_op > 2 || (fuse->x_op != 0 && (!fuse->x2 || (uintptr_t)fuse->x2 % 16))) return fail("gemv: bad fused x transform");
+        p.x2 = fuse->x2; p.eps = fuse->eps; p.x_op = fuse->x_op; p.accumulate = fuse->accumulate ? 1u : 0u;
+    }
     bool aligned = ((uintptr_t)W % 16 == 0) && (p.row_bytes % 16 == 0);
     for (unsigned s = 0; s < seg.nseg; ++s) aligned = aligned && (seg.woff[s] % 16 == 0);
     switch (dtype) {

@@ -112,10 +112,13 @@ __global__ void bias_kernel(float* __restrict__ y, const float* __restrict__ bia
 
 // One embedding row chosen by a token id that lives on the device; the sentinel
 // 0xFFFFFFFF (a chain slot not yet written) gives zeros.
+// `st` (optional) is a device-resident chain state {position, token index}: when given, the index comes from it.
 __global__ void embed_row_kernel(const uint32_t* __restrict__ tok, uint32_t idx, const uint8_t* __restrict__ W,
-                                 float* __restrict__ x, uint32_t D, uint32_t row_bytes, unsigned dtype) {
+                                 float* __restrict__ x, uint32_t D, uint32_t row_bytes, unsigned dtype,
+                                 const int* __restrict__ st) {
     const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= D) return;
+    if (st) idx = (uint32_t)st[1];
     const uint32_t row = tok[idx];
     x[k] = row == 0xFFFFFFFFu ? 0.f : decode_weight_dt(dtype, W + (size_t)row * row_bytes, k);
 }
@@ -136,8 +139,10 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
 template <bool SAMPLE>
 __global__ void __launch_bounds__(256) choose_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, uint32_t n,
                                                       uint32_t idx, float inv_temp, uint32_t seed,
-                                                      unsigned long long* __restrict__ scratch /* [0]=key, [1]=done */) {
+                                                      unsigned long long* __restrict__ scratch /* [0]=key, [1]=done */,
+                                                      const int* __restrict__ st) {
     __shared__ unsigned long long best_s[8];
+    if (st) idx = (uint32_t)st[1] + 1u;                     // chain: the token chosen now is fed by the next step
     unsigned long long best = pack_key(-CUDART_INF_F, 0);
     const uint32_t base = hash32(seed * 0x9e3779b9u + idx * 0x85ebca6bu + 0x1234567u);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -184,8 +189,13 @@ template <typename T, int DPL, int REP>
 __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict__ q, const T* __restrict__ kc,
                                                           const T* __restrict__ vc, float* __restrict__ part,
                                                           float* __restrict__ stat, uint32_t H, uint32_t ctx,
-                                                          uint32_t allow, uint32_t chunk, float scale) {
+                                                          uint32_t allow, uint32_t chunk, float scale,
+                                                          const int* __restrict__ st) {
     constexpr int dh = DPL * 32;
+    if (st) {                                               // chain: attend [0, position] with the grid's fixed split count
+        allow = min((uint32_t)st[0] + 1u, ctx);
+        chunk = (allow + gridDim.y - 1) / gridDim.y;
+    }
     const uint32_t kv = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t p0 = split * chunk, p1 = min(allow, p0 + chunk);
     __shared__ float sm_acc[4][REP][dh];
@@ -273,17 +283,47 @@ __global__ void attn_combine_kernel(const float* __restrict__ part, const float*
     }
 }
 
+// Chain form of rope(q) + rope(k) -> cache + v -> cache in one launch, position read from the chain state.
+// qkv = [q: H*dh | k: KVH*dh | v: KVH*dh]; thread t < (H+KVH)*dh/2 rotates one pair, the rest copy V.
+template <typename T>
+__global__ void qkv_post_kernel(float* __restrict__ qkv, T* __restrict__ kcache, T* __restrict__ vcache, uint32_t H,
+                                uint32_t KVH, uint32_t dh, uint32_t ctx, const float2* __restrict__ tbl, uint32_t tbl_n,
+                                const int* __restrict__ st) {
+    const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x, half = dh / 2;
+    const int pos = st[0];
+    if (pos < 0 || (uint32_t)pos >= ctx) return;
+    const uint32_t npair = (H + KVH) * half;
+    if (gid < npair) {
+        const uint32_t h = gid / half, j = gid % half;
+        if ((uint32_t)pos * half + j >= tbl_n) return;
+        const float2 cs = tbl[(size_t)(uint32_t)pos * half + j];
+        float* r = qkv + (size_t)h * dh;                     // heads H.. are the K heads, contiguous after q
+        const float a = r[j], b = r[j + half];
+        const float ra = a * cs.x - b * cs.y, rb = b * cs.x + a * cs.y;
+        if (h < H) { r[j] = ra; r[j + half] = rb; }
+        else {
+            T* dst = kcache + (size_t)(h - H) * ctx * dh + (size_t)pos * dh;
+            dst[j] = to_cache<T>(ra); dst[j + half] = to_cache<T>(rb);
+        }
+    } else if (gid < npair + KVH * dh) {
+        const uint32_t e = gid - npair, kv = e / dh, l = e % dh;
+        vcache[(size_t)kv * ctx * dh + (size_t)pos * dh + l] = to_cache<T>(qkv[(size_t)(H + KVH) * dh + e]);
+    }
+}
+__global__ void advance_kernel(int* __restrict__ st) { st[0] += 1; st[1] += 1; }
+
 inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
 
 template <typename T, int DPL>
 bool launch_attn_rep(const float* q, const T* kc, const T* vc, float* part, float* stat, unsigned H, unsigned KVH,
-                     unsigned ctx, unsigned allow, unsigned chunk, unsigned nsplit, float scale, unsigned REP, cudaStream_t st) {
+                     unsigned ctx, unsigned allow, unsigned chunk, unsigned nsplit, float scale, unsigned REP,
+                     const int* state, cudaStream_t st) {
     const dim3 grid(KVH, nsplit);
     switch (REP) {
-        case 1: attn_split_kernel<T, DPL, 1><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale); break;
-        case 2: attn_split_kernel<T, DPL, 2><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale); break;
-        case 4: attn_split_kernel<T, DPL, 4><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale); break;
-        case 8: attn_split_kernel<T, DPL, 8><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale); break;
+        case 1: attn_split_kernel<T, DPL, 1><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 2: attn_split_kernel<T, DPL, 2><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 4: attn_split_kernel<T, DPL, 4><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 8: attn_split_kernel<T, DPL, 8><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
         default: return fail("attention: REP=%u unsupported (1, 2, 4 or 8)", REP);
     }
     note_launch();
@@ -362,23 +402,38 @@ bool launch_half_to_f32(const void* src, float* dst, size_t n, cudaStream_t st) 
     note_launch();
     return check_launch("half_to_f32");
 }
-bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st) {
+bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st,
+                      const int* state) {
     const unsigned be = block_elems(dtype);
     if (!be || dtype == DT_F16 || D % be) return fail("embed: D=%u is not whole blocks of dtype %u", D, dtype);
-    embed_row_kernel<<<cdiv(D, 256), 256, 0, st>>>(tok, idx, W, x, D, (D / be) * block_bytes(dtype), dtype);
+    embed_row_kernel<<<cdiv(D, 256), 256, 0, st>>>(tok, idx, W, x, D, (D / be) * block_bytes(dtype), dtype, state);
     note_launch();
     return check_launch("embed_row");
 }
 bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
-                   unsigned long long* scratch, cudaStream_t st) {
+                   unsigned long long* scratch, cudaStream_t st, const int* state) {
     if (!x || !out || n == 0) return fail("argmax: bad arguments");
     unsigned grid = cdiv(n, 256 * 4);
     const unsigned sms = (unsigned)device_sm_count();
     if (grid > sms) grid = sms;
-    if (sample) choose_kernel<true><<<grid, 256, 0, st>>>(x, out, n, idx, inv_temp, seed, scratch);
-    else choose_kernel<false><<<grid, 256, 0, st>>>(x, out, n, idx, 0.f, 0u, scratch);
+    if (sample) choose_kernel<true><<<grid, 256, 0, st>>>(x, out, n, idx, inv_temp, seed, scratch, state);
+    else choose_kernel<false><<<grid, 256, 0, st>>>(x, out, n, idx, 0.f, 0u, scratch, state);
     note_launch();
     return check_launch("argmax");
+}
+
+bool launch_qkv_post(float* qkv, void* kc, void* vc, bool half_cache, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
+                     const float* tbl, unsigned tbl_entries, const int* state, cudaStream_t st) {
+    const unsigned n = (H + KVH) * (dh / 2) + KVH * dh;
+    if (half_cache) qkv_post_kernel<__half><<<cdiv(n, 256), 256, 0, st>>>(qkv, (__half*)kc, (__half*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
+    else qkv_post_kernel<float><<<cdiv(n, 256), 256, 0, st>>>(qkv, (float*)kc, (float*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
+    note_launch();
+    return check_launch("qkv_post");
+}
+bool launch_advance(int* state, cudaStream_t st) {
+    advance_kernel<<<1, 1, 0, st>>>(state);
+    note_launch();
+    return check_launch("advance");
 }
 
 AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t probs_bytes) {
@@ -401,17 +456,17 @@ AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, uns
 
 bool launch_attention(const float* q, const void* kc, const void* vc, bool half_cache, float* scratch, float* out,
                       unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, float scale, unsigned REP,
-                      const AttnPlan& pl, cudaStream_t st) {
+                      const AttnPlan& pl, cudaStream_t st, const int* state) {
     if (dh != 64 && dh != 128) return fail("attention: head dim %u unsupported (64 or 128)", dh);
     float* part = scratch;
     float* stat = scratch + pl.part_floats;
     bool ok;
     if (half_cache) {
-        ok = dh == 128 ? launch_attn_rep<__half, 4>(q, (const __half*)kc, (const __half*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, st)
-                       : launch_attn_rep<__half, 2>(q, (const __half*)kc, (const __half*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, st);
+        ok = dh == 128 ? launch_attn_rep<__half, 4>(q, (const __half*)kc, (const __half*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, state, st)
+                       : launch_attn_rep<__half, 2>(q, (const __half*)kc, (const __half*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, state, st);
     } else {
-        ok = dh == 128 ? launch_attn_rep<float, 4>(q, (const float*)kc, (const float*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, st)
-                       : launch_attn_rep<float, 2>(q, (const float*)kc, (const float*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, st);
+        ok = dh == 128 ? launch_attn_rep<float, 4>(q, (const float*)kc, (const float*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, state, st)
+                       : launch_attn_rep<float, 2>(q, (const float*)kc, (const float*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, state, st);
     }
     if (!ok) return false;
     attn_combine_kernel<<<H, dh < 128 ? 64 : 128, 0, st>>>(part, stat, out, H, dh, pl.nsplit);

@@ -19,10 +19,12 @@ bool launch_rope_k_cache(const float* ksrc, void* cache, bool half_cache, unsign
 bool launch_v_cache(const float* v, void* cache, bool half_cache, unsigned KVH, unsigned dh, unsigned ctx, int pos, cudaStream_t st);
 bool launch_f32_to_half(const float* src, void* dst, size_t n, cudaStream_t st);
 bool launch_half_to_f32(const void* src, float* dst, size_t n, cudaStream_t st);
-bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st);
+// state (optional, device): chain state {position, token index}; when given, position and index come from it
+bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st,
+                      const int* state = nullptr);
 // scratch: two zero-initialised 64-bit words owned by the caller, re-armed by the kernel
 bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
-                   unsigned long long* scratch, cudaStream_t st);
+                   unsigned long long* scratch, cudaStream_t st, const int* state = nullptr);
 
 struct AttnPlan {
     unsigned nsplit;        // 0: the scratch cannot hold even one split
@@ -33,6 +35,9 @@ struct AttnPlan {
 AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t scratch_bytes);
 bool launch_attention(const float* q, const void* kc, const void* vc, bool half_cache, float* scratch, float* out,
                       unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, float scale, unsigned REP,
-                      const AttnPlan& pl, cudaStream_t st);
+                      const AttnPlan& pl, cudaStream_t st, const int* state = nullptr);
+bool launch_qkv_post(float* qkv, void* kc, void* vc, bool half_cache, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
+                     const float* tbl, unsigned tbl_entries, const int* state, cudaStream_t st);
+bool launch_advance(int* state, cudaStream_t st);
 
 }  // namespace tmc

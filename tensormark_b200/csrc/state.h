@@ -51,6 +51,7 @@ struct State {
     int shared_id = -1;
     std::map<const void*, float*> norm_w;                       // rmsnorm weights cached by host pointer
     bool encoding = false;                                      // between tok_begin and the matching end
+    bool capturing = false;                                     // between tok_graph_begin and tok_graph_end
     bool sticky = false;                                        // a void encoder failed since the last end
     std::vector<cudaEvent_t> pending;                           // tok_end_async markers
     float* rope_tbl = nullptr;                                  // (cos, sin) pairs [cap][dh/2]

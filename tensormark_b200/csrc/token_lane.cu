@@ -478,6 +478,150 @@ bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream)
     return launch_choose(x, out, n, 0, 0.f, 0u, false, sc, (cudaStream_t)stream);
 }
 
+// ---- chain forms: position and token index live on the device -------------------------
+// A chain state is two ints in a slot: {position, token index}. The entries below read it on the
+// device, so one captured CUDA graph serves every token of a greedy chain.
+static const int* state_ptr(int stateslot, const char* who) { return (const int*)slot_ptr(stateslot, 8, who); }
+
+void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                            int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const char* who = "tok_gemv_fused";
+    const size_t row_bytes = weight_bytes(dtype, 1, K);
+    if (!row_bytes) { latch("%s: K=%u is not whole blocks of dtype %u", who, K, dtype); return; }
+    if (yoff % 4 || xoff % 16 || x2off % 16) { latch("%s: misaligned byte offset", who); return; }
+    SegTable t;
+    if (!make_segments(t, N, seg_woff, seg_rows, nseg)) { s.sticky = true; return; }
+    const int i = wid - kFirstWeight;
+    if (i < 0 || i >= (int)s.wbufs.size() || !s.wbufs[i].ptr) { latch("%s: unknown weight handle %d", who, wid); return; }
+    for (unsigned k = 0; k < nseg; ++k)
+        if (t.woff[k] > s.wbufs[i].bytes || (size_t)seg_rows[k] * row_bytes > s.wbufs[i].bytes - t.woff[k]) {
+            latch("%s: segment %u lies outside weight handle %d", who, k, wid); return;
+        }
+    const uint8_t* x = slot_ptr(xslot, xoff + (size_t)K * 4, who);
+    uint8_t* y = slot_ptr(yslot, yoff + (size_t)N * 4, who);
+    if (!x || !y) return;
+    GemvFuse f{};
+    f.x_op = (unsigned)x_op; f.eps = eps; f.accumulate = accumulate != 0; f.x2 = nullptr;
+    if (x_op == 1) {
+        if (!norm_w) { latch("%s: rmsnorm needs its weights", who); return; }
+        auto it = s.norm_w.find(norm_w);
+        if (it == s.norm_w.end()) {
+            float* dw = nullptr;
+            if (cudaMalloc(&dw, (size_t)K * 4) != cudaSuccess) { cudaGetLastError(); latch("%s: weight allocation failed", who); return; }
+            cudaMemcpyAsync(dw, norm_w, (size_t)K * 4, cudaMemcpyHostToDevice, s.stream);
+            it = s.norm_w.emplace(norm_w, dw).first;
+        }
+        f.x2 = it->second;
+    } else if (x_op == 2) {
+        const uint8_t* u = slot_ptr(x2slot, x2off + (size_t)K * 4, who);
+        if (!u) return;
+        f.x2 = (const float*)(u + x2off);
+    } else if (x_op != 0) { latch("%s: unknown x transform %d", who, x_op); return; }
+    if (!launch_gemv((const float*)(x + xoff), s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream, &f)) s.sticky = true;
+}
+void tm_cuda_tok_qkv_post_at(int qkvslot, int kcslot, int vcslot, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
+                             float theta, int stateslot) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (!ensure_rope(dh, ctx, theta)) return;
+    float* qkv = (float*)slot_ptr(qkvslot, (size_t)(H + 2 * KVH) * dh * 4, "tok_qkv_post_at");
+    uint8_t* kc = slot_ptr(kcslot, kv_elem() * KVH * ctx * dh, "tok_qkv_post_at");
+    uint8_t* vc = slot_ptr(vcslot, kv_elem() * KVH * ctx * dh, "tok_qkv_post_at");
+    const int* st = state_ptr(stateslot, "tok_qkv_post_at");
+    if (!qkv || !kc || !vc || !st) return;
+    if (!launch_qkv_post(qkv, kc, vc, s.kv_half, H, KVH, dh, ctx, s.rope_tbl, s.rope_cap * (dh / 2), st, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int outslot, unsigned QD, unsigned H,
+                         unsigned KVH, unsigned dh, unsigned ctx, float scale, unsigned REP, int stateslot) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (!H || !KVH || !dh || !ctx || H % KVH || REP != H / KVH || (uint64_t)H * dh != QD || !std::isfinite(scale) || scale <= 0) {
+        latch("tok_attn_at: invalid decode attention dimensions or scale");
+        return;
+    }
+    const float* q = (const float*)slot_ptr(qslot, (size_t)QD * 4, "tok_attn_at");
+    const uint8_t* kc = slot_ptr(kcslot, kv_elem() * KVH * ctx * dh, "tok_attn_at");
+    const uint8_t* vc = slot_ptr(vcslot, kv_elem() * KVH * ctx * dh, "tok_attn_at");
+    float* out = (float*)slot_ptr(outslot, (size_t)QD * 4, "tok_attn_at");
+    float* probs = (float*)slot_ptr(probslot, (size_t)H * (dh + 2) * 4, "tok_attn_at");
+    const int* st = state_ptr(stateslot, "tok_attn_at");
+    if (!q || !kc || !vc || !out || !probs || !st) return;
+    // the split count is fixed for the whole chain (sized for a full context); the kernel derives its chunk from the state
+    const AttnPlan pl = plan_attention(H, KVH, dh, ctx, ctx, s.slots[probslot].bytes);
+    if (!pl.nsplit) { latch("tok_attn_at: probs slot too small for one split"); return; }
+    if (!launch_attention(q, kc, vc, s.kv_half, probs, out, H, KVH, dh, ctx, ctx, scale, REP, pl, s.stream, st)) s.sticky = true;
+}
+void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, "tok_argmax_at");
+    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * (size_t)max_tokens, "tok_argmax_at");
+    const int* st = state_ptr(stateslot, "tok_argmax_at");
+    unsigned long long* sc = choose_scratch();
+    if (!x || !t || !st || !sc) return;
+    if (!launch_choose(x, t, n, 0, 0.f, 0u, false, sc, s.stream, st)) s.sticky = true;
+}
+void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
+                          int stateslot) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const unsigned* tok = (const unsigned*)slot_ptr(tokslot, sizeof(unsigned) * (size_t)max_tokens, "tok_embed_at");
+    float* x = (float*)slot_ptr(xslot, (size_t)D * 4, "tok_embed_at");
+    const uint8_t* W = weight_ptr(wid, woff, 0, "tok_embed_at");
+    const int* st = state_ptr(stateslot, "tok_embed_at");
+    if (!tok || !x || !W || !st) return;
+    if (!launch_embed_row(tok, 0, W, x, D, dtype, s.stream, st)) s.sticky = true;
+}
+void tm_cuda_tok_advance(int stateslot) {
+    if (!ensure_init(-1)) return;
+    int* st = (int*)slot_ptr(stateslot, 8, "tok_advance");
+    if (st && !launch_advance(st, state().stream)) state().sticky = true;
+}
+
+// ---- CUDA graphs over the lane -----------------------------------------------------------
+// Everything encoded between graph_begin and graph_end is captured instead of executed; the
+// resulting graph replays the same launches (same slots, same weight handles). Slots, weight
+// handles, norm weights and the rope table must exist before the capture starts: run the
+// sequence once eagerly first.
+static std::vector<cudaGraphExec_t>& graphs() { static std::vector<cudaGraphExec_t> g; return g; }
+bool tm_cuda_tok_graph_begin(void) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (s.capturing) return fail("tok_graph_begin: a capture is already open");
+    if (cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) return check_launch("tok_graph_begin");
+    s.capturing = true; s.encoding = true; s.sticky = false;
+    return true;
+}
+int tm_cuda_tok_graph_end(void) {
+    State& s = state();
+    if (!s.ready || !s.capturing) { fail("tok_graph_end: no capture is open"); return -1; }
+    cudaGraph_t g = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(s.stream, &g);
+    s.capturing = false; s.encoding = false;
+    const bool sticky = s.sticky; s.sticky = false;
+    if (e != cudaSuccess || !g) { cudaGetLastError(); fail("tok_graph_end: %s", cudaGetErrorString(e)); return -1; }
+    if (sticky) { cudaGraphDestroy(g); ++s.fallbacks; return -1; }
+    cudaGraphExec_t x = nullptr;
+    if (cudaGraphInstantiate(&x, g, 0) != cudaSuccess) { cudaGraphDestroy(g); check_launch("tok_graph_end: instantiate"); return -1; }
+    cudaGraphDestroy(g);
+    graphs().push_back(x);
+    return (int)graphs().size() - 1;
+}
+bool tm_cuda_tok_graph_launch(int id, unsigned times) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (id < 0 || id >= (int)graphs().size() || !graphs()[id]) return fail("tok_graph_launch: unknown graph %d", id);
+    for (unsigned i = 0; i < times; ++i)
+        if (cudaGraphLaunch(graphs()[id], s.stream) != cudaSuccess) return check_launch("tok_graph_launch");
+    return true;
+}
+void tm_cuda_tok_graph_destroy(int id) {
+    if (id >= 0 && id < (int)graphs().size() && graphs()[id]) { cudaGraphExecDestroy(graphs()[id]); graphs()[id] = nullptr; }
+}
+
 size_t tm_cuda_attn_decode_scratch(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow) {
     if (!ensure_init(-1) || !H || !KVH || !dh || !allow) return 0;
     const AttnPlan pl = plan_attention(H, KVH, dh, ctx, allow, (size_t)1 << 40);

@@ -73,6 +73,17 @@ SIGNATURES = {
     "tm_cuda_tok_argmax": (None, [C.c_int, C.c_int, _u, _u]),
     "tm_cuda_tok_sample": (None, [C.c_int, C.c_int, _u, _u, C.c_float, _u]),
     "tm_cuda_tok_peek": (_u, [C.c_int, _u]),
+    "tm_cuda_tok_gemv_fused": (None, [C.c_int, _sz, C.c_int, C.c_int, _sz, _vp, C.c_float, C.c_int, C.c_int, _sz, _u, _u, _u,
+                                      C.POINTER(_u64), C.POINTER(_u), _u, C.c_int]),
+    "tm_cuda_tok_qkv_post_at": (None, [C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_int]),
+    "tm_cuda_tok_attn_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, _u, C.c_float, _u, C.c_int]),
+    "tm_cuda_tok_argmax_at": (None, [C.c_int, C.c_int, _u, _u, C.c_int]),
+    "tm_cuda_tok_embed_at": (None, [C.c_int, C.c_int, _u64, C.c_int, _u, _u, _u, C.c_int]),
+    "tm_cuda_tok_advance": (None, [C.c_int]),
+    "tm_cuda_tok_graph_begin": (C.c_bool, []),
+    "tm_cuda_tok_graph_end": (C.c_int, []),
+    "tm_cuda_tok_graph_launch": (C.c_bool, [C.c_int, _u]),
+    "tm_cuda_tok_graph_destroy": (None, [C.c_int]),
     "tm_cuda_tok_slot_ptr": (_vp, [C.c_int]),
     "tm_cuda_tok_stream": (_vp, []),
 }

@@ -89,3 +89,46 @@ def make_tokens(n: int, vocab: int, seed: int, stream: int = 3) -> np.ndarray:
 # TinyLlama-1.1B and Llama-3-8B projection shapes (out, in) used by the sweeps.
 TINYLLAMA_SHAPES = [(2048, 2048), (256, 2048), (5632, 2048), (2048, 5632), (32000, 2048)]
 LLAMA3_8B_SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336)]
+
+
+# ---- synthetic Llama-style models (random-init weights of a named architecture) -----------
+LLAMA3_8B = dict(L=32, D=4096, H=32, KVH=8, dh=128, F=14336, V=128256, ctx=1024, theta=500000.0, eps=1e-5,
+                 dt_proj=Q4_0, dt_head=Q6_K, dt_embed=Q4_0)
+TINY_CHAIN = dict(L=2, D=256, H=4, KVH=2, dh=64, F=512, V=1024, ctx=96, theta=500000.0, eps=1e-5,
+                  dt_proj=Q4_0, dt_head=Q6_K, dt_embed=Q4_0)
+
+
+def make_llama(cfg: dict, seed: int, progress=None) -> dict:
+    """Random-init weights for a Llama-style decoder, every block tensor inside ONE contiguous
+    uint8 blob (as tensors sit in a mapped .tmq file), 16-byte aligned. Returns
+    {"blob": uint8 array, "<name>": view, ...} with names embed, head, rmsf, l{i}.q/k/v/o/gate/up/down/rms1/rms2.
+    Block contents follow the per-format distributions of make_weights; norm weights are N(1, 0.02)."""
+    L, D, F, V = cfg["L"], cfg["D"], cfg["F"], cfg["V"]
+    QD, KVD = cfg["H"] * cfg["dh"], cfg["KVH"] * cfg["dh"]
+    specs = [("embed", cfg["dt_embed"], V, D), ("head", cfg["dt_head"], V, D)]
+    for l in range(L):
+        for name, n, k in (("q", QD, D), ("k", KVD, D), ("v", KVD, D), ("o", D, QD), ("gate", F, D), ("up", F, D), ("down", D, F)):
+            specs.append((f"l{l}.{name}", cfg["dt_proj"], n, k))
+    offs, cur = {}, 0
+    for name, dt, n, k in specs:
+        offs[name] = cur
+        cur += (weight_bytes(dt, n, k) + 15) // 16 * 16
+    blob = np.zeros(cur + 64, dtype=np.uint8)
+    out = {"blob": blob}
+    for i, (name, dt, n, k) in enumerate(specs):
+        nb = weight_bytes(dt, n, k)
+        view = blob[offs[name]: offs[name] + nb].reshape(n, -1)
+        # large tensors are generated in row slabs to bound the temporary memory
+        step = max(1, (64 << 20) // max(1, nb // n))
+        for r0 in range(0, n, step):
+            r1 = min(n, r0 + step)
+            view[r0:r1] = make_weights(dt, r1 - r0, k, seed, stream=1000 + 64 * i + r0 // step)
+        out[name] = view
+        if progress:
+            progress(name)
+    g = rng_for(seed, 7)
+    out["rmsf"] = (1.0 + 0.02 * g.standard_normal(D)).astype(np.float32)
+    for l in range(L):
+        out[f"l{l}.rms1"] = (1.0 + 0.02 * g.standard_normal(D)).astype(np.float32)
+        out[f"l{l}.rms2"] = (1.0 + 0.02 * g.standard_normal(D)).astype(np.float32)
+    return out

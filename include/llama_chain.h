@@ -228,21 +228,7 @@ public:
             !tm_cuda_tok_upload(SLOT_TOK, 0, toks.data(), sizeof(unsigned) * (size_t)cap))
             throw std::runtime_error("cuda: token slot upload failed");
         if (use_graph_) {
-            const int st[2] = {seen, 0};
-            if (!tm_cuda_tok_upload(SLOT_STATE, 0, st, sizeof st)) throw std::runtime_error("cuda: chain state upload failed");
-            if (graph_ < 0) {
-                // the first token runs eagerly (it also creates every cached resource), the rest replay its capture
-                if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
-                encode_chain_token(cap);
-                if (!tm_cuda_tok_flush()) throw std::runtime_error(std::string("cuda: chain token failed: ") + tm_cuda_last_error());
-                if (!tm_cuda_tok_graph_begin()) throw std::runtime_error("cuda: graph capture failed");
-                encode_chain_token(cap);
-                graph_ = tm_cuda_tok_graph_end();
-                if (graph_ < 0) throw std::runtime_error(std::string("cuda: graph capture failed: ") + tm_cuda_last_error());
-                if (n > 1 && !tm_cuda_tok_graph_launch(graph_, (unsigned)(n - 1))) throw std::runtime_error("cuda: graph launch failed");
-            } else if (!tm_cuda_tok_graph_launch(graph_, (unsigned)n)) {
-                throw std::runtime_error("cuda: graph launch failed");
-            }
+            run_graph(n, /*forced=*/1);
         } else {
             for (int i = 0; i < n; ++i) {
                 if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
@@ -254,6 +240,32 @@ public:
         }
         chain_n_ = n; chain_seen0_ = seen;
     }
+    // Feed n known tokens (a prompt) through the graph lane, one position each; returns the token the
+    // model chooses after the last one. The reference prefills with its batched layer stack
+    // (tensormark/llama.h:6305-6352); on this path a prompt is decoded token by token, which leaves the
+    // K/V caches in exactly the state the chain continues from.
+    int gpu_feed(const int* toks, int n) {
+        if (n <= 0) throw std::invalid_argument("llama: feed needs n >= 1");
+        if (seen + n > d_.ctx) throw std::invalid_argument("llama: prompt exceeds context");
+        if (chain_n_) throw std::runtime_error("llama: chain already running");
+        gpu_token_prologue();
+        const unsigned cap = (unsigned)d_.ctx + 1;
+        std::vector<unsigned> t((size_t)cap, 0xFFFFFFFFu);
+        for (int i = 0; i < n; ++i) {
+            if (toks[i] < 0 || toks[i] >= d_.V) throw std::invalid_argument("llama: token id out of range");
+            t[(size_t)i] = (unsigned)toks[i];
+        }
+        if (!tm_cuda_tok_reserve(SLOT_TOK, sizeof(unsigned) * (size_t)cap) ||
+            !tm_cuda_tok_upload(SLOT_TOK, 0, t.data(), sizeof(unsigned) * (size_t)cap))
+            throw std::runtime_error("cuda: token slot upload failed");
+        run_graph(n, /*forced=*/n);
+        unsigned next = 0;
+        if (!tm_cuda_tok_wait_pending() || !tm_cuda_tok_download(SLOT_TOK, sizeof(unsigned) * (size_t)n, &next, sizeof next))
+            throw std::runtime_error(std::string("cuda: prompt execution failed: ") + tm_cuda_last_error());
+        seen += n;
+        return (int)next;
+    }
+
     // Chosen token i as soon as it has landed, -1 while pending.
     int gpu_chain_poll(int i) const {
         if (i < 0 || i >= chain_n_) return -1;
@@ -284,6 +296,27 @@ public:
     }
 
 private:
+    // Launch the captured token graph `n` times from position `seen`; the first `forced` entries of the
+    // token slot are inputs. The very first call runs one token eagerly (which creates every cached
+    // resource) and captures the second encoding.
+    void run_graph(int n, int forced) {
+        const unsigned cap = (unsigned)d_.ctx + 1;
+        const int st[3] = {seen, 0, forced};
+        if (!tm_cuda_tok_upload(SLOT_STATE, 0, st, sizeof st)) throw std::runtime_error("cuda: chain state upload failed");
+        int left = n;
+        if (graph_ < 0) {
+            if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
+            encode_chain_token(cap);
+            if (!tm_cuda_tok_flush()) throw std::runtime_error(std::string("cuda: chain token failed: ") + tm_cuda_last_error());
+            if (!tm_cuda_tok_graph_begin()) throw std::runtime_error("cuda: graph capture failed");
+            encode_chain_token(cap);
+            graph_ = tm_cuda_tok_graph_end();
+            if (graph_ < 0) throw std::runtime_error(std::string("cuda: graph capture failed: ") + tm_cuda_last_error());
+            left -= 1;
+        }
+        if (left > 0 && !tm_cuda_tok_graph_launch(graph_, (unsigned)left)) throw std::runtime_error("cuda: graph launch failed");
+    }
+
     struct Handle { int id = -1; uint64_t woff = 0; };
     struct Registered { Handle q, k, v, o, gate, up, down; };
     static bool same_buffer(const Handle& a, const Handle& b, const Handle& c) { return a.id == b.id && b.id == c.id; }

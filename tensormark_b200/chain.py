@@ -26,6 +26,7 @@ def load() -> C.CDLL:
         L.tmchain_set_seen.argtypes = [C.c_void_p, C.c_int]
         L.tmchain_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.tmchain_greedy.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.tmchain_feed.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.tmchain_chain_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.tmchain_chain_poll.argtypes = [C.c_void_p, C.c_int]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
@@ -75,6 +76,13 @@ class Chain:
         logits = np.empty(self.cfg["V"], np.float32)
         self._check(self.L.tmchain_greedy(self.h, int(first), n, out.ctypes.data, logits.ctypes.data, int(graph)))
         return out, logits
+
+    def feed(self, tokens) -> int:
+        """Run known tokens (a prompt) through the graph lane; returns the token chosen after the last one."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        nxt = self.L.tmchain_feed(self.h, t.ctypes.data, t.size)
+        self._check(nxt >= 0)
+        return nxt
 
     def chain_begin(self, first: int, n: int, graph: bool = True):
         self._check(self.L.tmchain_chain_begin(self.h, int(first), n, int(graph)))

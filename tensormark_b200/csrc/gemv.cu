@@ -48,7 +48,7 @@ struct GemvParams {
     const float* x;
     float* y;
     uint32_t N, K, row_bytes;
-    uint32_t stages, rows_per_warp;
+    uint32_t stages, rows_per_cta;
     // optional fusions (decode chain): a transform of x while it is staged, and y += instead of y =
     const float* x2;            // x_op 1: rmsnorm weights; x_op 2: the "up" vector
     float eps;
@@ -114,10 +114,14 @@ template <int DT> __device__ __forceinline__ int lane_valid(int lane, int units_
 
 // Shared memory: [x units: one per lane and step][mbarriers][stages]
 //
-// Work split: the rows are cut into one contiguous range per warp of the grid
-// (rows_per_warp = ceil(N / warps)), so every warp streams one contiguous piece of
-// the tensor and the ranges differ by at most one row. A warp walks its range in
-// groups of R rows; a group times one step of the row is one ring item.
+// Work split: the rows are cut into one contiguous range per CTA (rows_per_cta =
+// ceil(N / grid)). Inside a CTA the warps form teams of `nchunks` warps, one warp per step of
+// the row: a warp keeps the activations of ITS step in registers for the whole kernel and
+// streams that step of the team's rows, R rows per ring item; teams take the CTA's row groups
+// round-robin. With one step per row (K <= 2048) every warp is its own team and stores y
+// directly; with several steps the warps leave per-step partial sums in shared memory and the
+// CTA adds them in step order after one barrier. Which mode runs depends on K only, never on
+// N, so a row's bits are the same in a segmented and in a separate launch.
 template <int DT, int R, int kWarps>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const GemvParams p) {
     using L = Lane<DT>;
@@ -133,10 +137,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     uint64_t* mybar = bars + warp * kMaxStages;
     uint8_t* mystage = stages + (size_t)warp * S * R * ROWCAP;
 
-    const uint32_t gwarp = blockIdx.x * kWarps + warp;
-    const uint32_t row_lo = min(p.N, gwarp * p.rows_per_warp), row_hi = min(p.N, row_lo + p.rows_per_warp);
-    const uint32_t ngroups = (row_hi - row_lo + R - 1) / R;
-    const uint32_t items = ngroups * nchunks;
+    float* partial = reinterpret_cast<float*>(stages + (size_t)kWarps * S * R * ROWCAP);   // [rows_per_cta][nchunks], only when nchunks > 1
+
+    const uint32_t teams = kWarps / nchunks;               // >= 1 (the launcher guarantees nchunks <= kWarps)
+    const uint32_t team = (uint32_t)warp / nchunks, myc = (uint32_t)warp % nchunks;
+    const uint32_t cta_lo = min(p.N, blockIdx.x * p.rows_per_cta), cta_hi = min(p.N, cta_lo + p.rows_per_cta);
+    const uint32_t row_first = cta_lo + team * R, grp_stride = teams * R;
+    const uint32_t items = (team < teams && row_first < cta_hi) ? (cta_hi - row_first + grp_stride - 1) / grp_stride : 0;
 
     if (lane == 0) {
         for (uint32_t s = 0; s < S; ++s) mbar_init(&mybar[s], 1);
@@ -144,16 +151,16 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     }
     __syncwarp();
 
-    // Issue cursor (same value in every lane): next item = rows [irow, irow+R) x step ic.
-    uint32_t irow = row_lo, ic = 0, issued = 0;
+    // Issue cursor (same value in every lane): next item = rows [irow, irow+R) x this warp's step.
+    const uint32_t off = myc * (uint32_t)L::STEP_BYTES;
+    const uint32_t bytes = p.row_bytes > off ? min((uint32_t)L::STEP_BYTES, p.row_bytes - off) : 0u;
+    uint32_t irow = row_first, issued = 0;
     auto issue = [&](uint32_t slot) {
-        const uint32_t rows = min((uint32_t)R, row_hi - irow);
-        const uint32_t off = ic * (uint32_t)L::STEP_BYTES;
-        const uint32_t bytes = min((uint32_t)L::STEP_BYTES, p.row_bytes - off);
+        const uint32_t rows = min((uint32_t)R, cta_hi - irow);
         if (lane == 0) mbar_expect_tx(&mybar[slot], rows * bytes);
         if ((uint32_t)lane < rows)                          // one row copy per lane, issued in parallel
             bulk_g2s(mystage + ((size_t)slot * R + lane) * ROWCAP, row_ptr(p, irow + lane) + off, bytes, &mybar[slot]);
-        if (++ic == nchunks) { ic = 0; irow += R; }
+        irow += grp_stride;
         ++issued;
     };
     for (uint32_t s = 0; s < S && issued < items; ++s) issue(s);
@@ -257,69 +264,80 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
 
     // ---- consume -------------------------------------------------------------
     typename L::X xr;
-    float acc[R];
     bool dead = false;
-    uint32_t slot = 0, phase = 0, c = 0, row0 = row_lo;
+    uint32_t slot = 0, phase = 0, row0 = row_first;
+    if (items) load_x_unit<DT>(xr, units, myc * 32u + (uint32_t)lane);
+    const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - myc * L::STEP_W);
+    const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
     for (uint32_t t = 0; t < items; ++t) {
-        if (c == 0) {
+        float acc[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] = 0.f;
-        }
-        if (nchunks > 1 || t == 0) load_x_unit<DT>(xr, units, c * 32u + (uint32_t)lane);
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
         if (!mbar_wait(&mybar[slot], phase)) { dead = true; break; }
-        const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - c * L::STEP_W);
-        const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
         const uint8_t* st = mystage + (size_t)slot * R * ROWCAP;
-        const uint32_t rows = min((uint32_t)R, row_hi - row0);
+        const uint32_t rows = min((uint32_t)R, cta_hi - row0);
         if (L::LANE_UNITS == 2 ? valid > 0 : true) {
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 if ((uint32_t)r < rows) {                   // warp-uniform: rows past the range were never copied
                     const uint8_t* rowp = st + r * ROWCAP + (L::LANE_UNITS == 2 ? lane * L::LANE_BYTES : 0);
-                    acc[r] += L::dot(rowp, xr, lane, valid);
+                    acc[r] = L::dot(rowp, xr, lane, valid);
                 }
             }
         }
         __syncwarp();                                       // every lane is done with this stage
         if (issued < items) issue(slot);
         if (++slot == S) { slot = 0; phase ^= 1u; }
-        if (++c == nchunks) {
-            // Sum over lanes. The butterfly order (xor 16, 8, 4, 2, 1) is the same for every
-            // R, so a row's bits do not depend on how rows were grouped; with R > 1 the first
-            // stages also fold the R rows onto disjoint lanes to save shuffles.
-            float v;
-            int my_row;
-            if constexpr (R == 4) {
-                const bool h16 = lane & 16, h8 = lane & 8;
-                float k0 = h16 ? acc[2] : acc[0], k1 = h16 ? acc[3] : acc[1];
-                const float s0 = h16 ? acc[0] : acc[2], s1 = h16 ? acc[1] : acc[3];
-                k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
-                k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-                v = h8 ? k1 : k0;
-                const float sv = h8 ? k0 : k1;
-                v += __shfl_xor_sync(0xffffffffu, sv, 8);
-                my_row = (h16 ? 2 : 0) + (h8 ? 1 : 0);
-            } else if constexpr (R == 2) {
-                const bool h16 = lane & 16;
-                v = h16 ? acc[1] : acc[0];
-                const float sv = h16 ? acc[0] : acc[1];
-                v += __shfl_xor_sync(0xffffffffu, sv, 16);
-                v += __shfl_xor_sync(0xffffffffu, v, 8);
-                my_row = h16 ? 1 : 0;
+        // Sum over lanes. The butterfly order (xor 16, 8, 4, 2, 1) is the same for every R, so a
+        // row's bits do not depend on how rows were grouped; with R > 1 the first stages also
+        // fold the R rows onto disjoint lanes to save shuffles.
+        float v;
+        int my_row;
+        if constexpr (R == 4) {
+            const bool h16 = lane & 16, h8 = lane & 8;
+            float k0 = h16 ? acc[2] : acc[0], k1 = h16 ? acc[3] : acc[1];
+            const float s0 = h16 ? acc[0] : acc[2], s1 = h16 ? acc[1] : acc[3];
+            k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+            k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+            v = h8 ? k1 : k0;
+            const float sv = h8 ? k0 : k1;
+            v += __shfl_xor_sync(0xffffffffu, sv, 8);
+            my_row = (h16 ? 2 : 0) + (h8 ? 1 : 0);
+        } else if constexpr (R == 2) {
+            const bool h16 = lane & 16;
+            v = h16 ? acc[1] : acc[0];
+            const float sv = h16 ? acc[0] : acc[1];
+            v += __shfl_xor_sync(0xffffffffu, sv, 16);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            my_row = h16 ? 1 : 0;
+        } else {
+            v = acc[0];
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            my_row = 0;
+        }
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) {
+            const uint32_t row = row0 + (uint32_t)my_row;
+            if (nchunks == 1) {
+                if (p.accumulate) v += p.y[row];            // residual add folded into the store
+                p.y[row] = v;
             } else {
-                v = acc[0];
-                v += __shfl_xor_sync(0xffffffffu, v, 16);
-                v += __shfl_xor_sync(0xffffffffu, v, 8);
-                my_row = 0;
+                partial[(size_t)(row - cta_lo) * nchunks + myc] = v;
             }
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) {
-                if (p.accumulate) v += p.y[row0 + my_row];          // residual add folded into the store
-                p.y[row0 + my_row] = v;
-            }
-            c = 0; row0 += R;
+        }
+        row0 += grp_stride;
+    }
+    if (nchunks > 1) {
+        // every step's partial sum of every row of this CTA is in shared memory: add them in step order
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < cta_hi - cta_lo; i += blockDim.x) {
+            float v = partial[(size_t)i * nchunks];
+            for (uint32_t cc = 1; cc < nchunks; ++cc) v += partial[(size_t)i * nchunks + cc];
+            if (p.accumulate) v += p.y[cta_lo + i];
+            p.y[cta_lo + i] = v;
         }
     }
     if (dead) {
@@ -455,26 +473,14 @@ template <int DT> size_t stream_fixed_smem(unsigned K) {
     const size_t nchunks = (K + L::STEP_W - 1) / L::STEP_W;
     return ((nchunks * 32 * L::XW * 4 + 127) / 128) * 128 + ((kMaxWarps * kMaxStages * 8 + 127) / 128) * 128 + 128;
 }
-// Deepest ring (<= kMaxStages) that fits next to x; 0 when not even two stages fit.
-template <int DT> unsigned stream_stages(unsigned K, int R, int warps, unsigned ctas_per_sm) {
-    using L = Lane<DT>;
-    const size_t fixed = stream_fixed_smem<DT>(K), per = (size_t)warps * R * L::STEP_BYTES;
-    const size_t limit = ctas_per_sm > 1 ? (kSmemLimit + 1024) / ctas_per_sm - 1024 : kSmemLimit;   // 1 KB per CTA is reserved by the system
-    if (fixed + 2 * per > limit) return 0;
-    const size_t s = (limit - fixed) / per;
-    return (unsigned)(s > (size_t)kMaxStages ? kMaxStages : s);
-}
-
 int env_int(const char* name, int dflt) {
     const char* e = std::getenv(name);
     return e && *e ? std::atoi(e) : dflt;
 }
 
 template <int DT, int R, int kWarps>
-bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, cudaStream_t st) {
-    using L = Lane<DT>;
+bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, cudaStream_t st) {
     p.stages = stages;
-    const size_t smem = stream_fixed_smem<DT>(p.K) + (size_t)p.stages * kWarps * R * L::STEP_BYTES;
     static bool attr_set = false;
     static const bool pdl = env_int("TM_GEMV_PDL", 1) != 0;     // A/B knob: 0 launches without programmatic serialization
     if (!attr_set) {
@@ -496,45 +502,54 @@ bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, cudaStream_t 
 template <int DT>
 bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
     using L = Lane<DT>;
-    if (aligned) {
+    const unsigned nchunks = (p.K + L::STEP_W - 1) / L::STEP_W;
+    if (aligned && nchunks <= (unsigned)kMaxWarps) {
         const unsigned sms = (unsigned)device_sm_count();
         static const int force_r = env_int("TM_GEMV_R", 0), force_s = env_int("TM_GEMV_STAGES", 0),
                          force_w = env_int("TM_GEMV_WARPS", 0);
-        // One 16-warp CTA per SM; matrices too short to give every one of those warps a row use
-        // 8-warp CTAs (more CTAs share the staging of x, and they leave half of the register file
-        // to the next kernel of the stream). TM_GEMV_WARPS overrides.
-        int warps_cta = p.N >= 16u * sms ? 16 : 8;
-        if (force_w == 8 || force_w == 16) warps_cta = force_w;
-        const unsigned ctas_per_sm = 1;
-        unsigned grid = (p.N + warps_cta - 1) / warps_cta;
-        if (grid > sms * ctas_per_sm) grid = sms * ctas_per_sm;
-        const unsigned warps = grid * warps_cta;
-        p.rows_per_warp = (p.N + warps - 1) / warps;
-        // Rows per ring item: as many as the warp's range offers (x registers are reused
-        // across them), at most 4, and few enough that at least two stages fit.
-        int R = p.rows_per_warp >= 4 ? 4 : p.rows_per_warp >= 2 ? 2 : 1;
+        // One 16-warp CTA per SM; matrices with fewer than 8 rows per SM use 8-warp CTAs when the row
+        // has few enough steps (measured on the ten-GEMV sweep: 65 vs 71 us per pass). TM_GEMV_WARPS overrides.
+        int warps_cta = (p.N >= 8u * sms || nchunks > 8) ? 16 : 8;
+        if ((force_w == 8 && nchunks <= 8) || force_w == 16) warps_cta = force_w;
+        const unsigned teams = (unsigned)warps_cta / nchunks;
+        unsigned grid = (p.N + teams - 1) / teams;
+        if (grid > sms) grid = sms;
+        p.rows_per_cta = (p.N + grid - 1) / grid;
+        grid = (p.N + p.rows_per_cta - 1) / p.rows_per_cta;
+        const unsigned rows_per_team = (p.rows_per_cta + teams - 1) / teams;
+        // Rows per ring item: as many as a team's share offers (the step's activations stay in
+        // registers across them), at most 4, and few enough that at least two stages fit.
+        int R = rows_per_team >= 4 ? 4 : rows_per_team >= 2 ? 2 : 1;
         if (force_r == 1 || force_r == 2 || force_r == 4) R = force_r;
-        while (R > 1 && stream_stages<DT>(p.K, R, warps_cta, ctas_per_sm) < 2) R >>= 1;
-        unsigned S = stream_stages<DT>(p.K, R, warps_cta, ctas_per_sm);
+        const size_t fixed = stream_fixed_smem<DT>(p.K) + (nchunks > 1 ? (size_t)p.rows_per_cta * nchunks * 4 : 0);
+        auto fit = [&](int r) -> unsigned {
+            const size_t per = (size_t)warps_cta * r * L::STEP_BYTES;
+            if (fixed + 2 * per > kSmemLimit) return 0u;
+            const size_t s = (kSmemLimit - fixed) / per;
+            return (unsigned)(s > (size_t)kMaxStages ? kMaxStages : s);
+        };
+        while (R > 1 && fit(R) < 2) R >>= 1;
+        unsigned S = fit(R);
         if (S >= 2) {
-            // No deeper than the warp has items, and by default no deeper than 3: the ring only
-            // has to cover the DRAM latency, and a small footprint helps kernels overlap.
-            const unsigned items = ((p.rows_per_warp + R - 1) / R) * ((p.K + L::STEP_W - 1) / L::STEP_W);
+            // No deeper than a warp has items, and by default no deeper than 3: the ring only has
+            // to cover the DRAM latency.
+            const unsigned items = (rows_per_team + R - 1) / R;
             unsigned cap = force_s >= 2 ? (unsigned)force_s : 3u;
             if (cap > (unsigned)kMaxStages) cap = kMaxStages;
             if (S > cap) S = cap;
             if (S > items) S = items < 1 ? 1 : items;
+            const size_t smem = fixed + (size_t)S * warps_cta * R * L::STEP_BYTES;
             if (warps_cta == 16) {
                 switch (R) {
-                    case 4: return launch_stream_r<DT, 4, 16>(p, S, grid, st);
-                    case 2: return launch_stream_r<DT, 2, 16>(p, S, grid, st);
-                    default: return launch_stream_r<DT, 1, 16>(p, S, grid, st);
+                    case 4: return launch_stream_r<DT, 4, 16>(p, S, grid, smem, st);
+                    case 2: return launch_stream_r<DT, 2, 16>(p, S, grid, smem, st);
+                    default: return launch_stream_r<DT, 1, 16>(p, S, grid, smem, st);
                 }
             }
             switch (R) {
-                case 4: return launch_stream_r<DT, 4, 8>(p, S, grid, st);
-                case 2: return launch_stream_r<DT, 2, 8>(p, S, grid, st);
-                default: return launch_stream_r<DT, 1, 8>(p, S, grid, st);
+                case 4: return launch_stream_r<DT, 4, 8>(p, S, grid, smem, st);
+                case 2: return launch_stream_r<DT, 2, 8>(p, S, grid, smem, st);
+                default: return launch_stream_r<DT, 1, 8>(p, S, grid, smem, st);
             }
         }
     }

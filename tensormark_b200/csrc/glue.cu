@@ -112,7 +112,8 @@ __global__ void bias_kernel(float* __restrict__ y, const float* __restrict__ bia
 
 // One embedding row chosen by a token id that lives on the device; the sentinel
 // 0xFFFFFFFF (a chain slot not yet written) gives zeros.
-// `st` (optional) is a device-resident chain state {position, token index}: when given, the index comes from it.
+// `st` (optional) is a device-resident chain state {position, token index, forced count}: when given, the index comes
+// from it; entries below the forced count are prompt tokens that the chooser must not overwrite.
 __global__ void embed_row_kernel(const uint32_t* __restrict__ tok, uint32_t idx, const uint8_t* __restrict__ W,
                                  float* __restrict__ x, uint32_t D, uint32_t row_bytes, unsigned dtype,
                                  const int* __restrict__ st) {
@@ -142,7 +143,10 @@ __global__ void __launch_bounds__(256) choose_kernel(const float* __restrict__ x
                                                       unsigned long long* __restrict__ scratch /* [0]=key, [1]=done */,
                                                       const int* __restrict__ st) {
     __shared__ unsigned long long best_s[8];
-    if (st) idx = (uint32_t)st[1] + 1u;                     // chain: the token chosen now is fed by the next step
+    if (st) {
+        idx = (uint32_t)st[1] + 1u;                         // chain: the token chosen now is fed by the next step
+        if (idx < (uint32_t)st[2]) return;                  // ... unless that entry is a forced (prompt) token
+    }
     unsigned long long best = pack_key(-CUDART_INF_F, 0);
     const uint32_t base = hash32(seed * 0x9e3779b9u + idx * 0x85ebca6bu + 0x1234567u);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {

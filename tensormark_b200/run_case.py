@@ -21,9 +21,60 @@ from . import lib, synth
 NAMES = {v: k for k, v in synth.DTYPE_NAMES.items()}
 
 
+def run_chain(args, L, torch) -> None:
+    """Greedy decode chain of a random-init model: `--prompt` tokens fed one by one, then `--steps` chosen on the GPU."""
+    import time
+
+    from . import chain
+    cfg = dict(synth.LLAMA3_8B if args.model == "llama3-8b" else synth.TINY_CHAIN)
+    cfg["ctx"] = max(cfg["ctx"], args.prompt + args.steps + 1) if args.model == "llama3-8b" else cfg["ctx"]
+    t0 = time.perf_counter()
+    w = synth.make_llama(cfg, seed=5)
+    t_gen = time.perf_counter() - t0
+    m = chain.Chain(cfg, w)
+    prompt = synth.make_tokens(args.prompt, cfg["V"], seed=5).astype(np.int32)
+    stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
+    t0 = time.perf_counter()
+    if args.no_graph:
+        last = None
+        for t in prompt:
+            last = m.forward(int(t))
+        nxt = int(np.argmax(last))
+    else:
+        nxt = m.feed(prompt)
+    t_prompt = time.perf_counter() - t0
+    launches0 = int(L.tm_cuda_launch_count())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    t0 = time.perf_counter()
+    m.chain_begin(nxt, args.steps, graph=not args.no_graph)
+    e1.record(stream)
+    toks = m.chain_end(args.steps)
+    wall = time.perf_counter() - t0
+    dev_ms = e0.elapsed_time(e1)
+    QD, KVD = cfg["H"] * cfg["dh"], cfg["KVH"] * cfg["dh"]
+    per_layer = sum(synth.weight_bytes(cfg["dt_proj"], n, k) for n, k in
+                    ((QD, cfg["D"]), (KVD, cfg["D"]), (KVD, cfg["D"]), (cfg["D"], QD), (cfg["F"], cfg["D"]), (cfg["F"], cfg["D"]), (cfg["D"], cfg["F"])))
+    wbytes = cfg["L"] * per_layer + synth.weight_bytes(cfg["dt_head"], cfg["V"], cfg["D"])
+    print(json.dumps({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps,
+                      "lane": "host call per op" if args.no_graph else "CUDA graph per token",
+                      "decode_tok_per_s": round(args.steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / args.steps, 4),
+                      "wall_tok_per_s": round(args.steps / wall, 1),
+                      "prompt_tok_per_s": round(args.prompt / t_prompt, 1),
+                      "weight_bytes_per_token": wbytes,
+                      "weight_GBps": round(wbytes * args.steps / (dev_ms * 1e-3) / 1e9, 1),
+                      "kernels_encoded_per_chain_call": int(L.tm_cuda_launch_count()) - launches0,
+                      "first_tokens": [int(t) for t in toks[:8]], "model_build_s": round(t_gen, 1)}))
+    m.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["gemv", "gemm", "dequant"], default="gemv")
+    ap.add_argument("--op", choices=["gemv", "gemm", "dequant", "chain"], default="gemv")
+    ap.add_argument("--model", choices=["llama3-8b", "tiny"], default="llama3-8b", help="architecture of --op chain")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--no-graph", action="store_true", help="--op chain: one host call per op instead of the graph lane")
     ap.add_argument("--dtype", default="Q8_0", choices=sorted(NAMES))
     ap.add_argument("--m", type=int, default=2000)
     ap.add_argument("--n", type=int, default=32000)
@@ -38,6 +89,9 @@ def main() -> None:
     torch.cuda.set_device(0)
     L = lib.load()
     lib.check(L.tm_cuda_init(0), "tm_cuda_init")
+    if args.op == "chain":
+        run_chain(args, L, torch)
+        return
     dt = NAMES[args.dtype]
     n, k, m = args.n, args.k, args.m
     W = synth.make_weights(dt, n, k, seed=1).reshape(-1)

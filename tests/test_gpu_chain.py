@@ -70,6 +70,24 @@ def test_forward_matches_cpu_chain_teacher_forced(cuda, orc, tiny):
     gpu.close()
 
 
+def test_prompt_feed_equals_forward_loop(cuda, tiny):
+    cfg, w = tiny
+    toks = synth.make_tokens(20, cfg["V"], seed=9).astype(np.int32)
+    a = chain.Chain(cfg, w)
+    last = None
+    for t in toks:
+        last = a.forward(int(t))
+    nxt_loop = int(np.argmax(last))
+    cont_loop, _ = a.greedy(nxt_loop, 6, graph=False)
+    a.close()
+    b = chain.Chain(cfg, w)
+    nxt = b.feed(toks)
+    assert b.seen == len(toks) and nxt == nxt_loop
+    cont, _ = b.greedy(nxt, 6, graph=True)
+    assert list(cont) == list(cont_loop)
+    b.close()
+
+
 def test_chain_polling_and_argument_errors(cuda, tiny):
     cfg, w = tiny
     gpu = chain.Chain(cfg, w, shared_mapping=False)          # one device copy per tensor: no fused segments

@@ -42,13 +42,18 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from tensormark_b200 import synth  # noqa: E402
+from tensormark_b200 import shard, synth  # noqa: E402
 
 SWEEP = [(dt, shape) for dt in (synth.Q8_0, synth.Q4_1) for shape in synth.TINYLLAMA_SHAPES]
 SEEDS = {synth.Q8_0: 1, synth.Q4_1: 2}
 COPIES = 3
-SHARD_MIN_ROWS = 4096          # matrices with fewer rows stay on one GPU (replicated)
 WORKLOAD = "Q8_0+Q4_1 decode GEMV sweep, TinyLlama-1.1B projection shapes (BASELINE config 2)"
+
+
+def note(rank: int, msg: str) -> None:
+    """Progress marker on stderr (TM_BENCH_VERBOSE=1): which phase each rank has reached."""
+    if os.environ.get("TM_BENCH_VERBOSE") == "1":
+        print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
 
 
 def sweep_bytes() -> int:
@@ -167,6 +172,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     import torch.distributed as dist
     from tensormark_b200 import lib
 
+    # Libraries (NCCL's version banner among them) write to stdout: keep fd 1 for the one JSON line.
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
+
     torch.cuda.set_device(local_rank)
     L = lib.load()
     lib.check(L.tm_cuda_init(local_rank), "tm_cuda_init")
@@ -179,9 +189,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- resident inputs: this rank's row shard of every matrix, COPIES times
     mats = []
     for dt, (n, k) in SWEEP:
-        sharded = world > 1 and n >= SHARD_MIN_ROWS and n % world == 0
+        sharded = shard.is_sharded(n, world)
         W = synth.make_weights(dt, n, k, SEEDS[dt])
-        lo, hi = (rank * (n // world), (rank + 1) * (n // world)) if sharded else (0, n)
+        lo, hi = shard.row_range(n, rank, world)
         Wl = np.ascontiguousarray(W[lo:hi]).reshape(-1)
         copies = []
         for _ in range(COPIES):
@@ -195,6 +205,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     stream = torch.cuda.Stream()
     sp = C.c_void_p(stream.cuda_stream)
+    note(rank, "inputs resident")
 
     def launch_step(copy: int):
         for m in mats:
@@ -209,6 +220,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     with torch.cuda.stream(stream):
         launch_step(0)
         stream.synchronize()
+        note(rank, "first eager step done")
         before = L.tm_cuda_launch_count()
         launch_step(0)
         launches_per_step = int(L.tm_cuda_launch_count() - before)
@@ -221,6 +233,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     with torch.cuda.graph(g, stream=stream):
                         launch_step(c)
                     graphs.append(g)
+                note(rank, "graphs captured")
             except Exception as e:      # capture refused (e.g. a collective that cannot be captured): plain launches
                 if rank == 0:
                     print(f"[bench] graph capture unavailable, using stream launches: {e}", file=sys.stderr)
@@ -242,6 +255,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for i in range(args.warmup):
             step(i)
         barrier()
+        note(rank, "warm-up done")
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local_rank) as clk:
             ev0.record(stream)
@@ -250,6 +264,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             ev1.record(stream)
             barrier()
         ms = ev0.elapsed_time(ev1)
+    note(rank, f"timed region done: {ms:.3f} ms")
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -358,11 +373,23 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "clocks": clocks,
             "per_shape": per_shape,
         }
+    if line is not None:
+        os.write(out_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
+        # Graphs that captured collectives hold the communicator: release them before the group is
+        # destroyed (destroying first waits for ever), and bound the teardown now that the line is out.
+        graphs.clear()
+        import gc, threading
+        gc.collect()
+        torch.cuda.synchronize()
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
+        note(rank, "teardown")
         dist.barrier()
         dist.destroy_process_group()
-    if line is not None:
-        print(json.dumps(line), flush=True)
+        guard.cancel()
+        note(rank, "done")
 
 
 def main():

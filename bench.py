@@ -20,10 +20,13 @@ second: sum over the sweep of (block payload + 4*in + 4*out) divided by device t
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
   cpu_baseline  the CPU restatement of the reference's dot path on the host cores.
 
-With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the large
-matrices are sharded by output rows, every rank computes its rows and the outputs
-are all-gathered with NCCL; the two small shapes stay replicated. Total work is
-fixed, so scaling is "strong".
+With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs
+the whole sweep on its own activation vectors: N independent decode streams, no
+collective on the data path, per-GPU work fixed ("weak" scaling). These projection
+shapes are small enough that one GPU finishes each GEMV in 2-12 us, which is less than
+one all-gather costs, so they stay whole on a GPU. --shard selects the other layout for
+comparison: matrices of >= 4096 rows split by output rows over the ranks and their
+outputs all-gathered with NCCL; total work is then fixed ("strong" scaling).
 """
 from __future__ import annotations
 
@@ -186,12 +189,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     def vp(t):
         return C.c_void_p(t.data_ptr())
 
-    # ---- resident inputs: this rank's row shard of every matrix, COPIES times
+    shard_world = world if args.shard else 1
+    # ---- resident inputs: every matrix (this rank's row shard of it with --shard), COPIES times
     mats = []
     for dt, (n, k) in SWEEP:
-        sharded = shard.is_sharded(n, world)
+        sharded = shard.is_sharded(n, shard_world)
         W = synth.make_weights(dt, n, k, SEEDS[dt])
-        lo, hi = shard.row_range(n, rank, world)
+        lo, hi = shard.row_range(n, rank if sharded else 0, shard_world if sharded else 1)
         Wl = np.ascontiguousarray(W[lo:hi]).reshape(-1)
         copies = []
         for _ in range(COPIES):
@@ -270,7 +274,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     total = sweep_bytes()
-    value = total * args.steps / (ms * 1e-3) / 1e9
+    replicas = 1 if args.shard else world
+    value = replicas * total * args.steps / (ms * 1e-3) / 1e9
 
     # ---- correctness guard on what was just timed (cheap: sampled rows against numpy fp64)
     if rank == 0:
@@ -357,11 +362,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line = {
             "metric": "decode_gemv_algorithmic_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "gemvs_per_step": len(SWEEP), "bytes_per_step": total,
+            "scaling": "strong" if args.shard else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "gemvs_per_step": len(SWEEP), "bytes_per_step": total * replicas,
                        "l2": f"weights rotate over {COPIES} copies per matrix ({COPIES * 160} MB), more than 2x the 126 MB L2 between reuses",
                        "launch": "one CUDA graph per step" if graphs else "stream launches",
-                       "sharding": "rows over ranks + NCCL all-gather for matrices with >= 4096 rows" if world > 1 else "single GPU"},
+                       "sharding": ("single GPU" if world == 1 else
+                                    "rows over ranks + NCCL all-gather for matrices with >= 4096 rows" if args.shard else
+                                    "none: one independent sweep per GPU, no data-path collective")},
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                          "peak_kind": peak_kind + " STREAM-style copy",
                          "traffic": (traffic or {}).get("dram_bytes_per_launch"),
@@ -399,6 +406,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--shard", action="store_true", help="N > 1: split large matrices by rows over the ranks and all-gather (strong scaling)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -207,7 +207,24 @@ void tm_cuda_tok_advance(int stateslot);                         /* position += 
 bool tm_cuda_tok_graph_begin(void);
 int tm_cuda_tok_graph_end(void);
 bool tm_cuda_tok_graph_launch(int id, unsigned times);
-void tm_cuda_tok_graph_destroy(int id);
+void tm_cuda_tok_graph_destroy(int id);                         /* id < 0: every graph of the lane */
+
+/* ---- row-sharded models: one process per GPU -------------------------------------------------
+ * No counterpart in the reference, which runs on one GPU. A model whose FFN and LM-head rows are
+ * spread over `world` GPUs gathers each sharded GEMV's output with tm_cuda_tok_all_gather, an
+ * ncclAllGather on the lane's stream (captured into token graphs like any other op). NCCL is bound
+ * at run time, on the first call that needs it. Rank 0 makes the id (tm_cuda_comm_id_bytes() bytes),
+ * the caller carries it to the other ranks, and every rank calls tm_cuda_comm_init after
+ * tm_cuda_init(device). tm_cuda_comm_destroy first destroys every graph of the lane. */
+size_t tm_cuda_comm_id_bytes(void);
+bool tm_cuda_comm_unique_id(void* out);
+bool tm_cuda_comm_init(int rank, int world, const void* id_bytes);
+int tm_cuda_comm_rank(void);
+int tm_cuda_comm_world(void);
+bool tm_cuda_comm_destroy(void);
+/* dst[dst_off + r*count*4 ...) on every rank <- count floats at src[src_off] of rank r. In place when
+ * src is this rank's slice of dst. Offsets and count*4 are multiples of 16. world == 1: a copy. */
+void tm_cuda_tok_all_gather(int srcslot, size_t src_off, int dstslot, size_t dst_off, unsigned count);
 
 /* Device address of a slot (NULL when unreserved); for resident callers and tests. */
 void* tm_cuda_tok_slot_ptr(int slot);

@@ -51,13 +51,19 @@ struct CudaLlamaDesc {
     // gate|up run as one segmented GEMV each (tensormark/llama.h:5852-5881). Null: one copy per tensor.
     const void* map_base = nullptr;
     size_t map_size = 0;
+    // Row sharding over the GPUs of one box, one process per GPU (no counterpart in the reference).
+    // With world > 1 this rank holds rows [rank*R/world, (rank+1)*R/world) of gate, up, down and the
+    // LM head; every sharded GEMV is followed by tm_cuda_tok_all_gather, so the residual stream, the
+    // attention block (q/k/v/o, norms, rope, K/V cache) and the chosen tokens are replicated on every
+    // rank. tm_cuda_comm_init must have run. F, D and V must divide by world into multiples of 4 rows.
+    int rank = 0, world = 1;
 };
 
 class CudaLlama {
 public:
     enum {
         SLOT_X = 0, SLOT_H = 1, SLOT_QKV = 2, SLOT_AO = 3, SLOT_H2 = 4, SLOT_H2S = 5, SLOT_GU = 6, SLOT_DN = 7,
-        SLOT_XF = 8, SLOT_LOGITS = 9, SLOT_PROBS = 10, SLOT_TOK = 11, SLOT_BIAS = 12, SLOT_STATE = 13,
+        SLOT_XF = 8, SLOT_LOGITS = 9, SLOT_PROBS = 10, SLOT_TOK = 11, SLOT_BIAS = 12, SLOT_STATE = 13, SLOT_ACT = 14,
         SLOT_KC = 100, SLOT_VC = 200
     };
 
@@ -66,6 +72,9 @@ public:
             d.H % d.KVH || (d.dh & 1) || !d.embed || !d.head || !d.rmsf || !d.layers)
             throw std::invalid_argument("llama: invalid model description");
         if (d.L >= 100) throw std::invalid_argument("llama: the slot table holds at most 99 layers");
+        if (d.world < 1 || d.rank < 0 || d.rank >= d.world) throw std::invalid_argument("llama: invalid rank / world");
+        if (d.world > 1 && (d.F % (4 * d.world) || d.D % (4 * d.world) || d.V % (4 * d.world)))
+            throw std::invalid_argument("llama: F, D and V must split over the ranks into multiples of 4 rows");
         if (!tm_cuda_init(-1)) throw std::runtime_error(std::string("cuda: ") + tm_cuda_last_error());
         logits_.resize((size_t)d.V);
     }
@@ -84,31 +93,38 @@ public:
     void gpu_token_prologue() {
         if (ready_) return;
         const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh;
-        auto reg = [&](const void* p, unsigned dt, int rows, int cols) {
+        if (d_.world > 1 && (tm_cuda_comm_world() != d_.world || tm_cuda_comm_rank() != d_.rank))
+            throw std::runtime_error("llama: the communicator does not match the model's rank / world");
+        auto reg_rows = [&](const void* p, unsigned dt, int rows, int cols, bool sharded) {
             Handle h{};
-            const size_t bytes = tm_cuda_weight_bytes(dt, (size_t)rows, (size_t)cols);
-            if (!bytes) throw std::invalid_argument("llama: tensor shape is not whole blocks");
-            h.id = tm_cuda_tok_wbuf(p, bytes, d_.map_base, d_.map_size, d_.map_base ? 1 : 0, &h.woff);
+            const int mine = sharded ? rows / d_.world : rows;
+            const size_t row_bytes = tm_cuda_weight_bytes(dt, 1, (size_t)cols);
+            if (!row_bytes) throw std::invalid_argument("llama: tensor shape is not whole blocks");
+            const uint8_t* first = (const uint8_t*)p + (sharded ? (size_t)d_.rank * (size_t)mine * row_bytes : 0);
+            h.id = tm_cuda_tok_wbuf(first, (size_t)mine * row_bytes, d_.map_base, d_.map_size, d_.map_base ? 1 : 0, &h.woff);
             if (h.id < 0) throw std::runtime_error(std::string("cuda: weight registration failed: ") + tm_cuda_last_error());
             return h;
         };
+        auto reg = [&](const void* p, unsigned dt, int rows, int cols) { return reg_rows(p, dt, rows, cols, false); };
+        auto reg_shard = [&](const void* p, unsigned dt, int rows, int cols) { return reg_rows(p, dt, rows, cols, d_.world > 1); };
         w_.resize((size_t)d_.L);
         for (int l = 0; l < d_.L; ++l) {
             const CudaLlamaLayer& s = layers_[(size_t)l];
             Registered& r = w_[(size_t)l];
             r.q = reg(s.q, d_.dt_proj, QD, d_.D); r.k = reg(s.k, d_.dt_proj, KVD, d_.D); r.v = reg(s.v, d_.dt_proj, KVD, d_.D);
             r.o = reg(s.o, d_.dt_proj, d_.D, QD);
-            r.gate = reg(s.gate, d_.dt_proj, d_.F, d_.D); r.up = reg(s.up, d_.dt_proj, d_.F, d_.D);
-            r.down = reg(s.down, d_.dt_proj, d_.D, d_.F);
+            r.gate = reg_shard(s.gate, d_.dt_proj, d_.F, d_.D); r.up = reg_shard(s.up, d_.dt_proj, d_.F, d_.D);
+            r.down = reg_shard(s.down, d_.dt_proj, d_.D, d_.F);
         }
         embed_ = reg(d_.embed, d_.dt_embed, d_.V, d_.D);
-        head_ = reg(d_.head, d_.dt_head, d_.V, d_.D);
+        head_ = reg_shard(d_.head, d_.dt_head, d_.V, d_.D);
         const size_t D4 = (size_t)d_.D * 4;
         bool ok = tm_cuda_tok_reserve(SLOT_X, D4) && tm_cuda_tok_reserve(SLOT_H, D4) && tm_cuda_tok_reserve(SLOT_H2, D4) &&
                   tm_cuda_tok_reserve(SLOT_H2S, D4) && tm_cuda_tok_reserve(SLOT_DN, D4) && tm_cuda_tok_reserve(SLOT_XF, D4) &&
                   tm_cuda_tok_reserve(SLOT_QKV, (size_t)(QD + 2 * KVD) * 4) && tm_cuda_tok_reserve(SLOT_AO, (size_t)QD * 4) &&
                   tm_cuda_tok_reserve(SLOT_GU, (size_t)2 * d_.F * 4) && tm_cuda_tok_reserve(SLOT_LOGITS, (size_t)d_.V * 4) &&
-                  tm_cuda_tok_reserve(SLOT_PROBS, (size_t)d_.H * d_.ctx * 4) && tm_cuda_tok_reserve(SLOT_STATE, 64);
+                  tm_cuda_tok_reserve(SLOT_PROBS, (size_t)d_.H * d_.ctx * 4) && tm_cuda_tok_reserve(SLOT_STATE, 64) &&
+                  tm_cuda_tok_reserve(SLOT_ACT, (size_t)d_.F * 4);
         if (!ok) throw std::runtime_error("cuda: packed slot reservation failed");
         const size_t kv = (size_t)d_.KVH * d_.ctx * d_.dh;
         for (int l = 0; l < d_.L; ++l)
@@ -144,6 +160,17 @@ public:
             tm_cuda_tok_gemv_kq(SLOT_AO, r.o.id, r.o.woff, SLOT_H2, 0, (unsigned)d_.D, (unsigned)QD, dt);
             tm_cuda_tok_add(SLOT_X, SLOT_H2, (unsigned)d_.D);
             tm_cuda_tok_rmsnorm(SLOT_X, s.rms2, SLOT_H2S, (unsigned)d_.D, d_.eps);
+            if (d_.world > 1) {
+                const unsigned Fs = (unsigned)(d_.F / d_.world), Ds = (unsigned)(d_.D / d_.world);
+                tm_cuda_tok_gemv_kq(SLOT_H2S, r.gate.id, r.gate.woff, SLOT_GU, 0, Fs, (unsigned)d_.D, dt);
+                tm_cuda_tok_gemv_kq(SLOT_H2S, r.up.id, r.up.woff, SLOT_GU, (size_t)Fs * 4, Fs, (unsigned)d_.D, dt);
+                tm_cuda_tok_silu_mul(SLOT_GU, 0, SLOT_GU, (size_t)Fs * 4, Fs);
+                tm_cuda_tok_all_gather(SLOT_GU, 0, SLOT_ACT, 0, Fs);
+                tm_cuda_tok_gemv_kq(SLOT_ACT, r.down.id, r.down.woff, SLOT_DN, (size_t)d_.rank * Ds * 4, Ds, (unsigned)d_.F, dt);
+                tm_cuda_tok_all_gather(SLOT_DN, (size_t)d_.rank * Ds * 4, SLOT_DN, 0, Ds);
+                tm_cuda_tok_add(SLOT_X, SLOT_DN, (unsigned)d_.D);
+                continue;
+            }
             tm_cuda_tok_gemv_kq(SLOT_H2S, r.gate.id, r.gate.woff, SLOT_GU, 0, (unsigned)d_.F, (unsigned)d_.D, dt);
             tm_cuda_tok_gemv_kq(SLOT_H2S, r.up.id, r.up.woff, SLOT_GU, (size_t)d_.F * 4, (unsigned)d_.F, (unsigned)d_.D, dt);
             tm_cuda_tok_silu_mul(SLOT_GU, 0, SLOT_GU, (size_t)d_.F * 4, (unsigned)d_.F);
@@ -151,6 +178,12 @@ public:
             tm_cuda_tok_add(SLOT_X, SLOT_DN, (unsigned)d_.D);
         }
         tm_cuda_tok_rmsnorm(SLOT_X, d_.rmsf, SLOT_XF, (unsigned)d_.D, d_.eps);
+        if (d_.world > 1) {
+            const unsigned Vs = (unsigned)(d_.V / d_.world);
+            tm_cuda_tok_gemv_kq(SLOT_XF, head_.id, head_.woff, SLOT_LOGITS, (size_t)d_.rank * Vs * 4, Vs, (unsigned)d_.D, d_.dt_head);
+            tm_cuda_tok_all_gather(SLOT_LOGITS, (size_t)d_.rank * Vs * 4, SLOT_LOGITS, 0, Vs);
+            return;
+        }
         tm_cuda_tok_gemv_kq(SLOT_XF, head_.id, head_.woff, SLOT_LOGITS, 0, (unsigned)d_.V, (unsigned)d_.D, d_.dt_head);
     }
 
@@ -181,6 +214,24 @@ public:
                                 (unsigned)d_.dh, (unsigned)d_.ctx, scale, (unsigned)REP, SLOT_STATE);
             const unsigned Dn = (unsigned)d_.D, Fn = (unsigned)d_.F;
             tm_cuda_tok_gemv_fused(SLOT_AO, 0, 0, 0, 0, nullptr, 0.f, r.o.id, SLOT_X, 0, Dn, (unsigned)QD, dt, &r.o.woff, &Dn, 1, 1);
+            if (d_.world > 1) {
+                // this rank's rows of gate|up -> SiLU*up on the shard -> gather the activation; this rank's
+                // rows of down accumulate into its slice of the residual, which is then gathered in place
+                const unsigned Fs = Fn / (unsigned)d_.world, Ds = Dn / (unsigned)d_.world;
+                if (same_buffer(r.gate, r.up, r.up)) {
+                    const uint64_t woff[2] = {r.gate.woff, r.up.woff};
+                    const unsigned rows[2] = {Fs, Fs};
+                    tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.gate.id, SLOT_GU, 0, 2 * Fs, Dn, dt, woff, rows, 2, 0);
+                } else {
+                    tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.gate.id, SLOT_GU, 0, Fs, Dn, dt, &r.gate.woff, &Fs, 1, 0);
+                    tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.up.id, SLOT_GU, (size_t)Fs * 4, Fs, Dn, dt, &r.up.woff, &Fs, 1, 0);
+                }
+                tm_cuda_tok_silu_mul(SLOT_GU, 0, SLOT_GU, (size_t)Fs * 4, Fs);
+                tm_cuda_tok_all_gather(SLOT_GU, 0, SLOT_ACT, 0, Fs);
+                tm_cuda_tok_gemv_fused(SLOT_ACT, 0, 0, 0, 0, nullptr, 0.f, r.down.id, SLOT_X, (size_t)d_.rank * Ds * 4, Ds, Fn, dt, &r.down.woff, &Ds, 1, 1);
+                tm_cuda_tok_all_gather(SLOT_X, (size_t)d_.rank * Ds * 4, SLOT_X, 0, Ds);
+                continue;
+            }
             if (same_buffer(r.gate, r.up, r.up)) {
                 const uint64_t woff[2] = {r.gate.woff, r.up.woff};
                 const unsigned rows[2] = {Fn, Fn};
@@ -192,7 +243,13 @@ public:
             tm_cuda_tok_gemv_fused(SLOT_GU, 0, 2, SLOT_GU, (size_t)Fn * 4, nullptr, 0.f, r.down.id, SLOT_X, 0, Dn, Fn, dt, &r.down.woff, &Dn, 1, 1);
         }
         const unsigned Vn = (unsigned)d_.V;
-        tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, 0, Vn, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vn, 1, 0);
+        if (d_.world > 1) {
+            const unsigned Vs = Vn / (unsigned)d_.world;
+            tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, (size_t)d_.rank * Vs * 4, Vs, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vs, 1, 0);
+            tm_cuda_tok_all_gather(SLOT_LOGITS, (size_t)d_.rank * Vs * 4, SLOT_LOGITS, 0, Vs);
+        } else {
+            tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, 0, Vn, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vn, 1, 0);
+        }
         tm_cuda_tok_argmax_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE);
         tm_cuda_tok_advance(SLOT_STATE);
     }

@@ -34,14 +34,33 @@ def load() -> C.CDLL:
     return _lib
 
 
+def init_comm(cuda_lib, rank: int, world: int) -> None:
+    """Create the lane's communicator on every rank of an initialised torch.distributed group:
+    rank 0 makes the id, the group's broadcast carries it (any backend; gloo is enough)."""
+    import torch
+    import torch.distributed as dist
+
+    n = int(cuda_lib.tm_cuda_comm_id_bytes())
+    buf = (C.c_ubyte * n)()
+    if rank == 0 and not cuda_lib.tm_cuda_comm_unique_id(buf):
+        raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
+    t = torch.tensor(list(bytes(buf)), dtype=torch.uint8)
+    if dist.get_backend() == "nccl":
+        t = t.cuda()
+    dist.broadcast(t, src=0)
+    raw = bytes(t.cpu().tolist())
+    if not cuda_lib.tm_cuda_comm_init(rank, world, (C.c_ubyte * n).from_buffer_copy(raw)):
+        raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
+
+
 class Chain:
     """A model on the GPU decode lane. `weights` is the dict synth.make_llama returns (kept alive here:
     registrations are keyed by host address)."""
 
-    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True):
+    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True, rank: int = 0, world: int = 1):
         self.L, self.cfg, self.weights = load(), cfg, weights
-        icfg = (C.c_int * 11)(cfg["L"], cfg["D"], cfg["H"], cfg["KVH"], cfg["dh"], cfg["F"], cfg["V"], cfg["ctx"],
-                              cfg["dt_proj"], cfg["dt_head"], cfg["dt_embed"])
+        icfg = (C.c_int * 13)(cfg["L"], cfg["D"], cfg["H"], cfg["KVH"], cfg["dh"], cfg["F"], cfg["V"], cfg["ctx"],
+                              cfg["dt_proj"], cfg["dt_head"], cfg["dt_embed"], rank, world)
         ptrs = []
         for l in range(cfg["L"]):
             for n in ("q", "k", "v", "o", "gate", "up", "down", "rms1", "rms2"):

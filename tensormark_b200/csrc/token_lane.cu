@@ -619,6 +619,10 @@ bool tm_cuda_tok_graph_launch(int id, unsigned times) {
     return true;
 }
 void tm_cuda_tok_graph_destroy(int id) {
+    if (id < 0) {                                            // every graph of the lane
+        for (cudaGraphExec_t& g : graphs()) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+        return;
+    }
     if (id >= 0 && id < (int)graphs().size() && graphs()[id]) { cudaGraphExecDestroy(graphs()[id]); graphs()[id] = nullptr; }
 }
 

@@ -84,6 +84,13 @@ SIGNATURES = {
     "tm_cuda_tok_graph_end": (C.c_int, []),
     "tm_cuda_tok_graph_launch": (C.c_bool, [C.c_int, _u]),
     "tm_cuda_tok_graph_destroy": (None, [C.c_int]),
+    "tm_cuda_comm_id_bytes": (C.c_size_t, []),
+    "tm_cuda_comm_unique_id": (C.c_bool, [_vp]),
+    "tm_cuda_comm_init": (C.c_bool, [C.c_int, C.c_int, _vp]),
+    "tm_cuda_comm_rank": (C.c_int, []),
+    "tm_cuda_comm_world": (C.c_int, []),
+    "tm_cuda_comm_destroy": (C.c_bool, []),
+    "tm_cuda_tok_all_gather": (None, [C.c_int, C.c_size_t, C.c_int, C.c_size_t, C.c_uint]),
     "tm_cuda_tok_slot_ptr": (_vp, [C.c_int]),
     "tm_cuda_tok_stream": (_vp, []),
 }

@@ -21,17 +21,23 @@ from . import lib, synth
 NAMES = {v: k for k, v in synth.DTYPE_NAMES.items()}
 
 
-def run_chain(args, L, torch) -> None:
-    """Greedy decode chain of a random-init model: `--prompt` tokens fed one by one, then `--steps` chosen on the GPU."""
+def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
+    """Greedy decode chain of a random-init model: `--prompt` tokens fed one by one, then `--steps` chosen on the GPU.
+    Under torch.distributed.run (world > 1) the FFN and LM-head rows are sharded over the ranks."""
     import time
 
     from . import chain
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+        chain.init_comm(L, rank, world)
     cfg = dict(synth.LLAMA3_8B if args.model == "llama3-8b" else synth.TINY_CHAIN)
     cfg["ctx"] = max(cfg["ctx"], args.prompt + args.steps + 1) if args.model == "llama3-8b" else cfg["ctx"]
     t0 = time.perf_counter()
     w = synth.make_llama(cfg, seed=5)
     t_gen = time.perf_counter() - t0
-    m = chain.Chain(cfg, w)
+    m = chain.Chain(cfg, w, rank=rank, world=world)
     prompt = synth.make_tokens(args.prompt, cfg["V"], seed=5).astype(np.int32)
     stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
     t0 = time.perf_counter()
@@ -43,6 +49,8 @@ def run_chain(args, L, torch) -> None:
     else:
         nxt = m.feed(prompt)
     t_prompt = time.perf_counter() - t0
+    if dist:
+        dist.barrier()
     launches0 = int(L.tm_cuda_launch_count())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -52,11 +60,24 @@ def run_chain(args, L, torch) -> None:
     toks = m.chain_end(args.steps)
     wall = time.perf_counter() - t0
     dev_ms = e0.elapsed_time(e1)
+    same = True
+    if dist:
+        t = torch.tensor([dev_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = float(t.item())
+        mine = torch.tensor([int(x) for x in toks], dtype=torch.int64)
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool((lo == hi).all())
     QD, KVD = cfg["H"] * cfg["dh"], cfg["KVH"] * cfg["dh"]
     per_layer = sum(synth.weight_bytes(cfg["dt_proj"], n, k) for n, k in
                     ((QD, cfg["D"]), (KVD, cfg["D"]), (KVD, cfg["D"]), (cfg["D"], QD), (cfg["F"], cfg["D"]), (cfg["F"], cfg["D"]), (cfg["D"], cfg["F"])))
     wbytes = cfg["L"] * per_layer + synth.weight_bytes(cfg["dt_head"], cfg["V"], cfg["D"])
-    print(json.dumps({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps,
+    if rank == 0:
+        print(json.dumps({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps, "n_gpus": world,
+                      "sharding": "FFN and LM-head rows over ranks, NCCL all-gather after each" if world > 1 else "none",
+                      "tokens_equal_on_all_ranks": same,
                       "lane": "host call per op" if args.no_graph else "CUDA graph per token",
                       "decode_tok_per_s": round(args.steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / args.steps, 4),
                       "wall_tok_per_s": round(args.steps / wall, 1),
@@ -64,8 +85,12 @@ def run_chain(args, L, torch) -> None:
                       "weight_bytes_per_token": wbytes,
                       "weight_GBps": round(wbytes * args.steps / (dev_ms * 1e-3) / 1e9, 1),
                       "kernels_encoded_per_chain_call": int(L.tm_cuda_launch_count()) - launches0,
-                      "first_tokens": [int(t) for t in toks[:8]], "model_build_s": round(t_gen, 1)}))
+                      "first_tokens": [int(t) for t in toks[:8]], "model_build_s": round(t_gen, 1)}), flush=True)
     m.close()
+    if dist:
+        lib.check(L.tm_cuda_comm_destroy(), "tm_cuda_comm_destroy")
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main() -> None:
@@ -85,12 +110,16 @@ def main() -> None:
     ap.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph (no host launch cost)")
     args = ap.parse_args()
 
+    import os
+
     import torch
-    torch.cuda.set_device(0)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    dev = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev)
     L = lib.load()
-    lib.check(L.tm_cuda_init(0), "tm_cuda_init")
+    lib.check(L.tm_cuda_init(dev), "tm_cuda_init")
     if args.op == "chain":
-        run_chain(args, L, torch)
+        run_chain(args, L, torch, rank, world)
         return
     dt = NAMES[args.dtype]
     n, k, m = args.n, args.k, args.m

@@ -201,7 +201,7 @@ void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_toke
 /* x = row tok[index] of the embedding table. */
 void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
                           int stateslot);
-void tm_cuda_tok_advance(int stateslot);                         /* position += 1, index += 1 */
+void tm_cuda_tok_advance(int stateslot);                         /* position, index and exchange epoch += 1 (a state is 4 ints) */
 /* Capture the launches encoded between begin and end into a CUDA graph (returns its id, -1 on
  * failure) and replay it. Slots, weight handles and norm weights must exist before the capture. */
 bool tm_cuda_tok_graph_begin(void);
@@ -225,6 +225,31 @@ bool tm_cuda_comm_destroy(void);
 /* dst[dst_off + r*count*4 ...) on every rank <- count floats at src[src_off] of rank r. In place when
  * src is this rank's slice of dst. Offsets and count*4 are multiples of 16. world == 1: a copy. */
 void tm_cuda_tok_all_gather(int srcslot, size_t src_off, int dstslot, size_t dst_off, unsigned count);
+
+/* The same gather without a collective kernel: each rank's arena is mapped into every peer (CUDA
+ * IPC) and the GEMV that produces a shard stores its rows straight into the peers' copies of the
+ * output slot over NVLink, then raises a per-site flag; the kernel that consumes the gathered vector
+ * waits for the other ranks' flags (bounded: 2 s, then the status word reports it) before it reads.
+ * Set-up on every rank: tm_cuda_peer_arena -> exchange the handles -> tm_cuda_peer_open ->
+ * tm_cuda_tok_reserve_shared for the gathered slots, in the same order on every rank. A site is an
+ * index < 256 naming one gather per token; the chain state's fourth int is the token epoch the flags
+ * carry (tm_cuda_tok_advance increments it). At most 8 ranks. */
+size_t tm_cuda_peer_handle_bytes(void);
+bool tm_cuda_peer_arena(size_t bytes, void* handle_out);
+bool tm_cuda_peer_open(int rank, int world, const void* handles);
+int tm_cuda_peer_world(void);
+int tm_cuda_peer_rank(void);
+bool tm_cuda_peer_unmap(void);                                   /* then a barrier between the ranks, then: */
+bool tm_cuda_peer_close(void);
+bool tm_cuda_tok_reserve_shared(int slot, size_t bytes);
+/* tm_cuda_tok_gemv_fused with (a) one output byte offset per segment (seg_yoff), (b) wait_site >= 0:
+ * wait for that site's gather before reading x, (c) push_site >= 0: store the output rows into every
+ * peer's copy of yslot (a shared slot) as well and signal that site. */
+void tm_cuda_tok_gemv_xchg(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                           int wid, int yslot, const size_t* seg_yoff, unsigned N, unsigned K, unsigned dtype,
+                           const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate,
+                           int wait_site, int push_site, int stateslot);
+void tm_cuda_tok_argmax_xchg(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site);
 
 /* Device address of a slot (NULL when unreserved); for resident callers and tests. */
 void* tm_cuda_tok_slot_ptr(int slot);

@@ -57,6 +57,11 @@ struct CudaLlamaDesc {
     // attention block (q/k/v/o, norms, rope, K/V cache) and the chosen tokens are replicated on every
     // rank. tm_cuda_comm_init must have run. F, D and V must divide by world into multiples of 4 rows.
     int rank = 0, world = 1;
+    // How the shards are gathered in the chain forms. true: the GEMVs store their rows into the peers'
+    // buffers and the consumers wait on flags (tm_cuda_tok_gemv_xchg; needs tm_cuda_peer_open and one
+    // weight mapping, map_base). false: ncclAllGather after each sharded GEMV. The per-op lane
+    // (forward_gpu_one, the non-graph chain) always uses ncclAllGather.
+    bool peer_gather = false;
 };
 
 class CudaLlama {
@@ -93,8 +98,14 @@ public:
     void gpu_token_prologue() {
         if (ready_) return;
         const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh;
-        if (d_.world > 1 && (tm_cuda_comm_world() != d_.world || tm_cuda_comm_rank() != d_.rank))
+        if (d_.world > 1 && d_.peer_gather) {
+            if (tm_cuda_peer_world() != d_.world || tm_cuda_peer_rank() != d_.rank)
+                throw std::runtime_error("llama: the peer arena does not match the model's rank / world");
+            if (!d_.map_base) throw std::invalid_argument("llama: the peer gather needs all tensors in one mapping");
+            if (2 * d_.L + 1 > 256) throw std::invalid_argument("llama: too many layers for the exchange sites");
+        } else if (d_.world > 1 && (tm_cuda_comm_world() != d_.world || tm_cuda_comm_rank() != d_.rank)) {
             throw std::runtime_error("llama: the communicator does not match the model's rank / world");
+        }
         auto reg_rows = [&](const void* p, unsigned dt, int rows, int cols, bool sharded) {
             Handle h{};
             const int mine = sharded ? rows / d_.world : rows;
@@ -119,6 +130,10 @@ public:
         embed_ = reg(d_.embed, d_.dt_embed, d_.V, d_.D);
         head_ = reg_shard(d_.head, d_.dt_head, d_.V, d_.D);
         const size_t D4 = (size_t)d_.D * 4;
+        if (d_.world > 1 && d_.peer_gather &&
+            !(tm_cuda_tok_reserve_shared(SLOT_X, D4) && tm_cuda_tok_reserve_shared(SLOT_GU, (size_t)2 * d_.F * 4) &&
+              tm_cuda_tok_reserve_shared(SLOT_LOGITS, (size_t)d_.V * 4)))
+            throw std::runtime_error(std::string("cuda: shared slot reservation failed: ") + tm_cuda_last_error());
         bool ok = tm_cuda_tok_reserve(SLOT_X, D4) && tm_cuda_tok_reserve(SLOT_H, D4) && tm_cuda_tok_reserve(SLOT_H2, D4) &&
                   tm_cuda_tok_reserve(SLOT_H2S, D4) && tm_cuda_tok_reserve(SLOT_DN, D4) && tm_cuda_tok_reserve(SLOT_XF, D4) &&
                   tm_cuda_tok_reserve(SLOT_QKV, (size_t)(QD + 2 * KVD) * 4) && tm_cuda_tok_reserve(SLOT_AO, (size_t)QD * 4) &&
@@ -194,6 +209,7 @@ public:
         const float scale = 1.f / std::sqrt((float)d_.dh);
         const unsigned dt = d_.dt_proj;
         tm_cuda_tok_embed_at(SLOT_TOK, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed, max_tokens, SLOT_STATE);
+        if (d_.world > 1 && d_.peer_gather) { encode_chain_token_peer(max_tokens); return; }
         for (int l = 0; l < d_.L; ++l) {
             const Registered& r = w_[(size_t)l];
             const CudaLlamaLayer& s = layers_[(size_t)l];
@@ -251,6 +267,44 @@ public:
             tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, 0, Vn, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vn, 1, 0);
         }
         tm_cuda_tok_argmax_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE);
+        tm_cuda_tok_advance(SLOT_STATE);
+    }
+
+    // The chain token of a row-sharded model with the gather fused into the GEMVs. Sites: 2l = the
+    // activation of layer l, 2l+1 = the residual after layer l, 2L = the logits. A GEMV that computes
+    // a shard writes its rows at their place in the full vector, here and on every peer; the first
+    // kernel that reads a gathered vector waits for the other ranks' rows.
+    void encode_chain_token_peer(unsigned max_tokens) {
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh, REP = d_.H / d_.KVH;
+        const float scale = 1.f / std::sqrt((float)d_.dh);
+        const unsigned dt = d_.dt_proj, Dn = (unsigned)d_.D, Fn = (unsigned)d_.F, Vn = (unsigned)d_.V;
+        const unsigned Fs = Fn / (unsigned)d_.world, Ds = Dn / (unsigned)d_.world, Vs = Vn / (unsigned)d_.world;
+        const size_t rk = (size_t)d_.rank;
+        for (int l = 0; l < d_.L; ++l) {
+            const Registered& r = w_[(size_t)l];
+            const CudaLlamaLayer& s = layers_[(size_t)l];
+            const unsigned qkv_rows[3] = {(unsigned)QD, (unsigned)KVD, (unsigned)KVD};
+            const uint64_t qkv_woff[3] = {r.q.woff, r.k.woff, r.v.woff};
+            const size_t qkv_yoff[3] = {0, (size_t)QD * 4, (size_t)(QD + KVD) * 4};
+            tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, s.rms1, d_.eps, r.q.id, SLOT_QKV, qkv_yoff, (unsigned)(QD + 2 * KVD), Dn, dt,
+                                  qkv_woff, qkv_rows, 3, 0, l > 0 ? 2 * l - 1 : -1, -1, SLOT_STATE);
+            tm_cuda_tok_qkv_post_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, (unsigned)d_.H, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, d_.theta, SLOT_STATE);
+            tm_cuda_tok_attn_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)QD, (unsigned)d_.H, (unsigned)d_.KVH,
+                                (unsigned)d_.dh, (unsigned)d_.ctx, scale, (unsigned)REP, SLOT_STATE);
+            tm_cuda_tok_gemv_fused(SLOT_AO, 0, 0, 0, 0, nullptr, 0.f, r.o.id, SLOT_X, 0, Dn, (unsigned)QD, dt, &r.o.woff, &Dn, 1, 1);
+            const uint64_t gu_woff[2] = {r.gate.woff, r.up.woff};
+            const unsigned gu_rows[2] = {Fs, Fs};
+            const size_t gu_yoff[2] = {rk * Fs * 4, ((size_t)Fn + rk * Fs) * 4};
+            tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, s.rms2, d_.eps, r.gate.id, SLOT_GU, gu_yoff, 2 * Fs, Dn, dt, gu_woff, gu_rows, 2, 0,
+                                  -1, 2 * l, SLOT_STATE);
+            const size_t dn_yoff[1] = {rk * Ds * 4};
+            tm_cuda_tok_gemv_xchg(SLOT_GU, 0, 2, SLOT_GU, (size_t)Fn * 4, nullptr, 0.f, r.down.id, SLOT_X, dn_yoff, Ds, Fn, dt, &r.down.woff, &Ds, 1, 1,
+                                  2 * l, 2 * l + 1, SLOT_STATE);
+        }
+        const size_t hd_yoff[1] = {rk * Vs * 4};
+        tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, hd_yoff, Vs, Dn, d_.dt_head, &head_.woff, &Vs, 1, 0,
+                              2 * d_.L - 1, 2 * d_.L, SLOT_STATE);
+        tm_cuda_tok_argmax_xchg(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE, 2 * d_.L);
         tm_cuda_tok_advance(SLOT_STATE);
     }
 

@@ -53,14 +53,40 @@ def init_comm(cuda_lib, rank: int, world: int) -> None:
         raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
 
 
+def peer_arena_bytes(cfg: dict) -> int:
+    """Bytes of shared slots a sharded model gathers into: the residual, gate|up and the logits."""
+    return 4 * (cfg["D"] + 2 * cfg["F"] + cfg["V"]) + 4096
+
+
+def init_peer(cuda_lib, rank: int, world: int, arena_bytes: int) -> None:
+    """Create this rank's peer arena, exchange the IPC handles over the torch.distributed group and
+    map the other ranks' arenas."""
+    import torch
+    import torch.distributed as dist
+
+    n = int(cuda_lib.tm_cuda_peer_handle_bytes())
+    buf = (C.c_ubyte * n)()
+    if not cuda_lib.tm_cuda_peer_arena(arena_bytes, buf):
+        raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
+    mine = torch.tensor(list(bytes(buf)), dtype=torch.uint8)
+    if dist.get_backend() == "nccl":
+        mine = mine.cuda()
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    raw = b"".join(bytes(t.cpu().tolist()) for t in every)
+    if not cuda_lib.tm_cuda_peer_open(rank, world, (C.c_ubyte * len(raw)).from_buffer_copy(raw)):
+        raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
+
+
 class Chain:
     """A model on the GPU decode lane. `weights` is the dict synth.make_llama returns (kept alive here:
     registrations are keyed by host address)."""
 
-    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True, rank: int = 0, world: int = 1):
+    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True, rank: int = 0, world: int = 1,
+                 peer_gather: bool = False):
         self.L, self.cfg, self.weights = load(), cfg, weights
-        icfg = (C.c_int * 13)(cfg["L"], cfg["D"], cfg["H"], cfg["KVH"], cfg["dh"], cfg["F"], cfg["V"], cfg["ctx"],
-                              cfg["dt_proj"], cfg["dt_head"], cfg["dt_embed"], rank, world)
+        icfg = (C.c_int * 14)(cfg["L"], cfg["D"], cfg["H"], cfg["KVH"], cfg["dh"], cfg["F"], cfg["V"], cfg["ctx"],
+                              cfg["dt_proj"], cfg["dt_head"], cfg["dt_embed"], rank, world, int(peer_gather))
         ptrs = []
         for l in range(cfg["L"]):
             for n in ("q", "k", "v", "o", "gate", "up", "down", "rms1", "rms2"):

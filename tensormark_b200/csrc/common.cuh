@@ -32,7 +32,24 @@ constexpr int kMaxSeg = 16;
 struct SegTable {                           // rows [row_end[s-1], row_end[s]) start at byte woff[s]
     uint64_t woff[kMaxSeg];
     uint32_t row_end[kMaxSeg];
+    uint32_t yoff[kMaxSeg];                 // element of y that receives the segment's first row (default: its first row index)
     uint32_t nseg;
+};
+
+// Peer-memory all-gather fused into the kernels of a row-sharded model (one process per GPU). A
+// producer writes its rows of y into the same place of every peer's copy of the buffer and, once
+// its last CTA is done, raises its flag of the "site" in every peer's memory to the token's epoch;
+// a consumer waits until the site's flags of all other ranks have reached the epoch before it reads
+// the gathered vector. Flags only grow, every wait is bounded and reports through the status word.
+constexpr int kMaxPeers = 7;
+struct Exchange {
+    const int* epoch;                       // device int; the current token's epoch is *epoch + 1
+    const int* wait_flags;                  // consumer: the site's flags in local memory, one per rank
+    uint32_t nwait, self;                   // consumer: ranks (0 = no wait) and this rank's index
+    uint32_t npush;                         // producer: number of peers (0 = no push)
+    float* peer_y[kMaxPeers];               // producer: y as mapped from each peer
+    int* peer_flag[kMaxPeers];              // producer: this rank's flag of the site in each peer's memory
+    unsigned long long* arrive;             // producer: local count of finished CTAs of the site
 };
 
 // ---- kernel launchers (one per .cu) -----------------------------------------
@@ -41,6 +58,7 @@ struct GemvFuse {                           // optional fusions of the decode ch
     const float* x2;
     float eps;
     bool accumulate;                        // y[row] += dot instead of y[row] = dot
+    const Exchange* xchg;                   // nullptr: single GPU
 };
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
                  const SegTable& seg, cudaStream_t st, const GemvFuse* fuse = nullptr);

@@ -142,7 +142,7 @@ bool make_segments(SegTable& t, unsigned N, const uint64_t* seg_woff, const unsi
     if (nseg > (unsigned)kMaxSeg) return fail("segmented gemv: %u segments (at most %d)", nseg, kMaxSeg);
     std::memset(&t, 0, sizeof t);
     unsigned acc = 0;
-    for (unsigned i = 0; i < nseg; ++i) { acc += seg_rows[i]; t.row_end[i] = acc; t.woff[i] = seg_woff[i]; }
+    for (unsigned i = 0; i < nseg; ++i) { t.yoff[i] = acc; acc += seg_rows[i]; t.row_end[i] = acc; t.woff[i] = seg_woff[i]; }
     t.nseg = nseg;
     if (acc != N) return fail("segmented gemv: segment rows add up to %u, N is %u", acc, N);
     return true;

@@ -32,6 +32,7 @@
 // (tolerance-level, not bitwise, agreement with the fast path).
 #include "common.cuh"
 #include "gemv_lanes.cuh"
+#include "exchange.cuh"
 
 #include <cstdlib>
 
@@ -41,7 +42,6 @@ namespace {
 
 constexpr int kMaxWarps = 16;       // warps per CTA: 16 (512 threads x 128 registers fill the register file) or 8
 constexpr int kMaxStages = 8;      // ring depth per warp is chosen at launch, 2..kMaxStages
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a copy that has not landed in 2 s never will
 
 struct GemvParams {
     const uint8_t* W;
@@ -55,6 +55,7 @@ struct GemvParams {
     uint32_t x_op;              // 0 plain, 1 x*rsqrt(mean(x^2)+eps)*x2, 2 silu(x)*x2
     uint32_t accumulate;
     SegTable seg;
+    Exchange xc;                // row-sharded models: wait for peers before x, push y to peers after
     int* status;
 };
 
@@ -74,11 +75,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
 }
 // Bounded wait: false when the time limit ran out (the caller records it and leaves).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
@@ -100,6 +96,37 @@ __device__ __forceinline__ const uint8_t* row_ptr(const GemvParams& p, uint32_t 
     uint32_t s = 0, start = 0;
     while (s + 1 < p.seg.nseg && row >= p.seg.row_end[s]) { start = p.seg.row_end[s]; ++s; }
     return p.W + p.seg.woff[s] + (size_t)(row - start) * p.row_bytes;
+}
+
+// Element of y that receives `row` (segments may land at separate offsets of y).
+__device__ __forceinline__ uint32_t y_index(const GemvParams& p, uint32_t row) {
+    uint32_t s = 0, start = 0;
+    while (s + 1 < p.seg.nseg && row >= p.seg.row_end[s]) { start = p.seg.row_end[s]; ++s; }
+    return p.seg.yoff[s] + (row - start);
+}
+
+// Producer side: the CTA copies its finished rows of y (elements given by y_index) to every peer;
+// the CTA that finishes last raises this rank's flag on every peer. Call with all threads, after a
+// __syncthreads() that follows the CTA's last store to y.
+__device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t cta_lo, uint32_t cta_hi) {
+    const Exchange& xc = p.xc;
+    if (!xc.npush) return;
+    for (uint32_t i = threadIdx.x; i < cta_hi - cta_lo; i += blockDim.x) {
+        const uint32_t e = y_index(p, cta_lo + i);
+        const float v = __ldcg(p.y + e);
+        for (uint32_t q = 0; q < xc.npush; ++q) xc.peer_y[q][e] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned long long done = atomicAdd(xc.arrive, 1ull) + 1ull;
+        if (done % gridDim.x == 0) {
+            __threadfence_system();
+            const int epoch = *(volatile const int*)xc.epoch + 1;
+            for (uint32_t q = 0; q < xc.npush; ++q)
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(xc.peer_flag[q]), "r"(epoch) : "memory");
+        }
+    }
 }
 
 template <int DT> __device__ __forceinline__ int lane_valid(int lane, int units_in_chunk) {
@@ -170,6 +197,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     // weight prefetch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    exchange_wait(p.xc, p.status);                          // sharded models: x is complete once every peer has pushed
 
     // ---- stage x: block floating point planes in the lanes' byte layout -------
     // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
@@ -322,8 +350,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         if ((lane & 7) == 0 && (R == 4 || (lane & 8) == 0) && (uint32_t)my_row < rows) {
             const uint32_t row = row0 + (uint32_t)my_row;
             if (nchunks == 1) {
-                if (p.accumulate) v += p.y[row];            // residual add folded into the store
-                p.y[row] = v;
+                const uint32_t e = y_index(p, row);
+                if (p.accumulate) v += p.y[e];              // residual add folded into the store
+                p.y[e] = v;
             } else {
                 partial[(size_t)(row - cta_lo) * nchunks + myc] = v;
             }
@@ -336,9 +365,14 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         for (uint32_t i = threadIdx.x; i < cta_hi - cta_lo; i += blockDim.x) {
             float v = partial[(size_t)i * nchunks];
             for (uint32_t cc = 1; cc < nchunks; ++cc) v += partial[(size_t)i * nchunks + cc];
-            if (p.accumulate) v += p.y[cta_lo + i];
-            p.y[cta_lo + i] = v;
+            const uint32_t e = y_index(p, cta_lo + i);
+            if (p.accumulate) v += p.y[e];
+            p.y[e] = v;
         }
+    }
+    if (p.xc.npush) {
+        __syncthreads();                                    // every row of this CTA is in y
+        exchange_push(p, cta_lo, cta_hi);
     }
     if (dead) {
         // A copy never completed. Record it, give the copies still in flight a last
@@ -435,6 +469,7 @@ __global__ void __launch_bounds__(256) gemv_generic(const GemvParams p) {
     extern __shared__ __align__(16) float xs[];            // transformed x, only when a fused transform is requested
     __shared__ float red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    exchange_wait(p.xc, p.status);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* x = p.x;
     if (p.x_op != 0u) {
@@ -457,15 +492,22 @@ __global__ void __launch_bounds__(256) gemv_generic(const GemvParams p) {
         __syncthreads();
         x = xs;
     }
-    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= p.N) return;
-    float v = generic_row<DT>(row_ptr(p, row), x, p.K, lane);
+    const uint32_t cta_lo = blockIdx.x * (blockDim.x >> 5), row = cta_lo + warp;
+    if (row < p.N) {
+        float v = generic_row<DT>(row_ptr(p, row), x, p.K, lane);
 #pragma unroll
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) p.y[row] = p.accumulate ? p.y[row] + v : v;
+        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        const uint32_t e = y_index(p, row);
+        if (lane == 0) p.y[e] = p.accumulate ? p.y[e] + v : v;
+    }
+    if (p.xc.npush) {
+        __syncthreads();
+        exchange_push(p, cta_lo, min(p.N, cta_lo + (blockDim.x >> 5)));
+    }
 }
 
 constexpr size_t kSmemLimit = 227 * 1024 - 256;          // dynamic part; the kernel also has a few static words
+constexpr size_t kHalfSmem = 112 * 1024;                 // two such CTAs (of two kernels) fit one SM
 
 // Bytes of shared memory outside the stage rings.
 template <int DT> size_t stream_fixed_smem(unsigned K) {
@@ -486,6 +528,8 @@ bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, 
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemv_stream<DT, R, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit) != cudaSuccess)
             return fail("gemv: cannot raise the dynamic shared memory limit");
+        // every GEMV asks for the largest shared-memory carveout, so consecutive kernels share one SM configuration
+        cudaFuncSetAttribute(gemv_stream<DT, R, kWarps>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -509,8 +553,15 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
                          force_w = env_int("TM_GEMV_WARPS", 0);
         // One 16-warp CTA per SM; matrices with fewer than 8 rows per SM use 8-warp CTAs when the row
         // has few enough steps (measured on the ten-GEMV sweep: 65 vs 71 us per pass). TM_GEMV_WARPS overrides.
-        int warps_cta = (p.N >= 8u * sms || nchunks > 8) ? 16 : 8;
+        // TM_GEMV_HALF_MB > 0 (an experiment, off by default) gives matrices up to that many MB an 8-warp
+        // CTA limited to half of an SM's shared memory, so that two consecutive kernels can be resident
+        // together; measured slower (sweep 78 vs 65 us, 8B chain 3.2 vs 2.7 ms per token): 8 warps do not
+        // decode fast enough.
+        static const int half_mb = env_int("TM_GEMV_HALF_MB", 0);
+        const bool half = half_mb > 0 && nchunks <= 8 && (size_t)p.N * p.row_bytes <= (size_t)half_mb << 20;
+        int warps_cta = half ? 8 : ((p.N >= 8u * sms || nchunks > 8) ? 16 : 8);
         if ((force_w == 8 && nchunks <= 8) || force_w == 16) warps_cta = force_w;
+        const size_t smem_limit = half ? kHalfSmem : kSmemLimit;
         const unsigned teams = (unsigned)warps_cta / nchunks;
         unsigned grid = (p.N + teams - 1) / teams;
         if (grid > sms) grid = sms;
@@ -524,8 +575,8 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         const size_t fixed = stream_fixed_smem<DT>(p.K) + (nchunks > 1 ? (size_t)p.rows_per_cta * nchunks * 4 : 0);
         auto fit = [&](int r) -> unsigned {
             const size_t per = (size_t)warps_cta * r * L::STEP_BYTES;
-            if (fixed + 2 * per > kSmemLimit) return 0u;
-            const size_t s = (kSmemLimit - fixed) / per;
+            if (fixed + 2 * per > smem_limit) return 0u;
+            const size_t s = (smem_limit - fixed) / per;
             return (unsigned)(s > (size_t)kMaxStages ? kMaxStages : s);
         };
         while (R > 1 && fit(R) < 2) R >>= 1;
@@ -534,7 +585,8 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
             // No deeper than a warp has items, and by default no deeper than 3: the ring only has
             // to cover the DRAM latency.
             const unsigned items = (rows_per_team + R - 1) / R;
-            unsigned cap = force_s >= 2 ? (unsigned)force_s : 3u;
+            // The half-SM shape prefetches while the previous kernel runs: as deep as the warp has items.
+            unsigned cap = force_s >= 2 ? (unsigned)force_s : (half ? (unsigned)kMaxStages : 3u);
             if (cap > (unsigned)kMaxStages) cap = kMaxStages;
             if (S > cap) S = cap;
             if (S > items) S = items < 1 ? 1 : items;
@@ -584,6 +636,11 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     p.row_bytes = (K / be) * block_bytes(dtype);
     p.seg = seg; p.status = device_status_word();
     p.x2 = nullptr; p.eps = 0.f; p.x_op = 0; p.accumulate = 0;
+    p.xc = Exchange{};
+    if (fuse && fuse->xchg) p.xc = *fuse->xchg;
+    if (p.xc.npush > (unsigned)kMaxPeers || (p.xc.nwait && !p.xc.wait_flags) || ((p.xc.npush || p.xc.nwait) && !p.xc.epoch) ||
+        (p.xc.npush && !p.xc.arrive))
+        return fail("gemv: incomplete peer exchange description");
     if (fuse) {
         if (fuse->x_op > 2 || (fuse->x_op != 0 && (!fuse->x2 || (uintptr_t)fuse->x2 % 16))) return fail("gemv: bad fused x transform");
         p.x2 = fuse->x2; p.eps = fuse->eps; p.x_op = fuse->x_op; p.accumulate = fuse->accumulate ? 1u : 0u;

@@ -9,6 +9,7 @@
 // All arithmetic is fp32; K/V rows are rounded to half once, when written.
 #include "common.cuh"
 #include "glue.h"
+#include "exchange.cuh"
 #include "qdecode.cuh"
 
 #include <cuda_fp16.h>
@@ -141,16 +142,17 @@ template <bool SAMPLE>
 __global__ void __launch_bounds__(256) choose_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, uint32_t n,
                                                       uint32_t idx, float inv_temp, uint32_t seed,
                                                       unsigned long long* __restrict__ scratch /* [0]=key, [1]=done */,
-                                                      const int* __restrict__ st) {
+                                                      const int* __restrict__ st, const Exchange xc, int* status) {
     __shared__ unsigned long long best_s[8];
     if (st) {
         idx = (uint32_t)st[1] + 1u;                         // chain: the token chosen now is fed by the next step
         if (idx < (uint32_t)st[2]) return;                  // ... unless that entry is a forced (prompt) token
     }
+    exchange_wait(xc, status);                              // sharded head: every rank's slice of x has arrived
     unsigned long long best = pack_key(-CUDART_INF_F, 0);
     const uint32_t base = hash32(seed * 0x9e3779b9u + idx * 0x85ebca6bu + 0x1234567u);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        float v = x[i];
+        float v = __ldcg(x + i);
         if (SAMPLE && inv_temp > 0.f) {
             const uint32_t h = hash32(base ^ (i * 0x27d4eb2fu + 0x165667b1u));
             const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
@@ -314,7 +316,7 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, T* __restrict__ kcache,
         vcache[(size_t)kv * ctx * dh + (size_t)pos * dh + l] = to_cache<T>(qkv[(size_t)(H + KVH) * dh + e]);
     }
 }
-__global__ void advance_kernel(int* __restrict__ st) { st[0] += 1; st[1] += 1; }
+__global__ void advance_kernel(int* __restrict__ st) { st[0] += 1; st[1] += 1; st[3] += 1; }   // position, token index, exchange epoch
 
 inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
 
@@ -415,13 +417,15 @@ bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float
     return check_launch("embed_row");
 }
 bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
-                   unsigned long long* scratch, cudaStream_t st, const int* state) {
+                   unsigned long long* scratch, cudaStream_t st, const int* state, const Exchange* xchg) {
     if (!x || !out || n == 0) return fail("argmax: bad arguments");
     unsigned grid = cdiv(n, 256 * 4);
     const unsigned sms = (unsigned)device_sm_count();
     if (grid > sms) grid = sms;
-    if (sample) choose_kernel<true><<<grid, 256, 0, st>>>(x, out, n, idx, inv_temp, seed, scratch, state);
-    else choose_kernel<false><<<grid, 256, 0, st>>>(x, out, n, idx, 0.f, 0u, scratch, state);
+    const Exchange xc = xchg ? *xchg : Exchange{};
+    if (xc.nwait && (!xc.wait_flags || !xc.epoch)) return fail("argmax: incomplete peer exchange description");
+    if (sample) choose_kernel<true><<<grid, 256, 0, st>>>(x, out, n, idx, inv_temp, seed, scratch, state, xc, device_status_word());
+    else choose_kernel<false><<<grid, 256, 0, st>>>(x, out, n, idx, 0.f, 0u, scratch, state, xc, device_status_word());
     note_launch();
     return check_launch("argmax");
 }

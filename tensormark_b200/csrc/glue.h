@@ -5,6 +5,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace tmc {
 
 bool launch_rmsnorm(const float* x, const float* w, float* out, unsigned D, float eps, cudaStream_t st);
@@ -24,7 +26,7 @@ bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float
                       const int* state = nullptr);
 // scratch: two zero-initialised 64-bit words owned by the caller, re-armed by the kernel
 bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
-                   unsigned long long* scratch, cudaStream_t st, const int* state = nullptr);
+                   unsigned long long* scratch, cudaStream_t st, const int* state = nullptr, const Exchange* xchg = nullptr);
 
 struct AttnPlan {
     unsigned nsplit;        // 0: the scratch cannot hold even one split

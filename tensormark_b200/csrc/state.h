@@ -24,6 +24,21 @@ struct Scratch {                 // grow-only device buffer
 struct Slot {                    // token-lane slot: backend-owned device buffer (tensormark/metal.h:2262-2281)
     uint8_t* ptr = nullptr;
     size_t bytes = 0;
+    bool shared = false;         // carved from the peer arena: never grown, never freed on its own
+};
+
+// Row-sharded models: this rank's arena (exported to the peers) and the peers' arenas mapped here.
+// The arena starts with the exchange flags, flags[site][rank]; shared slots follow, at the same
+// offsets on every rank because every rank reserves them in the same order.
+constexpr int kMaxRanks = 8, kMaxSites = 256;
+constexpr size_t kFlagBytes = (size_t)kMaxSites * kMaxRanks * sizeof(int);
+struct PeerState {
+    uint8_t* arena = nullptr;
+    size_t bytes = 0, used = 0;
+    uint8_t* base[kMaxRanks] = {};                              // base[rank] == arena once opened
+    int rank = 0, world = 1;
+    bool open = false;
+    unsigned long long* arrive = nullptr;                       // [kMaxSites] finished-CTA counters, local
 };
 
 struct WeightBuf {               // registered weights: handle id = 1000 + index (metal.h:3282-3337)
@@ -58,6 +73,7 @@ struct State {
     unsigned rope_dh = 0, rope_cap = 0;
     float rope_theta = 0.f;
     unsigned* peek_host = nullptr;                              // pinned mirror for tok_peek
+    PeerState peer;
 };
 
 State& state();

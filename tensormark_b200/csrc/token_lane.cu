@@ -22,6 +22,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -50,6 +51,7 @@ uint8_t* slot_ptr(int sid, size_t bytes, const char* who) {
     if ((int)s.slots.size() <= sid) s.slots.resize((size_t)sid + 1);
     Slot& sl = s.slots[sid];
     if (sl.ptr && sl.bytes >= bytes) return sl.ptr;
+    if (sl.shared) { latch("%s: shared slot %d holds %zu bytes, %zu wanted", who, sid, sl.bytes, bytes); return nullptr; }
     if (sl.ptr && s.encoding) { latch("%s: slot %d must be reserved before token encoding (%zu > %zu bytes)", who, sid, bytes, sl.bytes); return nullptr; }
     if (bytes == 0) { latch("%s: slot %d is empty", who, sid); return nullptr; }
     uint8_t* p = nullptr;
@@ -481,14 +483,45 @@ bool tm_cuda_argmax_dev(const float* x, unsigned* out, unsigned n, void* stream)
 // ---- chain forms: position and token index live on the device -------------------------
 // A chain state is two ints in a slot: {position, token index}. The entries below read it on the
 // device, so one captured CUDA graph serves every token of a greedy chain.
-static const int* state_ptr(int stateslot, const char* who) { return (const int*)slot_ptr(stateslot, 8, who); }
+static const int* state_ptr(int stateslot, const char* who) { return (const int*)slot_ptr(stateslot, 16, who); }
 
-void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
-                            int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
-                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate) {
+// Exchange description of one launch. wait_site / push_site < 0: that half is absent. The flags of a
+// site live at the start of the arena; y must be a shared slot when pushing (its offset in the arena
+// is the same on every rank).
+static bool make_exchange(Exchange& xc, int wait_site, int push_site, int stateslot, const uint8_t* y_base, const char* who) {
+    State& s = state();
+    PeerState& ps = s.peer;
+    xc = Exchange{};
+    if (wait_site < 0 && push_site < 0) return true;
+    if (!ps.open) { latch("%s: the peer arena is not open", who); return false; }
+    if (wait_site >= kMaxSites || push_site >= kMaxSites) { latch("%s: exchange site out of range", who); return false; }
+    const int* st = (const int*)slot_ptr(stateslot, 16, who);
+    if (!st) return false;
+    xc.epoch = st + 3;
+    int* flags = (int*)ps.arena;
+    if (wait_site >= 0) { xc.wait_flags = flags + (size_t)wait_site * kMaxRanks; xc.nwait = (uint32_t)ps.world; xc.self = (uint32_t)ps.rank; }
+    if (push_site >= 0) {
+        if (!y_base || y_base < ps.arena + kFlagBytes || y_base >= ps.arena + ps.used) { latch("%s: the pushed output must be a shared slot", who); return false; }
+        const size_t off = (size_t)(y_base - ps.arena);
+        uint32_t n = 0;
+        for (int q = 0; q < ps.world; ++q) {
+            if (q == ps.rank) continue;
+            xc.peer_y[n] = (float*)(ps.base[q] + off);
+            xc.peer_flag[n] = (int*)ps.base[q] + (size_t)push_site * kMaxRanks + ps.rank;
+            ++n;
+        }
+        xc.npush = n;
+        xc.arrive = ps.arrive + push_site;
+    }
+    return true;
+}
+
+static void gemv_fused_impl(const char* who, int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                            int wid, int yslot, size_t yoff, const size_t* seg_yoff, unsigned N, unsigned K, unsigned dtype,
+                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate,
+                            int wait_site, int push_site, int stateslot) {
     if (!ensure_init(-1)) return;
     State& s = state();
-    const char* who = "tok_gemv_fused";
     const size_t row_bytes = weight_bytes(dtype, 1, K);
     if (!row_bytes) { latch("%s: K=%u is not whole blocks of dtype %u", who, K, dtype); return; }
     if (yoff % 4 || xoff % 16 || x2off % 16) { latch("%s: misaligned byte offset", who); return; }
@@ -500,11 +533,25 @@ void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t
         if (t.woff[k] > s.wbufs[i].bytes || (size_t)seg_rows[k] * row_bytes > s.wbufs[i].bytes - t.woff[k]) {
             latch("%s: segment %u lies outside weight handle %d", who, k, wid); return;
         }
+    size_t y_need = yoff + (size_t)N * 4;
+    if (seg_yoff) {                                          // every segment lands at its own byte offset of the slot
+        y_need = 0;
+        for (unsigned k = 0; k < nseg; ++k) {
+            if (seg_yoff[k] % 4) { latch("%s: misaligned output offset", who); return; }
+            t.yoff[k] = (uint32_t)(seg_yoff[k] / 4);
+            const size_t end = seg_yoff[k] + (size_t)seg_rows[k] * 4;
+            y_need = end > y_need ? end : y_need;
+        }
+        yoff = 0;
+    }
     const uint8_t* x = slot_ptr(xslot, xoff + (size_t)K * 4, who);
-    uint8_t* y = slot_ptr(yslot, yoff + (size_t)N * 4, who);
+    uint8_t* y = slot_ptr(yslot, y_need, who);
     if (!x || !y) return;
+    Exchange xc;
+    if (!make_exchange(xc, wait_site, push_site, stateslot, y + yoff, who)) return;
     GemvFuse f{};
     f.x_op = (unsigned)x_op; f.eps = eps; f.accumulate = accumulate != 0; f.x2 = nullptr;
+    f.xchg = (xc.nwait || xc.npush) ? &xc : nullptr;
     if (x_op == 1) {
         if (!norm_w) { latch("%s: rmsnorm needs its weights", who); return; }
         auto it = s.norm_w.find(norm_w);
@@ -521,6 +568,21 @@ void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t
         f.x2 = (const float*)(u + x2off);
     } else if (x_op != 0) { latch("%s: unknown x transform %d", who, x_op); return; }
     if (!launch_gemv((const float*)(x + xoff), s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream, &f)) s.sticky = true;
+}
+
+void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                            int wid, int yslot, size_t yoff, unsigned N, unsigned K, unsigned dtype,
+                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate) {
+    gemv_fused_impl("tok_gemv_fused", xslot, xoff, x_op, x2slot, x2off, norm_w, eps, wid, yslot, yoff, nullptr, N, K, dtype,
+                    seg_woff, seg_rows, nseg, accumulate, -1, -1, -1);
+}
+void tm_cuda_tok_gemv_xchg(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
+                           int wid, int yslot, const size_t* seg_yoff, unsigned N, unsigned K, unsigned dtype,
+                           const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate,
+                           int wait_site, int push_site, int stateslot) {
+    if (!seg_yoff) { if (ensure_init(-1)) latch("tok_gemv_xchg: null output offsets"); return; }
+    gemv_fused_impl("tok_gemv_xchg", xslot, xoff, x_op, x2slot, x2off, norm_w, eps, wid, yslot, 0, seg_yoff, N, K, dtype,
+                    seg_woff, seg_rows, nseg, accumulate, wait_site, push_site, stateslot);
 }
 void tm_cuda_tok_qkv_post_at(int qkvslot, int kcslot, int vcslot, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
                              float theta, int stateslot) {
@@ -554,15 +616,23 @@ void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int ou
     if (!pl.nsplit) { latch("tok_attn_at: probs slot too small for one split"); return; }
     if (!launch_attention(q, kc, vc, s.kv_half, probs, out, H, KVH, dh, ctx, ctx, scale, REP, pl, s.stream, st)) s.sticky = true;
 }
-void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot) {
+static void argmax_at_impl(const char* who, int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site) {
     if (!ensure_init(-1)) return;
     State& s = state();
-    const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, "tok_argmax_at");
-    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * (size_t)max_tokens, "tok_argmax_at");
-    const int* st = state_ptr(stateslot, "tok_argmax_at");
+    const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, who);
+    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * (size_t)max_tokens, who);
+    const int* st = state_ptr(stateslot, who);
     unsigned long long* sc = choose_scratch();
     if (!x || !t || !st || !sc) return;
-    if (!launch_choose(x, t, n, 0, 0.f, 0u, false, sc, s.stream, st)) s.sticky = true;
+    Exchange xc;
+    if (!make_exchange(xc, wait_site, -1, stateslot, nullptr, who)) return;
+    if (!launch_choose(x, t, n, 0, 0.f, 0u, false, sc, s.stream, st, xc.nwait ? &xc : nullptr)) s.sticky = true;
+}
+void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot) {
+    argmax_at_impl("tok_argmax_at", xslot, tokslot, n, max_tokens, stateslot, -1);
+}
+void tm_cuda_tok_argmax_xchg(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site) {
+    argmax_at_impl("tok_argmax_xchg", xslot, tokslot, n, max_tokens, stateslot, wait_site);
 }
 void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
                           int stateslot) {
@@ -577,7 +647,7 @@ void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsign
 }
 void tm_cuda_tok_advance(int stateslot) {
     if (!ensure_init(-1)) return;
-    int* st = (int*)slot_ptr(stateslot, 8, "tok_advance");
+    int* st = (int*)slot_ptr(stateslot, 16, "tok_advance");
     if (st && !launch_advance(st, state().stream)) state().sticky = true;
 }
 

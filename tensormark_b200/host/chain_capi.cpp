@@ -21,7 +21,7 @@ struct Holder {
 
 TMCHAIN_API const char* tmchain_error(void) { return g_err.c_str(); }
 
-// cfg = {L, D, H, KVH, dh, F, V, ctx, dt_proj, dt_head, dt_embed, rank, world}; layer_ptrs holds, per layer,
+// cfg = {L, D, H, KVH, dh, F, V, ctx, dt_proj, dt_head, dt_embed, rank, world, peer_gather}; layer_ptrs holds, per layer,
 // q, k, v, o, gate, up, down, rms1, rms2 (9 pointers).
 TMCHAIN_API void* tmchain_create(const int* cfg, float theta, float eps, const void* embed, const void* head,
                                  const float* rmsf, const void* const* layer_ptrs, const void* map_base, size_t map_size) {
@@ -32,7 +32,7 @@ TMCHAIN_API void* tmchain_create(const int* cfg, float theta, float eps, const v
         d.dt_proj = (unsigned)cfg[8]; d.dt_head = (unsigned)cfg[9]; d.dt_embed = (unsigned)cfg[10];
         d.theta = theta; d.eps = eps; d.embed = embed; d.head = head; d.rmsf = rmsf;
         d.map_base = map_base; d.map_size = map_size;
-        d.rank = cfg[11]; d.world = cfg[12];
+        d.rank = cfg[11]; d.world = cfg[12]; d.peer_gather = cfg[13] != 0;
         h->layers.resize((size_t)(d.L > 0 ? d.L : 0));
         for (int l = 0; l < d.L; ++l) {
             const void* const* p = layer_ptrs + 9 * l;

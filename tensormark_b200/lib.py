@@ -91,6 +91,17 @@ SIGNATURES = {
     "tm_cuda_comm_world": (C.c_int, []),
     "tm_cuda_comm_destroy": (C.c_bool, []),
     "tm_cuda_tok_all_gather": (None, [C.c_int, C.c_size_t, C.c_int, C.c_size_t, C.c_uint]),
+    "tm_cuda_peer_handle_bytes": (C.c_size_t, []),
+    "tm_cuda_peer_arena": (C.c_bool, [C.c_size_t, _vp]),
+    "tm_cuda_peer_open": (C.c_bool, [C.c_int, C.c_int, _vp]),
+    "tm_cuda_peer_world": (C.c_int, []),
+    "tm_cuda_peer_rank": (C.c_int, []),
+    "tm_cuda_peer_unmap": (C.c_bool, []),
+    "tm_cuda_peer_close": (C.c_bool, []),
+    "tm_cuda_tok_reserve_shared": (C.c_bool, [C.c_int, C.c_size_t]),
+    "tm_cuda_tok_gemv_xchg": (None, [C.c_int, _sz, C.c_int, C.c_int, _sz, _vp, C.c_float, C.c_int, C.c_int, C.POINTER(_sz), _u, _u, _u,
+                                     C.POINTER(_u64), C.POINTER(_u), _u, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tm_cuda_tok_argmax_xchg": (None, [C.c_int, C.c_int, _u, _u, C.c_int, C.c_int]),
     "tm_cuda_tok_slot_ptr": (_vp, [C.c_int]),
     "tm_cuda_tok_stream": (_vp, []),
 }

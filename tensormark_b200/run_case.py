@@ -21,6 +21,12 @@ from . import lib, synth
 NAMES = {v: k for k, v in synth.DTYPE_NAMES.items()}
 
 
+def cfg_for(args) -> dict:
+    cfg = dict(synth.LLAMA3_8B if args.model == "llama3-8b" else synth.TINY_CHAIN)
+    cfg["ctx"] = max(cfg["ctx"], args.prompt + args.steps + 1) if args.model == "llama3-8b" else cfg["ctx"]
+    return cfg
+
+
 def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
     """Greedy decode chain of a random-init model: `--prompt` tokens fed one by one, then `--steps` chosen on the GPU.
     Under torch.distributed.run (world > 1) the FFN and LM-head rows are sharded over the ranks."""
@@ -32,12 +38,13 @@ def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
         import torch.distributed as dist
         dist.init_process_group("gloo")
         chain.init_comm(L, rank, world)
-    cfg = dict(synth.LLAMA3_8B if args.model == "llama3-8b" else synth.TINY_CHAIN)
-    cfg["ctx"] = max(cfg["ctx"], args.prompt + args.steps + 1) if args.model == "llama3-8b" else cfg["ctx"]
+        if args.gather == "peer":
+            chain.init_peer(L, rank, world, chain.peer_arena_bytes(cfg_for(args)))
+    cfg = cfg_for(args)
     t0 = time.perf_counter()
     w = synth.make_llama(cfg, seed=5)
     t_gen = time.perf_counter() - t0
-    m = chain.Chain(cfg, w, rank=rank, world=world)
+    m = chain.Chain(cfg, w, rank=rank, world=world, peer_gather=world > 1 and args.gather == "peer")
     prompt = synth.make_tokens(args.prompt, cfg["V"], seed=5).astype(np.int32)
     stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
     t0 = time.perf_counter()
@@ -76,7 +83,8 @@ def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
     wbytes = cfg["L"] * per_layer + synth.weight_bytes(cfg["dt_head"], cfg["V"], cfg["D"])
     if rank == 0:
         print(json.dumps({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps, "n_gpus": world,
-                      "sharding": "FFN and LM-head rows over ranks, NCCL all-gather after each" if world > 1 else "none",
+                      "sharding": "none" if world == 1 else "FFN and LM-head rows over ranks, " +
+                      ("rows stored into the peers' buffers by the GEMVs, flags" if args.gather == "peer" else "NCCL all-gather after each"),
                       "tokens_equal_on_all_ranks": same,
                       "lane": "host call per op" if args.no_graph else "CUDA graph per token",
                       "decode_tok_per_s": round(args.steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / args.steps, 4),
@@ -88,7 +96,11 @@ def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
                       "first_tokens": [int(t) for t in toks[:8]], "model_build_s": round(t_gen, 1)}), flush=True)
     m.close()
     if dist:
+        dist.barrier()
         lib.check(L.tm_cuda_comm_destroy(), "tm_cuda_comm_destroy")
+        lib.check(L.tm_cuda_peer_unmap(), "tm_cuda_peer_unmap")
+        dist.barrier()
+        lib.check(L.tm_cuda_peer_close(), "tm_cuda_peer_close")
         dist.barrier()
         dist.destroy_process_group()
 
@@ -99,6 +111,7 @@ def main() -> None:
     ap.add_argument("--model", choices=["llama3-8b", "tiny"], default="llama3-8b", help="architecture of --op chain")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--gather", choices=["nccl", "peer"], default="peer", help="--op chain on several GPUs: how shards are gathered")
     ap.add_argument("--no-graph", action="store_true", help="--op chain: one host call per op instead of the graph lane")
     ap.add_argument("--dtype", default="Q8_0", choices=sorted(NAMES))
     ap.add_argument("--m", type=int, default=2000)

@@ -10,9 +10,9 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(world: int, port: int) -> dict:
+def _run(world: int, port: int, gather: str = "nccl") -> dict:
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    case = ["-m", "tensormark_b200.run_case", "--op", "chain", "--model", "tiny", "--prompt", "8", "--steps", "24"]
+    case = ["-m", "tensormark_b200.run_case", "--op", "chain", "--model", "tiny", "--prompt", "8", "--steps", "24", "--gather", gather]
     if world == 1:
         cmd = [sys.executable] + case
     else:
@@ -30,8 +30,9 @@ def test_sharded_chain_matches_single_gpu(torch_mod):
     if torch_mod.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     one = _run(1, 0)
-    two = _run(2, 29631)
-    assert two["n_gpus"] == 2 and two["tokens_equal_on_all_ranks"]
-    # each output row is one dot product whichever rank computes it; the split of a row over warps can
-    # differ between the full and the sharded launch, so logits agree to rounding and greedy tokens agree
-    assert two["first_tokens"] == one["first_tokens"]
+    for gather, port in (("nccl", 29631), ("peer", 29632)):
+        two = _run(2, port, gather)
+        assert two["n_gpus"] == 2 and two["tokens_equal_on_all_ranks"], gather
+        # each output row is one dot product whichever rank computes it; the split of a row over warps can
+        # differ between the full and the sharded launch, so logits agree to rounding and greedy tokens agree
+        assert two["first_tokens"] == one["first_tokens"], gather

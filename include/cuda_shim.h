@@ -54,6 +54,13 @@ const char* tm_cuda_last_error(void);
 unsigned long long tm_cuda_fallback_count(void);
 /* Number of kernels of this library launched so far in this process. */
 unsigned long long tm_cuda_launch_count(void);
+/* Kernel timeline, for tuning (no counterpart in the reference). With TM_CUDA_TRACE=1 in the
+ * environment at tm_cuda_init, CTA 0 of every GEMV records six 64-bit words: %globaltimer (ns) at its
+ * start, after the wait for the preceding kernel, after x is staged, at its end; then (N << 32 | K) and
+ * (dtype | x_op << 8 | warps << 16 | rows-per-item << 24). tm_cuda_trace_read synchronises the lane,
+ * copies up to cap_launches records (in launch-start order) and clears the log. Returns the count; 0
+ * when tracing is off. At most 8192 launches are kept between reads. */
+size_t tm_cuda_trace_read(unsigned long long* out, size_t cap_launches);
 /* Number of multiprocessors of the selected device. */
 int tm_cuda_sm_count(void);
 
@@ -79,7 +86,10 @@ bool tm_cuda_sgemm_q(const float* A, const void* W, float* C, unsigned M, unsign
  * (quant.h:194-200, 267-277, 304-330, 338-365, 397-408). The fp32 form of
  * q4_dequant_f32 (metal.h:1516-1562), for every block dtype. */
 bool tm_cuda_dequant(const void* W, float* out, unsigned N, unsigned K, unsigned dtype);
-/* Drop every cached weight copy made by the host-pointer entries. */
+/* Drop every device copy of weights this library holds: the caches of the host-pointer entries, the
+ * token lane's registrations (their handles become invalid; handle ids are not reused), the cached norm
+ * weights, and every lane graph. Copies are keyed by HOST address, as in the reference, so a caller
+ * that frees a tensor and may get the same address back for another one calls this in between. */
 void tm_cuda_release_weights(void);
 
 /* ---- device-pointer kernels ---------------------------------------------- */
@@ -197,6 +207,12 @@ void tm_cuda_tok_qkv_post_at(int qkvslot, int kcslot, int vcslot, unsigned H, un
 void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int outslot, unsigned QD, unsigned H,
                          unsigned KVH, unsigned dh, unsigned ctx, float scale, unsigned REP, int stateslot);
 /* tok[index + 1] = argmax(x[0..n)); the token slot holds max_tokens entries. */
+/* tok_qkv_post_at and tok_attn_at as ONE launch: rope(q), rope(k) -> K cache, v -> V cache, attention
+ * over [0, position] and the merge of its splits. qkvslot holds the token's un-rotated [q | k | v]; q is
+ * not written back. probslot is scratch: (dh + 2) * H * 4 bytes per split, as many splits as fit up to
+ * one CTA per SM. (metal.h:3950-4030, 4153-4222 in one dispatch.) */
+void tm_cuda_tok_attn_fused_at(int qkvslot, int kcslot, int vcslot, int probslot, int outslot, unsigned H, unsigned KVH,
+                               unsigned dh, unsigned ctx, float scale, float theta, int stateslot);
 void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot);
 /* x = row tok[index] of the embedding table. */
 void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,

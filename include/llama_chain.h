@@ -16,7 +16,7 @@
 //     of include/cuda_shim.h (position and token index live in a device "chain state"), captured
 //     in a CUDA graph, and replayed per token. RMSNorm and SiLU*up ride in the staging of the
 //     following GEMV, the residual adds in the epilogue of the o / down GEMVs, and rope(q),
-//     rope(k)->cache and v->cache are one launch: 7 launches per layer instead of 14.
+//     rope(k)->cache, v->cache, attention and the merge of its splits are one launch: 5 launches per layer instead of 14.
 //
 // Scope: dense Llama-style layers, block-quantized projections (Q8_0/Q4_0/Q4_1/Q5_K/Q6_K),
 // GQA attention, greedy choice. Tokenizers, sampling front ends, hybrid/GDN layers, speculative
@@ -130,6 +130,10 @@ public:
         embed_ = reg(d_.embed, d_.dt_embed, d_.V, d_.D);
         head_ = reg_shard(d_.head, d_.dt_head, d_.V, d_.D);
         const size_t D4 = (size_t)d_.D * 4;
+        // attention scratch: the reference's size, and room for one split per SM of the fused chain kernel
+        size_t probs_bytes = (size_t)d_.H * d_.ctx * 4;
+        const size_t per_split = (size_t)d_.H * (d_.dh + 2) * 4, want = per_split * (size_t)(tm_cuda_sm_count() / d_.KVH + 1);
+        if (probs_bytes < want) probs_bytes = want;
         if (d_.world > 1 && d_.peer_gather &&
             !(tm_cuda_tok_reserve_shared(SLOT_X, D4) && tm_cuda_tok_reserve_shared(SLOT_GU, (size_t)2 * d_.F * 4) &&
               tm_cuda_tok_reserve_shared(SLOT_LOGITS, (size_t)d_.V * 4)))
@@ -138,7 +142,7 @@ public:
                   tm_cuda_tok_reserve(SLOT_H2S, D4) && tm_cuda_tok_reserve(SLOT_DN, D4) && tm_cuda_tok_reserve(SLOT_XF, D4) &&
                   tm_cuda_tok_reserve(SLOT_QKV, (size_t)(QD + 2 * KVD) * 4) && tm_cuda_tok_reserve(SLOT_AO, (size_t)QD * 4) &&
                   tm_cuda_tok_reserve(SLOT_GU, (size_t)2 * d_.F * 4) && tm_cuda_tok_reserve(SLOT_LOGITS, (size_t)d_.V * 4) &&
-                  tm_cuda_tok_reserve(SLOT_PROBS, (size_t)d_.H * d_.ctx * 4) && tm_cuda_tok_reserve(SLOT_STATE, 64) &&
+                  tm_cuda_tok_reserve(SLOT_PROBS, probs_bytes) && tm_cuda_tok_reserve(SLOT_STATE, 64) &&
                   tm_cuda_tok_reserve(SLOT_ACT, (size_t)d_.F * 4);
         if (!ok) throw std::runtime_error("cuda: packed slot reservation failed");
         const size_t kv = (size_t)d_.KVH * d_.ctx * d_.dh;
@@ -205,7 +209,7 @@ public:
     // Chain form of the same token: position and token index come from SLOT_STATE on the device,
     // norms / SiLU / residuals are folded into the GEMVs. Encoded once and captured.
     void encode_chain_token(unsigned max_tokens) {
-        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh, REP = d_.H / d_.KVH;
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh;
         const float scale = 1.f / std::sqrt((float)d_.dh);
         const unsigned dt = d_.dt_proj;
         tm_cuda_tok_embed_at(SLOT_TOK, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed, max_tokens, SLOT_STATE);
@@ -225,9 +229,8 @@ public:
                     yoff += (size_t)qkv_rows[i] * 4;
                 }
             }
-            tm_cuda_tok_qkv_post_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, (unsigned)d_.H, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, d_.theta, SLOT_STATE);
-            tm_cuda_tok_attn_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)QD, (unsigned)d_.H, (unsigned)d_.KVH,
-                                (unsigned)d_.dh, (unsigned)d_.ctx, scale, (unsigned)REP, SLOT_STATE);
+            tm_cuda_tok_attn_fused_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)d_.H, (unsigned)d_.KVH,
+                                      (unsigned)d_.dh, (unsigned)d_.ctx, scale, d_.theta, SLOT_STATE);
             const unsigned Dn = (unsigned)d_.D, Fn = (unsigned)d_.F;
             tm_cuda_tok_gemv_fused(SLOT_AO, 0, 0, 0, 0, nullptr, 0.f, r.o.id, SLOT_X, 0, Dn, (unsigned)QD, dt, &r.o.woff, &Dn, 1, 1);
             if (d_.world > 1) {
@@ -275,7 +278,7 @@ public:
     // a shard writes its rows at their place in the full vector, here and on every peer; the first
     // kernel that reads a gathered vector waits for the other ranks' rows.
     void encode_chain_token_peer(unsigned max_tokens) {
-        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh, REP = d_.H / d_.KVH;
+        const int QD = d_.H * d_.dh, KVD = d_.KVH * d_.dh;
         const float scale = 1.f / std::sqrt((float)d_.dh);
         const unsigned dt = d_.dt_proj, Dn = (unsigned)d_.D, Fn = (unsigned)d_.F, Vn = (unsigned)d_.V;
         const unsigned Fs = Fn / (unsigned)d_.world, Ds = Dn / (unsigned)d_.world, Vs = Vn / (unsigned)d_.world;
@@ -288,9 +291,8 @@ public:
             const size_t qkv_yoff[3] = {0, (size_t)QD * 4, (size_t)(QD + KVD) * 4};
             tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, s.rms1, d_.eps, r.q.id, SLOT_QKV, qkv_yoff, (unsigned)(QD + 2 * KVD), Dn, dt,
                                   qkv_woff, qkv_rows, 3, 0, l > 0 ? 2 * l - 1 : -1, -1, SLOT_STATE);
-            tm_cuda_tok_qkv_post_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, (unsigned)d_.H, (unsigned)d_.KVH, (unsigned)d_.dh, (unsigned)d_.ctx, d_.theta, SLOT_STATE);
-            tm_cuda_tok_attn_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)QD, (unsigned)d_.H, (unsigned)d_.KVH,
-                                (unsigned)d_.dh, (unsigned)d_.ctx, scale, (unsigned)REP, SLOT_STATE);
+            tm_cuda_tok_attn_fused_at(SLOT_QKV, SLOT_KC + l, SLOT_VC + l, SLOT_PROBS, SLOT_AO, (unsigned)d_.H, (unsigned)d_.KVH,
+                                      (unsigned)d_.dh, (unsigned)d_.ctx, scale, d_.theta, SLOT_STATE);
             tm_cuda_tok_gemv_fused(SLOT_AO, 0, 0, 0, 0, nullptr, 0.f, r.o.id, SLOT_X, 0, Dn, (unsigned)QD, dt, &r.o.woff, &Dn, 1, 1);
             const uint64_t gu_woff[2] = {r.gate.woff, r.up.woff};
             const unsigned gu_rows[2] = {Fs, Fs};

@@ -26,7 +26,11 @@ bool fail(const char* fmt, ...);            // records the message, bumps the fa
 void note_launch(unsigned n = 1);           // counts kernels launched by this library
 bool check_launch(const char* what);        // cudaGetLastError -> fail()
 int device_sm_count();
-int* device_status_word();                  // device int the kernels write a nonzero code to when a bounded wait ran out
+int* device_status_word();
+// Kernel timeline (off unless TM_CUDA_TRACE=1): CTA 0 of every GEMV stamps %globaltimer at its start, after
+// the wait for its predecessor, after x is staged and at its end, plus its shape: kTraceWords words per launch.
+constexpr int kTraceWords = 6, kTraceLaunches = 8192;
+unsigned long long* device_trace();         // nullptr when tracing is off                  // device int the kernels write a nonzero code to when a bounded wait ran out
 
 constexpr int kMaxSeg = 16;
 struct SegTable {                           // rows [row_end[s-1], row_end[s]) start at byte woff[s]

@@ -49,6 +49,7 @@ bool check_launch(const char* what) {
 
 int device_sm_count() { return state().sm_count; }
 int* device_status_word() { return state().status_dev; }
+unsigned long long* device_trace() { return state().trace_dev; }
 
 bool ensure_init(int device) {
     State& s = state();
@@ -76,6 +77,12 @@ bool ensure_init(int device) {
     if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return check_launch("cudaStreamCreate");
     if (cudaMalloc(&s.status_dev, 64) != cudaSuccess) return check_launch("cudaMalloc(status)");
     cudaMemset(s.status_dev, 0, 64);
+    const char* tr = std::getenv("TM_CUDA_TRACE");
+    if (tr && *tr == '1') {
+        const size_t words = 1 + (size_t)kTraceWords * kTraceLaunches;
+        if (cudaMalloc(&s.trace_dev, words * 8) != cudaSuccess) return check_launch("cudaMalloc(trace)");
+        cudaMemset(s.trace_dev, 0, words * 8);
+    }
     const char* v = std::getenv("TM_CUDA_VERBOSE");
     s.verbose = v && *v == '1';
     const char* kh = std::getenv("TM_CUDA_KV_HALF");
@@ -272,12 +279,32 @@ bool tm_cuda_q4_prefill(const float* A, const void* const* Wqs, const unsigned* 
     return gemm_parts_host(A, Wqs, Ns, nparts, C, M, K, DT_Q4_0);
 }
 
+size_t tm_cuda_trace_read(unsigned long long* out, size_t cap_launches) {
+    State& s = state();
+    if (!s.ready || !s.trace_dev || !out) return 0;
+    cudaStreamSynchronize(s.stream);
+    unsigned long long n = 0;
+    if (cudaMemcpy(&n, s.trace_dev, 8, cudaMemcpyDeviceToHost) != cudaSuccess) { check_launch("trace_read"); return 0; }
+    if (n > (unsigned long long)kTraceLaunches) n = kTraceLaunches;
+    if (n > cap_launches) n = cap_launches;
+    if (n && cudaMemcpy(out, s.trace_dev + 1, n * kTraceWords * 8, cudaMemcpyDeviceToHost) != cudaSuccess) { check_launch("trace_read"); return 0; }
+    cudaMemset(s.trace_dev, 0, 8);
+    return (size_t)n;
+}
+
 void tm_cuda_release_weights(void) {
     State& s = state();
     if (!s.ready) return;
     cudaStreamSynchronize(s.stream);
     for (auto& kv : s.wcache) cudaFree(kv.second);
     s.wcache.clear();
+    // the lane's registrations are keyed by host address too: graphs first (they hold the device pointers)
+    tm_cuda_tok_graph_destroy(-1);
+    for (WeightBuf& w : s.wbufs) if (w.ptr) { cudaFree(w.ptr); w.ptr = nullptr; w.bytes = 0; }
+    s.wreg.clear();
+    s.shared_base = nullptr; s.shared_id = -1;
+    for (auto& kv : s.norm_w) cudaFree(kv.second);
+    s.norm_w.clear();
 }
 
 // ---- the reference's symbol names ----------------------------------------------

@@ -56,6 +56,7 @@ struct GemvParams {
     uint32_t accumulate;
     SegTable seg;
     Exchange xc;                // row-sharded models: wait for peers before x, push y to peers after
+    unsigned long long* trace;  // kernel timeline, nullptr when off
     int* status;
 };
 
@@ -155,6 +156,16 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     constexpr int ROWCAP = L::STEP_BYTES;                  // multiple of 16
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* tr = nullptr;                       // this launch's timeline record (CTA 0, thread 0 only)
+    if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+        const unsigned long long slot = atomicAdd(p.trace, 1ull);
+        if (slot < (unsigned long long)kTraceLaunches) {
+            tr = p.trace + 1 + slot * kTraceWords;
+            tr[0] = global_ns();
+            tr[4] = ((unsigned long long)p.N << 32) | p.K;
+            tr[5] = (unsigned long long)DT | ((unsigned long long)p.x_op << 8) | ((unsigned long long)kWarps << 16) | ((unsigned long long)R << 24);
+        }
+    }
     const uint32_t nchunks = (p.K + L::STEP_W - 1) / L::STEP_W;
     const uint32_t nunits = nchunks * 32u;
     uint32_t* units = reinterpret_cast<uint32_t*>(smem);
@@ -198,6 +209,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     exchange_wait(p.xc, p.status);                          // sharded models: x is complete once every peer has pushed
+    if (tr) tr[1] = global_ns();
 
     // ---- stage x: block floating point planes in the lanes' byte layout -------
     // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
@@ -289,6 +301,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         }
     }
     __syncthreads();
+    if (tr) tr[2] = global_ns();
 
     // ---- consume -------------------------------------------------------------
     typename L::X xr;
@@ -374,6 +387,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         __syncthreads();                                    // every row of this CTA is in y
         exchange_push(p, cta_lo, cta_hi);
     }
+    if (tr) tr[3] = global_ns();
     if (dead) {
         // A copy never completed. Record it, give the copies still in flight a last
         // bounded chance to land (they target this CTA's shared memory) and leave.
@@ -634,7 +648,7 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     GemvParams p;
     p.W = W; p.x = x; p.y = y; p.N = N; p.K = K;
     p.row_bytes = (K / be) * block_bytes(dtype);
-    p.seg = seg; p.status = device_status_word();
+    p.seg = seg; p.status = device_status_word(); p.trace = device_trace();
     p.x2 = nullptr; p.eps = 0.f; p.x_op = 0; p.accumulate = 0;
     p.xc = Exchange{};
     if (fuse && fuse->xchg) p.xc = *fuse->xchg;

@@ -12,10 +12,34 @@
 #include "exchange.cuh"
 #include "qdecode.cuh"
 
+#include <cstdlib>
+
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
 namespace tmc {
+
+// Programmatic dependent launch for the chain's small kernels: each one lets its successor become
+// resident at once and then waits for its predecessor before it touches any data. A GEMV that
+// follows such a kernel is then already on the SMs, pulling its weights, while the small kernel runs.
+// Every CTA executes the wait before it can exit, so completion stays transitive along the stream.
+// These kernels are resident while their producer still writes, so pointers to produced data carry
+// no __restrict__: the compiler must not route those loads through the read-only cache.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... P, typename... A>
+static void launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, cudaStream_t st, A... args) {
+    static const bool on = [] { const char* e = std::getenv("TM_GLUE_PDL"); return !(e && *e == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = on ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
 
 namespace {
 
@@ -115,9 +139,10 @@ __global__ void bias_kernel(float* __restrict__ y, const float* __restrict__ bia
 // 0xFFFFFFFF (a chain slot not yet written) gives zeros.
 // `st` (optional) is a device-resident chain state {position, token index, forced count}: when given, the index comes
 // from it; entries below the forced count are prompt tokens that the chooser must not overwrite.
-__global__ void embed_row_kernel(const uint32_t* __restrict__ tok, uint32_t idx, const uint8_t* __restrict__ W,
-                                 float* __restrict__ x, uint32_t D, uint32_t row_bytes, unsigned dtype,
-                                 const int* __restrict__ st) {
+__global__ void embed_row_kernel(const uint32_t* tok, uint32_t idx, const uint8_t* __restrict__ W,
+                                 float* x, uint32_t D, uint32_t row_bytes, unsigned dtype,
+                                 const int* st) {
+    pdl_enter();
     const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= D) return;
     if (st) idx = (uint32_t)st[1];
@@ -139,10 +164,11 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
 }
 
 template <bool SAMPLE>
-__global__ void __launch_bounds__(256) choose_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, uint32_t n,
+__global__ void __launch_bounds__(256) choose_kernel(const float* x, uint32_t* out, uint32_t n,
                                                       uint32_t idx, float inv_temp, uint32_t seed,
-                                                      unsigned long long* __restrict__ scratch /* [0]=key, [1]=done */,
-                                                      const int* __restrict__ st, const Exchange xc, int* status) {
+                                                      unsigned long long* scratch /* [0]=key, [1]=done */,
+                                                      const int* st, const Exchange xc, int* status) {
+    pdl_enter();
     __shared__ unsigned long long best_s[8];
     if (st) {
         idx = (uint32_t)st[1] + 1u;                         // chain: the token chosen now is fed by the next step
@@ -192,11 +218,12 @@ __global__ void __launch_bounds__(256) choose_kernel(const float* __restrict__ x
 // shared memory and the CTA writes one unnormalised partial per query head:
 // part[(split*H + head)*dh + d] and stat[(split*H + head)*2] = (max, sum).
 template <typename T, int DPL, int REP>
-__global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict__ q, const T* __restrict__ kc,
-                                                          const T* __restrict__ vc, float* __restrict__ part,
-                                                          float* __restrict__ stat, uint32_t H, uint32_t ctx,
+__global__ void __launch_bounds__(128) attn_split_kernel(const float* q, const T* kc,
+                                                          const T* vc, float* part,
+                                                          float* stat, uint32_t H, uint32_t ctx,
                                                           uint32_t allow, uint32_t chunk, float scale,
-                                                          const int* __restrict__ st) {
+                                                          const int* st) {
+    pdl_enter();
     constexpr int dh = DPL * 32;
     if (st) {                                               // chain: attend [0, position] with the grid's fixed split count
         allow = min((uint32_t)st[0] + 1u, ctx);
@@ -268,8 +295,9 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
 }
 
 // out[head][d] = sum_s e^(m_s - M) part_s[d] / sum_s e^(m_s - M) l_s
-__global__ void attn_combine_kernel(const float* __restrict__ part, const float* __restrict__ stat, float* __restrict__ out,
+__global__ void attn_combine_kernel(const float* part, const float* stat, float* out,
                                     uint32_t H, uint32_t dh, uint32_t nsplit) {
+    pdl_enter();
     const uint32_t head = blockIdx.x;
     float M = -CUDART_INF_F;
     for (uint32_t s = 0; s < nsplit; ++s) M = fmaxf(M, stat[((size_t)s * H + head) * 2]);
@@ -292,9 +320,10 @@ __global__ void attn_combine_kernel(const float* __restrict__ part, const float*
 // Chain form of rope(q) + rope(k) -> cache + v -> cache in one launch, position read from the chain state.
 // qkv = [q: H*dh | k: KVH*dh | v: KVH*dh]; thread t < (H+KVH)*dh/2 rotates one pair, the rest copy V.
 template <typename T>
-__global__ void qkv_post_kernel(float* __restrict__ qkv, T* __restrict__ kcache, T* __restrict__ vcache, uint32_t H,
+__global__ void qkv_post_kernel(float* qkv, T* kcache, T* vcache, uint32_t H,
                                 uint32_t KVH, uint32_t dh, uint32_t ctx, const float2* __restrict__ tbl, uint32_t tbl_n,
-                                const int* __restrict__ st) {
+                                const int* st) {
+    pdl_enter();
     const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x, half = dh / 2;
     const int pos = st[0];
     if (pos < 0 || (uint32_t)pos >= ctx) return;
@@ -316,7 +345,7 @@ __global__ void qkv_post_kernel(float* __restrict__ qkv, T* __restrict__ kcache,
         vcache[(size_t)kv * ctx * dh + (size_t)pos * dh + l] = to_cache<T>(qkv[(size_t)(H + KVH) * dh + e]);
     }
 }
-__global__ void advance_kernel(int* __restrict__ st) { st[0] += 1; st[1] += 1; st[3] += 1; }   // position, token index, exchange epoch
+__global__ void advance_kernel(int* st) { pdl_enter(); st[0] += 1; st[1] += 1; st[3] += 1; }   // position, token index, exchange epoch
 
 inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
 
@@ -326,10 +355,10 @@ bool launch_attn_rep(const float* q, const T* kc, const T* vc, float* part, floa
                      const int* state, cudaStream_t st) {
     const dim3 grid(KVH, nsplit);
     switch (REP) {
-        case 1: attn_split_kernel<T, DPL, 1><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
-        case 2: attn_split_kernel<T, DPL, 2><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
-        case 4: attn_split_kernel<T, DPL, 4><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
-        case 8: attn_split_kernel<T, DPL, 8><<<grid, 128, 0, st>>>(q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 1: launch_pdl(attn_split_kernel<T, DPL, 1>, grid, dim3(128), st, q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 2: launch_pdl(attn_split_kernel<T, DPL, 2>, grid, dim3(128), st, q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 4: launch_pdl(attn_split_kernel<T, DPL, 4>, grid, dim3(128), st, q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
+        case 8: launch_pdl(attn_split_kernel<T, DPL, 8>, grid, dim3(128), st, q, kc, vc, part, stat, H, ctx, allow, chunk, scale, state); break;
         default: return fail("attention: REP=%u unsupported (1, 2, 4 or 8)", REP);
     }
     note_launch();
@@ -412,7 +441,7 @@ bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float
                       const int* state) {
     const unsigned be = block_elems(dtype);
     if (!be || dtype == DT_F16 || D % be) return fail("embed: D=%u is not whole blocks of dtype %u", D, dtype);
-    embed_row_kernel<<<cdiv(D, 256), 256, 0, st>>>(tok, idx, W, x, D, (D / be) * block_bytes(dtype), dtype, state);
+    launch_pdl(embed_row_kernel, dim3(cdiv(D, 256)), dim3(256), st, tok, idx, W, x, D, (D / be) * block_bytes(dtype), dtype, state);
     note_launch();
     return check_launch("embed_row");
 }
@@ -424,8 +453,8 @@ bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, floa
     if (grid > sms) grid = sms;
     const Exchange xc = xchg ? *xchg : Exchange{};
     if (xc.nwait && (!xc.wait_flags || !xc.epoch)) return fail("argmax: incomplete peer exchange description");
-    if (sample) choose_kernel<true><<<grid, 256, 0, st>>>(x, out, n, idx, inv_temp, seed, scratch, state, xc, device_status_word());
-    else choose_kernel<false><<<grid, 256, 0, st>>>(x, out, n, idx, 0.f, 0u, scratch, state, xc, device_status_word());
+    if (sample) launch_pdl(choose_kernel<true>, dim3(grid), dim3(256), st, x, out, n, idx, inv_temp, seed, scratch, state, xc, device_status_word());
+    else launch_pdl(choose_kernel<false>, dim3(grid), dim3(256), st, x, out, n, idx, 0.f, 0u, scratch, state, xc, device_status_word());
     note_launch();
     return check_launch("argmax");
 }
@@ -433,13 +462,13 @@ bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, floa
 bool launch_qkv_post(float* qkv, void* kc, void* vc, bool half_cache, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
                      const float* tbl, unsigned tbl_entries, const int* state, cudaStream_t st) {
     const unsigned n = (H + KVH) * (dh / 2) + KVH * dh;
-    if (half_cache) qkv_post_kernel<__half><<<cdiv(n, 256), 256, 0, st>>>(qkv, (__half*)kc, (__half*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
-    else qkv_post_kernel<float><<<cdiv(n, 256), 256, 0, st>>>(qkv, (float*)kc, (float*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
+    if (half_cache) launch_pdl(qkv_post_kernel<__half>, dim3(cdiv(n, 256)), dim3(256), st, qkv, (__half*)kc, (__half*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
+    else launch_pdl(qkv_post_kernel<float>, dim3(cdiv(n, 256)), dim3(256), st, qkv, (float*)kc, (float*)vc, H, KVH, dh, ctx, (const float2*)tbl, tbl_entries, state);
     note_launch();
     return check_launch("qkv_post");
 }
 bool launch_advance(int* state, cudaStream_t st) {
-    advance_kernel<<<1, 1, 0, st>>>(state);
+    launch_pdl(advance_kernel, dim3(1), dim3(1), st, state);
     note_launch();
     return check_launch("advance");
 }
@@ -477,7 +506,7 @@ bool launch_attention(const float* q, const void* kc, const void* vc, bool half_
                        : launch_attn_rep<float, 2>(q, (const float*)kc, (const float*)vc, part, stat, H, KVH, ctx, allow, pl.chunk, pl.nsplit, scale, REP, state, st);
     }
     if (!ok) return false;
-    attn_combine_kernel<<<H, dh < 128 ? 64 : 128, 0, st>>>(part, stat, out, H, dh, pl.nsplit);
+    launch_pdl(attn_combine_kernel, dim3(H), dim3(dh < 128 ? 64 : 128), st, part, stat, out, H, dh, pl.nsplit);
     note_launch();
     return check_launch("attn_combine");
 }

@@ -41,5 +41,11 @@ bool launch_attention(const float* q, const void* kc, const void* vc, bool half_
 bool launch_qkv_post(float* qkv, void* kc, void* vc, bool half_cache, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,
                      const float* tbl, unsigned tbl_entries, const int* state, cudaStream_t st);
 bool launch_advance(int* state, cudaStream_t st);
+// One launch for rope(q), rope(k) -> cache, v -> cache, split-K attention over [0, position] and the merge
+// (attn_fused.cu). qkv = [q | k | v] of the current token, un-rotated; scratch as for launch_attention.
+unsigned attn_fused_splits(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, size_t scratch_bytes);
+bool launch_attn_fused(const float* qkv, void* kc, void* vc, bool half_cache, float* scratch, size_t scratch_bytes, float* out,
+                       unsigned H, unsigned KVH, unsigned dh, unsigned ctx, float scale, const float* tbl, unsigned tbl_entries,
+                       const int* state, cudaStream_t st);
 
 }  // namespace tmc

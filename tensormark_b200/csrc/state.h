@@ -51,6 +51,7 @@ struct State {
     int device = -1, sm_count = 0;
     cudaStream_t stream = nullptr;
     int* status_dev = nullptr;
+    unsigned long long* trace_dev = nullptr;                    // TM_CUDA_TRACE=1: [0] = launches recorded, then kTraceWords per launch
     std::string last_error;
     unsigned long long fallbacks = 0, launches = 0;
 

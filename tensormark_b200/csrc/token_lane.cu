@@ -616,6 +616,23 @@ void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int ou
     if (!pl.nsplit) { latch("tok_attn_at: probs slot too small for one split"); return; }
     if (!launch_attention(q, kc, vc, s.kv_half, probs, out, H, KVH, dh, ctx, ctx, scale, REP, pl, s.stream, st)) s.sticky = true;
 }
+void tm_cuda_tok_attn_fused_at(int qkvslot, int kcslot, int vcslot, int probslot, int outslot, unsigned H, unsigned KVH,
+                               unsigned dh, unsigned ctx, float scale, float theta, int stateslot) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const char* who = "tok_attn_fused_at";
+    if (!H || !KVH || !dh || !ctx || H % KVH || !std::isfinite(scale) || scale <= 0) { latch("%s: invalid attention dimensions or scale", who); return; }
+    if (!ensure_rope(dh, ctx, theta)) return;
+    const float* qkv = (const float*)slot_ptr(qkvslot, (size_t)(H + 2 * KVH) * dh * 4, who);
+    uint8_t* kc = slot_ptr(kcslot, kv_elem() * KVH * ctx * dh, who);
+    uint8_t* vc = slot_ptr(vcslot, kv_elem() * KVH * ctx * dh, who);
+    float* out = (float*)slot_ptr(outslot, (size_t)H * dh * 4, who);
+    float* probs = (float*)slot_ptr(probslot, (size_t)H * (dh + 2) * 4, who);
+    const int* st = state_ptr(stateslot, who);
+    if (!qkv || !kc || !vc || !out || !probs || !st) return;
+    if (!launch_attn_fused(qkv, kc, vc, s.kv_half, probs, s.slots[probslot].bytes, out, H, KVH, dh, ctx, scale, s.rope_tbl,
+                           s.rope_cap * (dh / 2), st, s.stream)) s.sticky = true;
+}
 static void argmax_at_impl(const char* who, int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site) {
     if (!ensure_init(-1)) return;
     State& s = state();

@@ -45,7 +45,11 @@ TMCHAIN_API void* tmchain_create(const int* cfg, float theta, float eps, const v
         return h.release();
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
-TMCHAIN_API void tmchain_destroy(void* p) { delete static_cast<Holder*>(p); }
+// Also drops the lane's weight registrations: they are keyed by the host addresses of this model's tensors.
+TMCHAIN_API void tmchain_destroy(void* p) {
+    delete static_cast<Holder*>(p);
+    tm_cuda_release_weights();
+}
 TMCHAIN_API int tmchain_seen(void* p) { return static_cast<Holder*>(p)->m->seen; }
 TMCHAIN_API void tmchain_set_seen(void* p, int seen) { static_cast<Holder*>(p)->m->seen = seen; }
 

@@ -77,6 +77,7 @@ SIGNATURES = {
                                       C.POINTER(_u64), C.POINTER(_u), _u, C.c_int]),
     "tm_cuda_tok_qkv_post_at": (None, [C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_int]),
     "tm_cuda_tok_attn_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, _u, C.c_float, _u, C.c_int]),
+    "tm_cuda_tok_attn_fused_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_float, C.c_int]),
     "tm_cuda_tok_argmax_at": (None, [C.c_int, C.c_int, _u, _u, C.c_int]),
     "tm_cuda_tok_embed_at": (None, [C.c_int, C.c_int, _u64, C.c_int, _u, _u, _u, C.c_int]),
     "tm_cuda_tok_advance": (None, [C.c_int]),
@@ -102,6 +103,7 @@ SIGNATURES = {
     "tm_cuda_tok_gemv_xchg": (None, [C.c_int, _sz, C.c_int, C.c_int, _sz, _vp, C.c_float, C.c_int, C.c_int, C.POINTER(_sz), _u, _u, _u,
                                      C.POINTER(_u64), C.POINTER(_u), _u, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tm_cuda_tok_argmax_xchg": (None, [C.c_int, C.c_int, _u, _u, C.c_int, C.c_int]),
+    "tm_cuda_trace_read": (C.c_size_t, [_vp, C.c_size_t]),
     "tm_cuda_tok_slot_ptr": (_vp, [C.c_int]),
     "tm_cuda_tok_stream": (_vp, []),
 }

@@ -42,3 +42,12 @@ def torch_mod():
     import torch
     assert torch.cuda.is_available(), "a gpu-marked test ran without a CUDA device"
     return torch
+
+
+@pytest.fixture(autouse=True)
+def _fresh_weight_registrations(request):
+    """Weight copies on the device are keyed by host address; numpy reuses addresses between tests."""
+    yield
+    if request.node.get_closest_marker("gpu"):
+        from tensormark_b200 import lib
+        lib.load().tm_cuda_release_weights()

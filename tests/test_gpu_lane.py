@@ -299,3 +299,45 @@ def test_probe_copy_reads_registered_weights(cuda):
     wid, woff = wbuf(cuda, W)
     assert cuda.tm_cuda_tok_probe_copy(wid, 10, T1, 64), lib.last_error()
     assert np.array_equal(down(cuda, T1, 64, np.uint8), W.reshape(-1)[10:74])
+
+
+@pytest.mark.parametrize("dh,pos", [(128, 0), (128, 31), (128, 32), (128, 257), (64, 100)])
+def test_fused_chain_attention_equals_the_separate_launches(cuda, dh, pos):
+    """tok_attn_fused_at (one launch) against tok_qkv_post_at + tok_attn_at on the same inputs: the caches
+    receive bit-identical rows at the position, the outputs agree to fp32 rounding of a reordered sum."""
+    Hh, KVH, ctx = 8, 2, 300
+    QD, KVD = Hh * dh, KVH * dh
+    g = np.random.default_rng(1234 + pos)
+    qkv = g.standard_normal(QD + 2 * KVD).astype(np.float32)
+    hist_k = g.standard_normal(KVH * ctx * dh).astype(np.float32)
+    hist_v = g.standard_normal(KVH * ctx * dh).astype(np.float32)
+    S_QKV, S_KC1, S_VC1, S_KC2, S_VC2, S_P1, S_P2, S_O1, S_O2, S_ST = range(40, 50)
+    scale, theta = 1.0 / np.sqrt(dh), 500000.0
+    for s in (S_KC1, S_KC2):
+        assert cuda.tm_cuda_tok_kv_reserve(s, KVH * ctx * dh)
+        lib.check(cuda.tm_cuda_tok_kv_upload(s, 0, hist_k.ctypes.data, hist_k.size), "kv_upload")
+    for s in (S_VC1, S_VC2):
+        assert cuda.tm_cuda_tok_kv_reserve(s, KVH * ctx * dh)
+        lib.check(cuda.tm_cuda_tok_kv_upload(s, 0, hist_v.ctypes.data, hist_v.size), "kv_upload")
+    assert cuda.tm_cuda_tok_reserve(S_QKV, qkv.nbytes) and cuda.tm_cuda_tok_reserve(S_ST, 64)
+    assert cuda.tm_cuda_tok_reserve(S_O1, QD * 4) and cuda.tm_cuda_tok_reserve(S_O2, QD * 4)
+    assert cuda.tm_cuda_tok_reserve(S_P1, Hh * ctx * 4) and cuda.tm_cuda_tok_reserve(S_P2, Hh * (dh + 2) * 4 * 80)
+    up(cuda, S_ST, np.array([pos, 0, 0, 0], np.int32))
+    # separate launches (they rotate q in place, so the fused call gets a fresh copy afterwards)
+    up(cuda, S_QKV, qkv)
+    assert cuda.tm_cuda_tok_begin()
+    cuda.tm_cuda_tok_qkv_post_at(S_QKV, S_KC1, S_VC1, Hh, KVH, dh, ctx, theta, S_ST)
+    cuda.tm_cuda_tok_attn_at(S_QKV, S_KC1, S_VC1, S_P1, S_O1, QD, Hh, KVH, dh, ctx, scale, Hh // KVH, S_ST)
+    assert cuda.tm_cuda_tok_flush(), lib.last_error()
+    up(cuda, S_QKV, qkv)
+    assert cuda.tm_cuda_tok_begin()
+    cuda.tm_cuda_tok_attn_fused_at(S_QKV, S_KC2, S_VC2, S_P2, S_O2, Hh, KVH, dh, ctx, scale, theta, S_ST)
+    assert cuda.tm_cuda_tok_flush(), lib.last_error()
+    o1, o2 = down(cuda, S_O1, QD), down(cuda, S_O2, QD)
+    assert np.all(np.isfinite(o2))
+    assert np.max(np.abs(o1 - o2)) <= 2e-5 * max(1.0, np.max(np.abs(o1)))
+    for a, b in ((S_KC1, S_KC2), (S_VC1, S_VC2)):
+        ka, kb = np.empty(KVH * ctx * dh, np.float32), np.empty(KVH * ctx * dh, np.float32)
+        lib.check(cuda.tm_cuda_tok_kv_download(a, 0, ka.ctypes.data, ka.size), "kv_download")
+        lib.check(cuda.tm_cuda_tok_kv_download(b, 0, kb.ctypes.data, kb.size), "kv_download")
+        assert np.array_equal(ka.view(np.uint32), kb.view(np.uint32))

@@ -57,7 +57,9 @@ unsigned long long tm_cuda_launch_count(void);
 /* Kernel timeline, for tuning (no counterpart in the reference). With TM_CUDA_TRACE=1 in the
  * environment at tm_cuda_init, CTA 0 of every GEMV records six 64-bit words: %globaltimer (ns) at its
  * start, after the wait for the preceding kernel, after x is staged, at its end; then (N << 32 | K) and
- * (dtype | x_op << 8 | warps << 16 | rows-per-item << 24). tm_cuda_trace_read synchronises the lane,
+ * (dtype | x_op << 8 | warps << 16 | rows-per-item << 24). The fused chain attention records, for its
+ * CTA (0, 0): start, after the wait, after its prologue, after the split handoff, after its tiles, and
+ * the handoff time again (words 4 and 5 are then timestamps). tm_cuda_trace_read synchronises the lane,
  * copies up to cap_launches records (in launch-start order) and clears the log. Returns the count; 0
  * when tracing is off. At most 8192 launches are kept between reads. */
 size_t tm_cuda_trace_read(unsigned long long* out, size_t cap_launches);

@@ -35,6 +35,11 @@ namespace {
 
 constexpr unsigned kMaxSplits = 32;      // merge scratch in shared memory: 2 * REP * kMaxSplits floats
 
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void pdl_enter() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -87,8 +92,14 @@ template <typename T, int DPL, int REP>
 __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc, T* vc, float* part, float* stat,
                                                           unsigned* counters, float* out, uint32_t H, uint32_t KVH,
                                                           uint32_t ctx, float scale, const float2* __restrict__ tbl,
-                                                          uint32_t tbl_n, const int* st) {
+                                                          uint32_t tbl_n, const int* st, unsigned long long* trace) {
+    unsigned long long* tr = nullptr;                         // timeline of CTA (0, 0), thread 0 (see tm_cuda_trace_read)
+    if (trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+        const unsigned long long slot = atomicAdd(trace, 1ull);
+        if (slot < (unsigned long long)kTraceLaunches) { tr = trace + 1 + slot * kTraceWords; tr[0] = now_ns(); }
+    }
     pdl_enter();
+    if (tr) tr[1] = now_ns();
     constexpr int dh = DPL * 32, half = dh / 2;
     const uint32_t kv = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,6 +138,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc
         for (uint32_t j = threadIdx.x; j < (uint32_t)dh; j += 128) vdst[j] = to_cache<T>(__ldcg(vn + j));
     }
     __syncthreads();
+    if (tr) tr[2] = now_ns();
 
     // ---- this warp's tiles
     float m[REP], l[REP], acc[REP][DPL];
@@ -203,6 +215,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc
         }
     }
 
+    if (tr) tr[4] = now_ns();
     // ---- merge the four warps, leave this split's partial
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
@@ -237,6 +250,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc
         if (sm_last) counters[kv] = 0u;                       // re-armed for the next launch
     }
     __syncthreads();
+    if (tr) { tr[5] = now_ns(); tr[3] = tr[5]; }
     if (!sm_last) return;
     __threadfence();
     // statistics of every (head, split) into shared memory with one load each, then the weights
@@ -295,7 +309,7 @@ void launch_one(dim3 grid, cudaStream_t st, const float* qkv, void* kc, void* vc
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, attn_fused_kernel<T, DPL, REP>, qkv, (T*)kc, (T*)vc, part, stat, counters, out, (uint32_t)H, (uint32_t)KVH,
-                       (uint32_t)ctx, scale, (const float2*)tbl, (uint32_t)tbl_n, state);
+                       (uint32_t)ctx, scale, (const float2*)tbl, (uint32_t)tbl_n, state, device_trace());
 }
 
 template <typename T, int DPL>

@@ -93,6 +93,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// ---- thread-block clusters: the CTAs of a cluster share the staging of x ---------------------
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// The address of this CTA's shared-memory object `p` in CTA `rank` of the cluster (generic pointer).
+template <typename T> __device__ __forceinline__ T* cluster_map(T* p, uint32_t rank) {
+    uint64_t out;
+    asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"((uint64_t)(uintptr_t)p), "r"(rank));
+    return (T*)(uintptr_t)out;
+}
+
 __device__ __forceinline__ const uint8_t* row_ptr(const GemvParams& p, uint32_t row) {
     uint32_t s = 0, start = 0;
     while (s + 1 < p.seg.nseg && row >= p.seg.row_end[s]) { start = p.seg.row_end[s]; ++s; }
@@ -188,6 +200,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    const uint32_t csize = cluster_size(), crank = csize > 1 ? cluster_rank() : 0u;
+    if (csize > 1) cluster_arrive();                        // "this CTA runs": awaited before the first access to a peer's shared memory
 
     // Issue cursor (same value in every lane): next item = rows [irow, irow+R) x this warp's step.
     const uint32_t off = myc * (uint32_t)L::STEP_BYTES;
@@ -214,48 +228,59 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     // ---- stage x: block floating point planes in the lanes' byte layout -------
     // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
     // the run sums come from three shuffle stages, the plane bytes leave as packed stores.
-    // A warp stages four blocks per pass and two passes are interleaved.
-    float norm_inv = 1.f;
-    if (p.x_op == 1u) {
-        // RMSNorm folded into the staging: every CTA needs all of x anyway, so each one
-        // recomputes the (cheap) sum of squares instead of a separate kernel writing a normed copy.
-        __shared__ float red[kWarps];
-        const float4* xg = reinterpret_cast<const float4*>(p.x);
-        float ss = 0.f;
-        for (uint32_t i = threadIdx.x; i < p.K / 4; i += blockDim.x) {
-            const float4 t = __ldcg(xg + i);
-            ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) tot += red[w];
-        norm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-    }
+    // A warp stages eight blocks (256 activations, one "group") per pass.
+    //
+    // Every CTA needs all of x, and staging it costs as much as streaming a few hundred KB of
+    // weights, so the CTAs of a cluster share the work: CTA r of C stages groups [r*gpc, (r+1)*gpc)
+    // into ITS shared memory, and after the cluster barrier every warp reads its unit from the CTA
+    // that staged it (distributed shared memory). A launch without clusters is the case C = 1.
+    const uint32_t ngroups = (p.K + 255u) / 256u, gpc = (ngroups + csize - 1) / csize;
+    const uint32_t g_lo = min(ngroups, crank * gpc), g_hi = min(ngroups, g_lo + gpc);
+    __shared__ float xsum[8];                               // RMSNorm: one partial sum of squares per CTA of the cluster
+    __shared__ float red[kWarps];
     {
         constexpr int B = 2;
         const uint32_t nblk = p.K / 32, li = lane & 7u, sub = lane >> 3;
         const float4* xg4 = reinterpret_cast<const float4*>(p.x);
         const float4* x24 = reinterpret_cast<const float4*>(p.x2);
-        for (uint32_t b0 = warp * (4 * B); b0 < nblk; b0 += kWarps * (4 * B)) {
+        float ss = 0.f;
+        // The loads of the next group are issued before the current group is quantized: a warp's passes are
+        // otherwise a chain of L2 latencies.
+        float4 nv[B], nw[B];
+        auto fetch = [&](uint32_t g) {
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                const uint32_t b = g * (4 * B) + 4 * j + sub;
+                const bool in = g < g_hi && b < nblk;
+                nv[j] = in ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+                nw[j] = (in && p.x_op != 0u) ? __ldcg(x24 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        fetch(g_lo + warp);
+        for (uint32_t g = g_lo + warp; g < g_hi; g += kWarps) {
+            const uint32_t b0 = g * (4 * B);
             float4 v[B];
             float am[B], s8[B], s16[B], s32[B];
             bool bad[B];
+            float4 w2s[B];
+#pragma unroll
+            for (int j = 0; j < B; ++j) { v[j] = nv[j]; w2s[j] = nw[j]; }
+            fetch(g + kWarps);
 #pragma unroll
             for (int j = 0; j < B; ++j) {
                 const uint32_t b = b0 + 4 * j + sub;
-                v[j] = b < nblk ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
                 if (p.x_op != 0u && b < nblk) {
-                    const float4 w2 = __ldcg(x24 + b * 8 + li);
+                    const float4 w2 = w2s[j];
                     if (p.x_op == 1u) {
-                        v[j].x = v[j].x * norm_inv * w2.x; v[j].y = v[j].y * norm_inv * w2.y;
-                        v[j].z = v[j].z * norm_inv * w2.z; v[j].w = v[j].w * norm_inv * w2.w;
+                        // RMSNorm: x * w is staged; the factor rsqrt(mean(x^2) + eps) is one number for the whole
+                        // vector and multiplies the finished row sums instead
+                        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+                        v[j].x *= w2.x; v[j].y *= w2.y; v[j].z *= w2.z; v[j].w *= w2.w;
                     } else {
-                        v[j].x = v[j].x / (1.0f + expf(-v[j].x)) * w2.x; v[j].y = v[j].y / (1.0f + expf(-v[j].y)) * w2.y;
-                        v[j].z = v[j].z / (1.0f + expf(-v[j].z)) * w2.z; v[j].w = v[j].w / (1.0f + expf(-v[j].w)) * w2.w;
+                        // silu(x) * up with the hardware exponential and reciprocal: relative error 2^-21, far inside
+                        // what the three-plane quantization that follows keeps
+                        v[j].x = __fdividef(v[j].x, 1.0f + __expf(-v[j].x)) * w2.x; v[j].y = __fdividef(v[j].y, 1.0f + __expf(-v[j].y)) * w2.y;
+                        v[j].z = __fdividef(v[j].z, 1.0f + __expf(-v[j].z)) * w2.z; v[j].w = __fdividef(v[j].w, 1.0f + __expf(-v[j].w)) * w2.w;
                     }
                 }
                 am[j] = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
@@ -299,15 +324,55 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
                 }
             }
         }
+        if (p.x_op == 1u) {
+            // this CTA's share of sum(x^2), handed to every CTA of the cluster below
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp] = ss;
+        }
     }
-    __syncthreads();
+    if (csize > 1) {
+        cluster_wait();                                     // every CTA of the cluster has started
+        if (p.x_op == 1u) {
+            __syncthreads();
+            if (threadIdx.x < csize) {
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) tot += red[w];
+                *cluster_map(&xsum[crank], threadIdx.x) = tot;
+            }
+        }
+        cluster_arrive();                                   // x units and partial sums are in place ...
+        cluster_wait();                                     // ... in every CTA
+    } else {
+        __syncthreads();
+        if (p.x_op == 1u && threadIdx.x == 0) {
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) tot += red[w];
+            xsum[0] = tot;
+        }
+        if (p.x_op == 1u) __syncthreads();
+    }
+    float norm_inv = 1.f;
+    if (p.x_op == 1u) {
+        float tot = 0.f;
+        for (uint32_t c = 0; c < csize; ++c) tot += xsum[c];
+        norm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+    }
     if (tr) tr[2] = global_ns();
 
     // ---- consume -------------------------------------------------------------
     typename L::X xr;
     bool dead = false;
     uint32_t slot = 0, phase = 0, row0 = row_first;
-    if (items) load_x_unit<DT>(xr, units, myc * 32u + (uint32_t)lane);
+    if (items) {
+        const uint32_t u = myc * 32u + (uint32_t)lane;
+        constexpr uint32_t kUnitsPerGroup = 256u * 32u / (uint32_t)L::STEP_W;
+        const uint32_t owner = min(csize - 1u, (u / kUnitsPerGroup) / gpc);
+        load_x_unit<DT>(xr, csize > 1 ? cluster_map(units, owner) : units, u);
+    }
+    if (csize > 1) cluster_arrive();                        // this CTA is done with its peers' shared memory
     const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - myc * L::STEP_W);
     const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
     for (uint32_t t = 0; t < items; ++t) {
@@ -364,6 +429,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
             const uint32_t row = row0 + (uint32_t)my_row;
             if (nchunks == 1) {
                 const uint32_t e = y_index(p, row);
+                if (p.x_op == 1u) v *= norm_inv;
                 if (p.accumulate) v += p.y[e];              // residual add folded into the store
                 p.y[e] = v;
             } else {
@@ -379,6 +445,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
             float v = partial[(size_t)i * nchunks];
             for (uint32_t cc = 1; cc < nchunks; ++cc) v += partial[(size_t)i * nchunks + cc];
             const uint32_t e = y_index(p, cta_lo + i);
+            if (p.x_op == 1u) v *= norm_inv;
             if (p.accumulate) v += p.y[e];
             p.y[e] = v;
         }
@@ -388,6 +455,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         exchange_push(p, cta_lo, cta_hi);
     }
     if (tr) tr[3] = global_ns();
+    if (csize > 1) cluster_wait();                          // no CTA leaves while a peer may still read its x units
     if (dead) {
         // A copy never completed. Record it, give the copies still in flight a last
         // bounded chance to land (they target this CTA's shared memory) and leave.
@@ -535,7 +603,7 @@ int env_int(const char* name, int dflt) {
 }
 
 template <int DT, int R, int kWarps>
-bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, cudaStream_t st) {
+bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, unsigned cluster, cudaStream_t st) {
     p.stages = stages;
     static bool attr_set = false;
     static const bool pdl = env_int("TM_GEMV_PDL", 1) != 0;     // A/B knob: 0 launches without programmatic serialization
@@ -546,15 +614,50 @@ bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, 
         cudaFuncSetAttribute(gemv_stream<DT, R, kWarps>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_set = true;
     }
+    if (cluster > 1) grid = (grid + cluster - 1) / cluster * cluster;      // CTAs past the last row only help stage x
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchAttribute at[2];
+    unsigned na = 0;
+    if (pdl) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (cluster > 1) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = cluster; at[na].val.clusterDim.y = 1; at[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = at; cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, gemv_stream<DT, R, kWarps>, p) != cudaSuccess) return check_launch("gemv_stream");
     note_launch();
     return true;
+}
+
+// How many SMs a launch of one full-SM CTA per SM can cover when its CTAs come in clusters of `cluster`
+// (clusters live inside one GPC, so a GPC whose SM count is not a multiple of the cluster size leaves
+// SMs unused). Asked of the driver once per cluster size.
+template <int DT, int kWarps>
+unsigned cluster_sms(unsigned cluster, unsigned sms) {
+    static unsigned cached[9] = {};
+    if (cluster <= 1 || cluster > 8) return sms;
+    if (!cached[cluster]) {
+        cudaFuncSetAttribute(gemv_stream<DT, 1, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sms / cluster * cluster); cfg.blockDim = dim3(kWarps * 32);
+        cfg.dynamicSmemBytes = kWarps == 16 ? kSmemLimit : kHalfSmem;       // one CTA per SM (16 warps) or two (8 warps)
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = cluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemv_stream<DT, 1, kWarps>, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
+        unsigned got = (unsigned)n * cluster;
+        if (kWarps == 8) got /= 2;                                          // counted two CTAs per SM
+        cached[cluster] = got > sms ? sms : (got ? got : 1u);               // 1: clusters of this size do not fit at all
+    }
+    return cached[cluster];
 }
 
 template <int DT>
@@ -576,9 +679,22 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         int warps_cta = half ? 8 : ((p.N >= 8u * sms || nchunks > 8) ? 16 : 8);
         if ((force_w == 8 && nchunks <= 8) || force_w == 16) warps_cta = force_w;
         const size_t smem_limit = half ? kHalfSmem : kSmemLimit;
+        // Clusters can share the staging of x (see the kernel). Off by default: measured on B200, launching the
+        // GEMVs as clusters of 2 or 4 made every launch slower by more than the staging it saved (ten-GEMV
+        // sweep 129 vs 72 us, 8B chain 2.9 vs 2.25 ms per token; staging of K = 14336 fell from 10 to 5.7 us
+        // but the time from staged x to the last row grew by 6 us). TM_GEMV_CLUSTER=2 or 4 turns them on.
+        static const int force_c = env_int("TM_GEMV_CLUSTER", 1);
+        unsigned cluster = 1u;
+        if (force_c == 2 || force_c == 4) cluster = (unsigned)force_c;
+        unsigned sms_c = sms;
+        while (cluster > 1) {
+            sms_c = warps_cta == 16 ? cluster_sms<DT, 16>(cluster, sms) : cluster_sms<DT, 8>(cluster, sms);
+            if (sms_c * 16 >= sms * 15) break;               // at most 1/16 of the SMs lost to the cluster shape
+            cluster >>= 1; sms_c = sms;
+        }
         const unsigned teams = (unsigned)warps_cta / nchunks;
         unsigned grid = (p.N + teams - 1) / teams;
-        if (grid > sms) grid = sms;
+        if (grid > sms_c) grid = sms_c;
         p.rows_per_cta = (p.N + grid - 1) / grid;
         grid = (p.N + p.rows_per_cta - 1) / p.rows_per_cta;
         const unsigned rows_per_team = (p.rows_per_cta + teams - 1) / teams;
@@ -607,15 +723,15 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
             const size_t smem = fixed + (size_t)S * warps_cta * R * L::STEP_BYTES;
             if (warps_cta == 16) {
                 switch (R) {
-                    case 4: return launch_stream_r<DT, 4, 16>(p, S, grid, smem, st);
-                    case 2: return launch_stream_r<DT, 2, 16>(p, S, grid, smem, st);
-                    default: return launch_stream_r<DT, 1, 16>(p, S, grid, smem, st);
+                    case 4: return launch_stream_r<DT, 4, 16>(p, S, grid, smem, cluster, st);
+                    case 2: return launch_stream_r<DT, 2, 16>(p, S, grid, smem, cluster, st);
+                    default: return launch_stream_r<DT, 1, 16>(p, S, grid, smem, cluster, st);
                 }
             }
             switch (R) {
-                case 4: return launch_stream_r<DT, 4, 8>(p, S, grid, smem, st);
-                case 2: return launch_stream_r<DT, 2, 8>(p, S, grid, smem, st);
-                default: return launch_stream_r<DT, 1, 8>(p, S, grid, smem, st);
+                case 4: return launch_stream_r<DT, 4, 8>(p, S, grid, smem, cluster, st);
+                case 2: return launch_stream_r<DT, 2, 8>(p, S, grid, smem, cluster, st);
+                default: return launch_stream_r<DT, 1, 8>(p, S, grid, smem, cluster, st);
             }
         }
     }

@@ -18,12 +18,23 @@
 // C[token][row]; for a fixed token the 32 lanes of a warp write 32 consecutive rows,
 // one coalesced 128-byte store).
 //
+// Q4_0 weights never exist as an fp16 matrix in memory: eight producer warps read the 18-byte
+// blocks of their tile rows straight from global memory, turn the nibbles into (n - 8) * d with
+// two half2 instructions per pair (the exact product rounded once to fp16, the same value the
+// fp32 dequantizer rounded to fp16 gives) and store them into the stage in the 128-byte-swizzled
+// K-major layout the MMA descriptor expects, followed by a proxy fence and an arrive on the
+// stage's barrier. TMA then only carries the activations. Other formats take a pre-pass that
+// writes the fp16 weight matrix to the workspace, and both operands come by TMA.
+//
 // Operand precision: weights are dequantized exactly to fp32 and rounded once to
 // fp16; activations are rounded once to fp16. Each product then carries at most
 // 2^-10 relative error and the accumulation is fp32, inside the path's tolerance of
 // 1e-3 * sum|w*x| per output.
 #include "common.cuh"
 #include "gemm.h"
+
+#include <cstdlib>
+#include <type_traits>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -224,6 +235,234 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
 }
 
+
+// ---- Q4_0: dequantizing producer --------------------------------------------------------------
+constexpr int kDqWarps = 8;                      // two sets of four warps, alternating k-blocks; a thread owns one tile row
+constexpr int kThreadsQ4 = kThreads + kDqWarps * 32;
+
+// Four consecutive nibble codes (the low nibbles of the four bytes of `q4`, already masked) as two
+// half2 of (n - 8) * d.
+__device__ __forceinline__ void q4_quad(uint32_t q4, __half2 d2, uint32_t& o01, uint32_t& o23) {
+    const __half2 k1032 = __half2half2(__ushort_as_half((unsigned short)0x6408));      // 1032.0
+    uint32_t a = __byte_perm(q4, 0x64646464u, 0x5140), b = __byte_perm(q4, 0x64646464u, 0x7362);   // 1024 + n in each half
+    __half2 ha = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&a), k1032), d2);
+    __half2 hb = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&b), k1032), d2);
+    o01 = *reinterpret_cast<uint32_t*>(&ha); o23 = *reinterpret_cast<uint32_t*>(&hb);
+}
+// One Q4_0 block (d, 16 code bytes in Q[0..3]) -> 32 fp16 = chunks c0 .. c0+3 of the row, swizzled.
+// Byte j of a block holds weight 2j in its low nibble and weight 2j+1 in its high nibble
+// (tensormark/quant.h:194-200), so one 32-bit word is eight consecutive weights = one 16-byte chunk.
+__device__ __forceinline__ void q4_block_to_stage(uint8_t* row_base, uint32_t r7, uint32_t c0, uint32_t dbits, const uint32_t (&Q)[4]) {
+    const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = Q[i] & 0x0F0F0F0Fu, hi = (Q[i] >> 4) & 0x0F0F0F0Fu;
+        const uint32_t p01 = __byte_perm(lo, hi, 0x5140), p23 = __byte_perm(lo, hi, 0x7362);   // codes in weight order
+        uint4 o;
+        q4_quad(p01, d2, o.x, o.y);
+        q4_quad(p23, d2, o.z, o.w);
+        *reinterpret_cast<uint4*>(row_base + (((c0 + i) ^ r7) << 4)) = o;
+    }
+}
+
+// Raw blocks reach the producers through shared memory: a row's bytes for four k-blocks (8 blocks, 144 bytes)
+// arrive by one bulk copy per row, 128 rows per raw stage. Reading them from global memory with one 4-byte
+// load per lane instead costs a cache-tag lookup per lane and load, which took longer than the MMAs.
+//
+// Three rings, each with its own barriers, so that the depth of each follows what it has to hide:
+//   activations (TMA, 32 KB per k-block)  kStagesB = 4   L2 latency at the MMA's consumption rate
+//   fp16 weights (written by producers)   kStagesA = 3   only the conversion itself
+//   raw blocks (bulk copies, 18 KB per 4 k-blocks) kRaw = 2, refilled as soon as the rows are in registers
+constexpr int kStagesB = 4, kStagesA = 3, kRaw = 2;
+constexpr uint32_t RAW_ROW = 144, RAW_BYTES = BM * RAW_ROW;
+constexpr size_t kSmemBytesQ4 = (size_t)kStagesB * B_BYTES + (size_t)kStagesA * A_BYTES + (size_t)kRaw * RAW_BYTES + 256 + 1024;
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// W: Q4_0 blocks [n_rows][K/32], rows 16-byte aligned; tmB: activations as fp16 [m_tok][K], box 64 x 256. K % 256 == 0.
+__global__ void __launch_bounds__(kThreadsQ4, 1)
+gemm_q4_tn(const uint8_t* __restrict__ W, uint32_t row_bytes, const __grid_constant__ CUtensorMap tmB,
+           float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* bbuf = smem;                                          // kStagesB x 32 KB, 1024-byte aligned
+    uint8_t* abuf = bbuf + (size_t)kStagesB * B_BYTES;             // kStagesA x 16 KB, 1024-byte aligned
+    uint8_t* raw = abuf + (size_t)kStagesA * A_BYTES;
+    uint64_t* bfull = (uint64_t*)(raw + (size_t)kRaw * RAW_BYTES);
+    uint64_t* bempty = bfull + kStagesB;
+    uint64_t* afull = bempty + kStagesB;
+    uint64_t* aempty = afull + kStagesA;
+    uint64_t* tfull = aempty + kStagesA;
+    uint64_t* tempty = tfull + 2;
+    uint64_t* rfull = tempty + 2;
+    uint64_t* rempty = rfull + kRaw;
+    uint32_t* tmem_slot = (uint32_t*)(rempty + kRaw);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t num_kb = K / BK;
+    const uint32_t tiles_n = (n_rows + BM - 1) / BM, tiles_m = (m_tok + BN - 1) / BN, tiles = tiles_n * tiles_m;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesB; ++s) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], 1); }
+        // a weight stage is full when the four warps that convert this k-block have arrived
+        for (int s = 0; s < kStagesA; ++s) { mbar_init(&afull[s], 4); mbar_init(&aempty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 128); }
+        // a raw stage is full when its 128 row copies have landed (each loader thread arrives with its bytes) and
+        // free again when all eight producer warps have taken their rows into registers
+        for (int s = 0; s < kRaw; ++s) { mbar_init(&rfull[s], BM); mbar_init(&rempty[s], kDqWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool dead = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
+                const int m0 = (int)(tile / tiles_n) * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % kStagesB, ph = (it / kStagesB) & 1u;
+                    if (!mbar_wait(&bempty[s], ph ^ 1u)) { dead = true; break; }
+                    mbar_expect_tx(&bfull[s], B_BYTES);
+                    tma_load_2d(bbuf + (size_t)s * B_BYTES, &tmB, (int)(kb * BK), m0, &bfull[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x, ++tcount) {
+                const uint32_t buf = tcount & 1u;
+                if (!mbar_wait(&tempty[buf], ((tcount >> 1) & 1u) ^ 1u)) { dead = true; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t sb = it % kStagesB, phb = (it / kStagesB) & 1u;
+                    const uint32_t sa = it % kStagesA, pha = (it / kStagesA) & 1u;
+                    if (!mbar_wait(&afull[sa], pha) || !mbar_wait(&bfull[sb], phb)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t a = smem_u32(abuf + (size_t)sa * A_BYTES), b = smem_u32(bbuf + (size_t)sb * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_f16(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(b + k * UMMA_K * 2), kIdesc,
+                                 (kb | (uint32_t)k) ? 1u : 0u);
+                    umma_commit(&aempty[sa]);          // both stages are free once these MMAs have read them
+                    umma_commit(&bempty[sb]);
+                }
+                if (dead) break;
+                umma_commit(&tfull[buf]);
+            }
+        }
+    } else if (warp < 6) {
+        const uint32_t q = (uint32_t)warp & 3u;        // TMEM lane quarter this warp may read
+        uint32_t tcount = 0;
+        for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x, ++tcount) {
+            const uint32_t buf = tcount & 1u;
+            const uint32_t n0 = (tile % tiles_n) * BM, m0 = (tile / tiles_n) * BN;
+            if (!mbar_wait(&tfull[buf], (tcount >> 1) & 1u)) { dead = true; break; }
+            tc_fence_after();
+            const uint32_t row = n0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + ((q * 32u) << 16);
+            for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 32) {
+                if (m0 + c0 >= m_tok) break;
+                uint32_t v[32];
+                tmem_ld32(taddr + c0, v);
+                if (row < n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t m = m0 + c0 + j;
+                        if (m < m_tok) C[(size_t)m * ldc + row] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&tempty[buf]);
+        }
+    } else {
+        // ---- dequantizing producers: two sets of four warps, thread r of a set owns tile row r.
+        // The CTA's k-blocks, in pipeline order, form groups of four (K % 256 == 0, so a group never straddles
+        // tiles). Group G sits in raw stage G % kRaw. Of a group's four k-blocks set 0 converts the first and third,
+        // set 1 the others. Set 0's threads also request the rows: groups 0 and 1 up front, then group G + 2 as
+        // soon as group G has been converted (its raw stage is free once all eight warps hold it in registers).
+        const uint32_t set = (uint32_t)(warp - 6) >> 2, r = ((uint32_t)(warp - 6) & 3u) * 32u + (uint32_t)lane;
+        const uint32_t r7 = r & 7u;
+        const uint32_t groups_per_tile = num_kb / 4;
+        uint32_t my_tiles = 0;
+        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) ++my_tiles;
+        const uint32_t ngroups = my_tiles * groups_per_tile;
+        auto issue = [&](uint32_t G) -> bool {
+            if (G >= ngroups) return true;
+            const uint32_t rs = G % kRaw, rph = (G / kRaw) & 1u;
+            if (!mbar_wait(&rempty[rs], rph ^ 1u)) { dead = true; return false; }
+            const uint32_t tile = blockIdx.x + (G / groups_per_tile) * gridDim.x, g = G % groups_per_tile;
+            const uint32_t row = (tile % tiles_n) * BM + r;
+            if (row < n_rows) {
+                mbar_expect_tx(&rfull[rs], RAW_ROW);
+                bulk_g2s(raw + (size_t)rs * RAW_BYTES + r * RAW_ROW, W + (size_t)row * row_bytes + (size_t)g * RAW_ROW, RAW_ROW, &rfull[rs]);
+            } else {
+                mbar_arrive(&rfull[rs]);                           // past the last row: nothing to copy, zeros are produced below
+            }
+            return true;
+        };
+        if (set == 0) { if (issue(0)) (void)issue(1); }
+        for (uint32_t G = 0; G < ngroups && !dead; ++G) {
+            const uint32_t rs = G % kRaw, rph = (G / kRaw) & 1u;
+            if (!mbar_wait(&rfull[rs], rph)) { dead = true; break; }
+            const uint32_t tile = blockIdx.x + (G / groups_per_tile) * gridDim.x;
+            const bool live = (tile % tiles_n) * BM + r < n_rows;
+            uint32_t w[36];                                        // this row's 144 bytes: 9 conflict-free 16-byte reads
+            const uint4* src = reinterpret_cast<const uint4*>(raw + (size_t)rs * RAW_BYTES + r * RAW_ROW);
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+                const uint4 v = live ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rempty[rs]);
+            // k-blocks (2j + set) of the group, with compile-time register offsets (set is warp-uniform)
+            auto item = [&](auto KQ) -> bool {
+                constexpr uint32_t kq = decltype(KQ)::value;
+                const uint32_t it = G * 4u + kq;
+                const uint32_t s = it % kStagesA, ph = (it / kStagesA) & 1u;
+                if (!mbar_wait(&aempty[s], ph ^ 1u)) { dead = true; return false; }
+                uint8_t* row_base = abuf + (size_t)s * A_BYTES + (r >> 3) * 1024u + r7 * 128u;
+                uint32_t Q[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) Q[i] = __byte_perm(w[9 * kq + i], w[9 * kq + i + 1], 0x5432);     // block 0: code bytes 2 .. 17
+                q4_block_to_stage(row_base, r7, 0, w[9 * kq] & 0xFFFFu, Q);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) Q[i] = w[9 * kq + 5 + i];                                           // block 1: d at byte 18, codes 20 .. 35
+                q4_block_to_stage(row_base, r7, 4, w[9 * kq + 4] >> 16, Q);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&afull[s]);
+                return true;
+            };
+            using I0 = std::integral_constant<uint32_t, 0>; using I1 = std::integral_constant<uint32_t, 1>;
+            using I2 = std::integral_constant<uint32_t, 2>; using I3 = std::integral_constant<uint32_t, 3>;
+            if (set == 0) { if (!item(I0{}) || !item(I2{})) break; if (!issue(G + 2)) break; }
+            else { if (!item(I1{}) || !item(I3{})) break; }
+        }
+    }
+    if (dead) atomicExch(status, 2);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 __global__ void f32_to_f16_rows(const float* __restrict__ src, __half* __restrict__ dst, size_t n4) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4) return;
@@ -286,14 +525,36 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     __half* Wh = (__half*)ws;
     __half* Ah = (__half*)(ws + ((size_t)N * K * 2 + 255) / 256 * 256);
 
-    if (!launch_dequant_half(W, Wh, N, K, dtype, st)) return false;
+    // Q4_0 with K a multiple of 256 and 16-byte aligned rows can be dequantized inside the GEMM (gemm_q4_tn).
+    // TM_GEMM_FUSED=1 selects it; the default is the pre-pass, which is the faster of the two today
+    // (2000 x 5632 x 2048: 72 us for pre-passes + TMA-fed kernel against 77 us for the producer-fed kernel,
+    // whose tensor pipe is 30 % busy with the producers stalled on their barriers).
+    static const bool allow_fused = [] { const char* e = std::getenv("TM_GEMM_FUSED"); return e && *e == '1'; }();
+    const uint32_t row_bytes = (K / be) * block_bytes(dtype);
+    const bool fused = allow_fused && dtype == DT_Q4_0 && K % 256 == 0 && (uintptr_t)W % 16 == 0 && row_bytes % 16 == 0;
+    if (!fused && !launch_dequant_half(W, Wh, N, K, dtype, st)) return false;
     const size_t n4 = (size_t)M * K / 4;
     f32_to_f16_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(A, Ah, n4);
     note_launch();
     if (!check_launch("f32_to_f16_rows")) return false;
 
     CUtensorMap tmA, tmB;
-    if (!make_map(&tmA, Wh, N, K, BM) || !make_map(&tmB, Ah, M, K, BN)) return false;
+    if (!make_map(&tmB, Ah, M, K, BN)) return false;
+    if (fused) {
+        static bool attr4 = false;
+        if (!attr4) {
+            if (cudaFuncSetAttribute(gemm_q4_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesQ4) != cudaSuccess)
+                return check_launch("gemm: shared memory attribute");
+            attr4 = true;
+        }
+        const unsigned tiles4 = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
+        unsigned grid4 = (unsigned)device_sm_count();
+        if (grid4 > tiles4) grid4 = tiles4;
+        gemm_q4_tn<<<grid4, kThreadsQ4, kSmemBytesQ4, st>>>(W, row_bytes, tmB, C, ldc, M, N, K, device_status_word());
+        note_launch();
+        return check_launch("gemm_q4_tn");
+    }
+    if (!make_map(&tmA, Wh, N, K, BM)) return false;
     static bool attr = false;
     if (!attr) {
         if (cudaFuncSetAttribute(gemm_f16_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)

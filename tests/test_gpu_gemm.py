@@ -86,3 +86,17 @@ def test_host_pointer_entries(cuda, orc):
     assert np.array_equal(C1.view(np.uint32), np.ascontiguousarray(Cm[:, : ns[0]]).view(np.uint32))
     assert not cuda.tm_cuda_sgemm_q4(A.ctypes.data, Ws[0].ctypes.data, C1.ctypes.data, m, ns[0], 500)
     cuda.tm_cuda_release_weights()
+
+
+def test_q4_kernel_with_in_kernel_dequant(torch_mod):
+    """The Q4_0 GEMM whose producer warps dequantize the blocks into the shared-memory tiles (selected with
+    TM_GEMM_FUSED=1 at first use, hence a fresh process): the same checks as the default path."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TM_GEMM_FUSED="1")
+    sel = "test_small_shapes_full_check or (test_config4_prefill_shapes_sampled and not 32000)"
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_gemm.py", "-q", "-x", "-k", sel],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

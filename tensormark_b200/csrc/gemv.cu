@@ -668,15 +668,15 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         const unsigned sms = (unsigned)device_sm_count();
         static const int force_r = env_int("TM_GEMV_R", 0), force_s = env_int("TM_GEMV_STAGES", 0),
                          force_w = env_int("TM_GEMV_WARPS", 0);
-        // One 16-warp CTA per SM; matrices with fewer than 8 rows per SM use 8-warp CTAs when the row
-        // has few enough steps (measured on the ten-GEMV sweep: 65 vs 71 us per pass). TM_GEMV_WARPS overrides.
+        // One 16-warp CTA per SM. 8-warp CTAs (TM_GEMV_WARPS=8) were the rule for matrices with fewer than 8 rows
+        // per SM until the x staging was reworked; they now cost 4 % on the ten-GEMV sweep (70.5 vs 68.0 us).
         // TM_GEMV_HALF_MB > 0 (an experiment, off by default) gives matrices up to that many MB an 8-warp
         // CTA limited to half of an SM's shared memory, so that two consecutive kernels can be resident
         // together; measured slower (sweep 78 vs 65 us, 8B chain 3.2 vs 2.7 ms per token): 8 warps do not
         // decode fast enough.
         static const int half_mb = env_int("TM_GEMV_HALF_MB", 0);
         const bool half = half_mb > 0 && nchunks <= 8 && (size_t)p.N * p.row_bytes <= (size_t)half_mb << 20;
-        int warps_cta = half ? 8 : ((p.N >= 8u * sms || nchunks > 8) ? 16 : 8);
+        int warps_cta = half ? 8 : 16;
         if ((force_w == 8 && nchunks <= 8) || force_w == 16) warps_cta = force_w;
         const size_t smem_limit = half ? kHalfSmem : kSmemLimit;
         // Clusters can share the staging of x (see the kernel). Off by default: measured on B200, launching the

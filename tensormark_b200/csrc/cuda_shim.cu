@@ -75,8 +75,13 @@ bool ensure_init(int device) {
     s.device = device;
     s.sm_count = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return check_launch("cudaStreamCreate");
-    if (cudaMalloc(&s.status_dev, 64) != cudaSuccess) return check_launch("cudaMalloc(status)");
-    cudaMemset(s.status_dev, 0, 64);
+    // The status word lives in pinned host memory that the device sees: reading it after a synchronisation costs
+    // nothing, where a 4-byte copy back cost about 10 us on every blocking call.
+    void* hp = nullptr;
+    if (cudaHostAlloc(&hp, 64, cudaHostAllocMapped) != cudaSuccess) return check_launch("cudaHostAlloc(status)");
+    std::memset(hp, 0, 64);
+    s.status_host = (volatile int*)hp;
+    if (cudaHostGetDevicePointer((void**)&s.status_dev, hp, 0) != cudaSuccess) return check_launch("cudaHostGetDevicePointer(status)");
     const char* tr = std::getenv("TM_CUDA_TRACE");
     if (tr && *tr == '1') {
         const size_t words = 1 + (size_t)kTraceWords * kTraceLaunches;
@@ -94,10 +99,9 @@ bool ensure_init(int device) {
 // Reads and clears the device status word the kernels set when a bounded wait ran out.
 bool harvest_status(const char* where) {
     State& s = state();
-    int h = 0;
-    if (cudaMemcpy(&h, s.status_dev, sizeof h, cudaMemcpyDeviceToHost) != cudaSuccess) return check_launch(where);
+    const int h = *s.status_host;                        // the caller has just synchronised with the kernels
     if (h != 0) {
-        cudaMemset(s.status_dev, 0, sizeof h);
+        *s.status_host = 0;
         return fail("%s: a kernel gave up on a bounded wait (status %d)", where, h);
     }
     return true;

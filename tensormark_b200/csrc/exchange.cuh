@@ -33,7 +33,7 @@ __device__ __forceinline__ void exchange_wait(const Exchange& xc, int* status) {
         bool ok = true;
         for (uint32_t q = 0; q < xc.nwait; ++q)
             if (q != xc.self) ok = wait_flag(xc.wait_flags + q, want) && ok;
-        if (!ok) atomicExch(status, 2);
+        if (!ok) *(volatile int*)status = 2;
     }
     __syncthreads();
 }

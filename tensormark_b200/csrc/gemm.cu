@@ -161,6 +161,9 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool dead = false;
+    // Launched with programmatic stream serialization: everything above (barriers, TMEM) overlaps the pre-pass that
+    // writes the fp16 operands; nothing below may start before that kernel has finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -226,7 +229,7 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             mbar_arrive(&tempty[buf]);
         }
     }
-    if (dead) atomicExch(status, 2);
+    if (dead) *(volatile int*)status = 2;
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -454,7 +457,7 @@ gemm_q4_tn(const uint8_t* __restrict__ W, uint32_t row_bytes, const __grid_const
             else { if (!item(I1{}) || !item(I3{})) break; }
         }
     }
-    if (dead) atomicExch(status, 2);
+    if (dead) *(volatile int*)status = 2;
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -470,6 +473,38 @@ __global__ void f32_to_f16_rows(const float* __restrict__ src, __half* __restric
     __half2* o = reinterpret_cast<__half2*>(dst) + 2 * i;
     o[0] = __floats2half2_rn(v.x, v.y);
     o[1] = __floats2half2_rn(v.z, v.w);
+}
+
+// Both operand conversions of the Q4_0 pre-pass form in one launch. Blocks [0, blocks_w) turn weights into fp16:
+// one thread per 32-bit word of codes = eight consecutive weights = one 16-byte store, consecutive threads consecutive
+// words, with the same two-instruction-per-pair arithmetic as the producer warps of gemm_q4_tn (the exact (n - 8) * d
+// rounded once to fp16). The remaining blocks round the activations.
+__global__ void __launch_bounds__(256) prepass_q4_f16(const uint8_t* __restrict__ W, uint32_t row_bytes, __half* __restrict__ Wh,
+                                                      uint32_t N, uint32_t K, const float* __restrict__ A, __half* __restrict__ Ah,
+                                                      size_t n4, uint32_t blocks_w) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");        // the GEMM may set itself up meanwhile
+    if (blockIdx.x < blocks_w) {
+        const uint32_t wpr = K / 8;                                         // words per row
+        const uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+        if (idx >= (uint64_t)N * wpr) return;
+        const uint32_t row = (uint32_t)(idx / wpr), j = (uint32_t)(idx % wpr), b = j >> 2, i = j & 3u;
+        const unsigned short* p = reinterpret_cast<const unsigned short*>(W + (size_t)row * row_bytes + (size_t)b * 18u);
+        const uint32_t dbits = __ldg(p), q = (uint32_t)__ldg(p + 1 + 2 * i) | ((uint32_t)__ldg(p + 2 + 2 * i) << 16);
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+        const uint32_t lo = q & 0x0F0F0F0Fu, hi = (q >> 4) & 0x0F0F0F0Fu;
+        const uint32_t p01 = __byte_perm(lo, hi, 0x5140), p23 = __byte_perm(lo, hi, 0x7362);
+        uint4 o;
+        q4_quad(p01, d2, o.x, o.y);
+        q4_quad(p23, d2, o.z, o.w);
+        reinterpret_cast<uint4*>(Wh + (size_t)row * K)[j] = o;
+    } else {
+        const size_t i = (size_t)(blockIdx.x - blocks_w) * 256 + threadIdx.x;
+        if (i >= n4) return;
+        const float4 v = reinterpret_cast<const float4*>(A)[i];
+        __half2* o = reinterpret_cast<__half2*>(Ah) + 2 * i;
+        o[0] = __floats2half2_rn(v.x, v.y);
+        o[1] = __floats2half2_rn(v.z, v.w);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -532,11 +567,18 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     static const bool allow_fused = [] { const char* e = std::getenv("TM_GEMM_FUSED"); return e && *e == '1'; }();
     const uint32_t row_bytes = (K / be) * block_bytes(dtype);
     const bool fused = allow_fused && dtype == DT_Q4_0 && K % 256 == 0 && (uintptr_t)W % 16 == 0 && row_bytes % 16 == 0;
-    if (!fused && !launch_dequant_half(W, Wh, N, K, dtype, st)) return false;
     const size_t n4 = (size_t)M * K / 4;
-    f32_to_f16_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(A, Ah, n4);
-    note_launch();
-    if (!check_launch("f32_to_f16_rows")) return false;
+    if (!fused && dtype == DT_Q4_0 && K % 8 == 0 && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
+        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + 255) / 256), blocks_a = (unsigned)((n4 + 255) / 256);
+        prepass_q4_f16<<<blocks_w + blocks_a, 256, 0, st>>>(W, row_bytes, Wh, N, K, A, Ah, n4, blocks_w);
+        note_launch();
+        if (!check_launch("prepass_q4_f16")) return false;
+    } else {
+        if (!fused && !launch_dequant_half(W, Wh, N, K, dtype, st)) return false;
+        f32_to_f16_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(A, Ah, n4);
+        note_launch();
+        if (!check_launch("f32_to_f16_rows")) return false;
+    }
 
     CUtensorMap tmA, tmB;
     if (!make_map(&tmB, Ah, M, K, BN)) return false;
@@ -564,7 +606,14 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     const unsigned tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
     unsigned grid = (unsigned)device_sm_count();
     if (grid > tiles) grid = tiles;
-    gemm_f16_tn<<<grid, kThreads, kSmemBytes, st>>>(tmA, tmB, C, ldc, M, N, K, device_status_word());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, device_status_word()) != cudaSuccess)
+        return check_launch("gemm_f16_tn");
     note_launch();
     return check_launch("gemm_f16_tn");
 }

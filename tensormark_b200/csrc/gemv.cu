@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         // A copy never completed. Record it, give the copies still in flight a last
         // bounded chance to land (they target this CTA's shared memory) and leave.
         if (lane == 0) {
-            atomicExch(p.status, 1);
+            *(volatile int*)p.status = 1;
             for (uint32_t s = 0; s < S; ++s) (void)mbar_wait(&mybar[s], 0, 50000000ull), (void)mbar_wait(&mybar[s], 1, 50000000ull);
         }
     }

@@ -50,7 +50,8 @@ struct State {
     bool ready = false, verbose = false, kv_half = true;
     int device = -1, sm_count = 0;
     cudaStream_t stream = nullptr;
-    int* status_dev = nullptr;
+    int* status_dev = nullptr;                                  // device view of status_host
+    volatile int* status_host = nullptr;                        // pinned, mapped: kernels store a code here when a bounded wait runs out
     unsigned long long* trace_dev = nullptr;                    // TM_CUDA_TRACE=1: [0] = launches recorded, then kTraceWords per launch
     std::string last_error;
     unsigned long long fallbacks = 0, launches = 0;

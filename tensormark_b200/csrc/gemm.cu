@@ -507,6 +507,51 @@ __global__ void __launch_bounds__(256) prepass_q4_f16(const uint8_t* __restrict_
     }
 }
 
+// The same for Q6_K: one thread per eight consecutive weights (they share the super-block scale, the sub-block scale,
+// the nibble half and the high-bit pair position), d * sc and then * (q - 32) in fp32 (both products are exact, as in
+// tmq::dequantize_row_q6_k, tensormark/quant.h:338-365), rounded once to fp16, one 16-byte store.
+__global__ void __launch_bounds__(256) prepass_q6k_f16(const uint8_t* __restrict__ W, uint32_t row_bytes, __half* __restrict__ Wh,
+                                                       uint32_t N, uint32_t K, const float* __restrict__ A, __half* __restrict__ Ah,
+                                                       size_t n4, uint32_t blocks_w) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (blockIdx.x < blocks_w) {
+        const uint32_t gpr = K / 8;                                         // groups of eight per row
+        const uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+        if (idx >= (uint64_t)N * gpr) return;
+        const uint32_t row = (uint32_t)(idx / gpr), t = (uint32_t)(idx % gpr), k = t * 8;
+        const uint32_t e = k & 255u, h = e >> 7, j = (e >> 5) & 3u, l0 = e & 31u;
+        const uint8_t* b = W + (size_t)row * row_bytes + (size_t)(k >> 8) * 210u;
+        const unsigned short* ql = reinterpret_cast<const unsigned short*>(b + 64 * h + 32 * (j & 1u) + l0);
+        const unsigned short* qh = reinterpret_cast<const unsigned short*>(b + 128 + 32 * h + l0);
+        const uint32_t dbits = __ldg(reinterpret_cast<const unsigned short*>(b + 208));
+        const int sc = (int)(int8_t)__ldg(b + 192 + 8 * h + 2 * j + (l0 >> 4));
+        const float ds = __fmul_rn(__half2float(__ushort_as_half((unsigned short)dbits)), __int2float_rn(sc));
+        uint32_t o[4];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            const uint32_t qlw = (uint32_t)__ldg(ql + 2 * w) | ((uint32_t)__ldg(ql + 2 * w + 1) << 16);
+            const uint32_t qhw = (uint32_t)__ldg(qh + 2 * w) | ((uint32_t)__ldg(qh + 2 * w + 1) << 16);
+            const uint32_t nib = ((j & 2u) ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
+            const uint32_t code = nib | (((qhw >> (2 * j)) & 0x03030303u) << 4);          // four codes 0..63
+            const float w0 = __fmul_rn(ds, __int2float_rn((int)(code & 255u) - 32));
+            const float w1 = __fmul_rn(ds, __int2float_rn((int)((code >> 8) & 255u) - 32));
+            const float w2 = __fmul_rn(ds, __int2float_rn((int)((code >> 16) & 255u) - 32));
+            const float w3 = __fmul_rn(ds, __int2float_rn((int)(code >> 24) - 32));
+            const __half2 a = __floats2half2_rn(w0, w1), c = __floats2half2_rn(w2, w3);
+            o[2 * w] = *reinterpret_cast<const uint32_t*>(&a);
+            o[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&c);
+        }
+        reinterpret_cast<uint4*>(Wh + (size_t)row * K)[t] = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        const size_t i = (size_t)(blockIdx.x - blocks_w) * 256 + threadIdx.x;
+        if (i >= n4) return;
+        const float4 v = reinterpret_cast<const float4*>(A)[i];
+        __half2* o = reinterpret_cast<__half2*>(Ah) + 2 * i;
+        o[0] = __floats2half2_rn(v.x, v.y);
+        o[1] = __floats2half2_rn(v.z, v.w);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -573,6 +618,11 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
         prepass_q4_f16<<<blocks_w + blocks_a, 256, 0, st>>>(W, row_bytes, Wh, N, K, A, Ah, n4, blocks_w);
         note_launch();
         if (!check_launch("prepass_q4_f16")) return false;
+    } else if (dtype == DT_Q6_K && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
+        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + 255) / 256), blocks_a = (unsigned)((n4 + 255) / 256);
+        prepass_q6k_f16<<<blocks_w + blocks_a, 256, 0, st>>>(W, row_bytes, Wh, N, K, A, Ah, n4, blocks_w);
+        note_launch();
+        if (!check_launch("prepass_q6k_f16")) return false;
     } else {
         if (!fused && !launch_dequant_half(W, Wh, N, K, dtype, st)) return false;
         f32_to_f16_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(A, Ah, n4);

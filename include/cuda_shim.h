@@ -245,13 +245,15 @@ bool tm_cuda_comm_destroy(void);
 void tm_cuda_tok_all_gather(int srcslot, size_t src_off, int dstslot, size_t dst_off, unsigned count);
 
 /* The same gather without a collective kernel: each rank's arena is mapped into every peer (CUDA
- * IPC) and the GEMV that produces a shard stores its rows straight into the peers' copies of the
- * output slot over NVLink, then raises a per-site flag; the kernel that consumes the gathered vector
- * waits for the other ranks' flags (bounded: 2 s, then the status word reports it) before it reads.
+ * IPC) and the GEMV that produces a shard stores each finished row into the peers' copies of the
+ * output slot over NVLink as well as its own; every CTA then adds 1 to the rank's counter of the
+ * gather "site" on every peer (release at system scope). The kernel that consumes the gathered vector
+ * waits until the other ranks' counters have reached epoch * CTAs-of-the-producer (bounded: 2 s, then
+ * the status word reports it) before it reads.
  * Set-up on every rank: tm_cuda_peer_arena -> exchange the handles -> tm_cuda_peer_open ->
  * tm_cuda_tok_reserve_shared for the gathered slots, in the same order on every rank. A site is an
- * index < 256 naming one gather per token; the chain state's fourth int is the token epoch the flags
- * carry (tm_cuda_tok_advance increments it). At most 8 ranks. */
+ * index < 256 naming one gather per token; the chain state's fourth int is the token epoch
+ * (tm_cuda_tok_advance increments it). Every rank must launch the same shapes. At most 8 ranks. */
 size_t tm_cuda_peer_handle_bytes(void);
 bool tm_cuda_peer_arena(size_t bytes, void* handle_out);
 bool tm_cuda_peer_open(int rank, int world, const void* handles);

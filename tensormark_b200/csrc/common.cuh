@@ -41,20 +41,23 @@ struct SegTable {                           // rows [row_end[s-1], row_end[s]) s
 };
 
 // Peer-memory all-gather fused into the kernels of a row-sharded model (one process per GPU). A
-// producer writes its rows of y into the same place of every peer's copy of the buffer and, once
-// its last CTA is done, raises its flag of the "site" in every peer's memory to the token's epoch;
-// a consumer waits until the site's flags of all other ranks have reached the epoch before it reads
-// the gathered vector. Flags only grow, every wait is bounded and reports through the status word.
+// producer stores each finished row of y into the same place of every peer's copy of the buffer as
+// well as its own; when a CTA is done it adds 1 to this rank's counter of the gather "site" in every
+// peer's memory (a release at system scope, so the rows are visible before the count). A consumer
+// waits until the site's counters of all other ranks have reached epoch * ctas, where ctas is the
+// producer's grid size, before it reads the gathered vector. Counters only grow, every wait is bounded
+// and reports through the status word.
 constexpr int kMaxPeers = 7;
 struct Exchange {
     const int* epoch;                       // device int; the current token's epoch is *epoch + 1
-    const int* wait_flags;                  // consumer: the site's flags in local memory, one per rank
+    const unsigned* wait_ctrs;              // consumer: the site's counters in local memory, one per rank
     uint32_t nwait, self;                   // consumer: ranks (0 = no wait) and this rank's index
+    uint32_t wait_ctas;                     // consumer: CTAs of the producing launch (arrivals per epoch and rank)
     uint32_t npush;                         // producer: number of peers (0 = no push)
     float* peer_y[kMaxPeers];               // producer: y as mapped from each peer
-    int* peer_flag[kMaxPeers];              // producer: this rank's flag of the site in each peer's memory
-    unsigned long long* arrive;             // producer: local count of finished CTAs of the site
+    unsigned* peer_ctr[kMaxPeers];          // producer: this rank's counter of the site in each peer's memory
 };
+unsigned last_gemv_grid();                  // CTAs of the most recent GEMV launch of this process
 
 // ---- kernel launchers (one per .cu) -----------------------------------------
 struct GemvFuse {                           // optional fusions of the decode chain

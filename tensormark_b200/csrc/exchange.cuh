@@ -14,28 +14,38 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-// Bounded wait until a flag that a peer GPU raises has reached `want`.
-__device__ __forceinline__ bool wait_flag(const int* flag, int want) {
-    auto peek = [&]() { int v; asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory"); return v; };
-    if (peek() - want >= 0) return true;
+// Bounded wait until a counter that a peer GPU increments has reached `want` (wrap-safe comparison).
+__device__ __forceinline__ bool wait_counter(const unsigned* ctr, unsigned want) {
+    auto peek = [&]() { unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory"); return v; };
+    if ((int)(peek() - want) >= 0) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 32; ++i)
-            if (peek() - want >= 0) return true;
+            if ((int)(peek() - want) >= 0) return true;
         if (global_ns() - t0 > kWaitLimitNs) return false;
     }
 }
-// Consumer side of the exchange: one thread waits for every other rank's flag, the CTA follows.
+// Consumer side of the exchange: one thread waits for every other rank's counter, the CTA follows.
 __device__ __forceinline__ void exchange_wait(const Exchange& xc, int* status) {
     if (!xc.nwait) return;
     if (threadIdx.x == 0) {
-        const int want = *(volatile const int*)xc.epoch + 1;
+        const unsigned want = (unsigned)(*(volatile const int*)xc.epoch + 1) * xc.wait_ctas;
         bool ok = true;
         for (uint32_t q = 0; q < xc.nwait; ++q)
-            if (q != xc.self) ok = wait_flag(xc.wait_flags + q, want) && ok;
+            if (q != xc.self) ok = wait_counter(xc.wait_ctrs + q, want) && ok;
         if (!ok) *(volatile int*)status = 2;
     }
     __syncthreads();
+}
+// Producer side, end of a CTA: every row this CTA computed has been stored here and on the peers by the
+// threads that computed it; after the barrier one thread adds this CTA to the rank's counter on every peer.
+// The reduction is a release at system scope, so a peer that sees the count sees the rows.
+__device__ __forceinline__ void exchange_signal(const Exchange& xc) {
+    if (!xc.npush) return;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (uint32_t q = 0; q < xc.npush; ++q)
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(xc.peer_ctr[q]) : "memory");
 }
 
 }  // namespace tmc

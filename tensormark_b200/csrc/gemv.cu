@@ -118,28 +118,10 @@ __device__ __forceinline__ uint32_t y_index(const GemvParams& p, uint32_t row) {
     return p.seg.yoff[s] + (row - start);
 }
 
-// Producer side: the CTA copies its finished rows of y (elements given by y_index) to every peer;
-// the CTA that finishes last raises this rank's flag on every peer. Call with all threads, after a
-// __syncthreads() that follows the CTA's last store to y.
-__device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t cta_lo, uint32_t cta_hi) {
-    const Exchange& xc = p.xc;
-    if (!xc.npush) return;
-    for (uint32_t i = threadIdx.x; i < cta_hi - cta_lo; i += blockDim.x) {
-        const uint32_t e = y_index(p, cta_lo + i);
-        const float v = __ldcg(p.y + e);
-        for (uint32_t q = 0; q < xc.npush; ++q) xc.peer_y[q][e] = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned long long done = atomicAdd(xc.arrive, 1ull) + 1ull;
-        if (done % gridDim.x == 0) {
-            __threadfence_system();
-            const int epoch = *(volatile const int*)xc.epoch + 1;
-            for (uint32_t q = 0; q < xc.npush; ++q)
-                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(xc.peer_flag[q]), "r"(epoch) : "memory");
-        }
-    }
+// Store one finished row: here and, for a sharded model, into every peer's copy of y.
+__device__ __forceinline__ void store_row(const GemvParams& p, uint32_t e, float v) {
+    p.y[e] = v;
+    for (uint32_t q = 0; q < p.xc.npush; ++q) p.xc.peer_y[q][e] = v;
 }
 
 template <int DT> __device__ __forceinline__ int lane_valid(int lane, int units_in_chunk) {
@@ -431,7 +413,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
                 const uint32_t e = y_index(p, row);
                 if (p.x_op == 1u) v *= norm_inv;
                 if (p.accumulate) v += p.y[e];              // residual add folded into the store
-                p.y[e] = v;
+                store_row(p, e, v);
             } else {
                 partial[(size_t)(row - cta_lo) * nchunks + myc] = v;
             }
@@ -447,13 +429,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
             const uint32_t e = y_index(p, cta_lo + i);
             if (p.x_op == 1u) v *= norm_inv;
             if (p.accumulate) v += p.y[e];
-            p.y[e] = v;
+            store_row(p, e, v);
         }
     }
-    if (p.xc.npush) {
-        __syncthreads();                                    // every row of this CTA is in y
-        exchange_push(p, cta_lo, cta_hi);
-    }
+    exchange_signal(p.xc);                                  // sharded models: this CTA's rows are on every peer
     if (tr) tr[3] = global_ns();
     if (csize > 1) cluster_wait();                          // no CTA leaves while a peer may still read its x units
     if (dead) {
@@ -580,12 +559,9 @@ __global__ void __launch_bounds__(256) gemv_generic(const GemvParams p) {
 #pragma unroll
         for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         const uint32_t e = y_index(p, row);
-        if (lane == 0) p.y[e] = p.accumulate ? p.y[e] + v : v;
+        if (lane == 0) store_row(p, e, p.accumulate ? p.y[e] + v : v);
     }
-    if (p.xc.npush) {
-        __syncthreads();
-        exchange_push(p, cta_lo, min(p.N, cta_lo + (blockDim.x >> 5)));
-    }
+    exchange_signal(p.xc);
 }
 
 constexpr size_t kSmemLimit = 227 * 1024 - 256;          // dynamic part; the kernel also has a few static words
@@ -597,6 +573,7 @@ template <int DT> size_t stream_fixed_smem(unsigned K) {
     const size_t nchunks = (K + L::STEP_W - 1) / L::STEP_W;
     return ((nchunks * 32 * L::XW * 4 + 127) / 128) * 128 + ((kMaxWarps * kMaxStages * 8 + 127) / 128) * 128 + 128;
 }
+unsigned g_last_grid = 0;
 int env_int(const char* name, int dflt) {
     const char* e = std::getenv(name);
     return e && *e ? std::atoi(e) : dflt;
@@ -631,6 +608,7 @@ bool launch_stream_r(GemvParams p, unsigned stages, unsigned grid, size_t smem, 
     }
     cfg.attrs = at; cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, gemv_stream<DT, R, kWarps>, p) != cudaSuccess) return check_launch("gemv_stream");
+    g_last_grid = grid;
     note_launch();
     return true;
 }
@@ -745,11 +723,14 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         if (xsmem > 200 * 1024) return fail("gemv: K=%u is too long for the unaligned fused form", p.K);
     }
     gemv_generic<DT><<<(p.N + rows_per_cta - 1) / rows_per_cta, rows_per_cta * 32, xsmem, st>>>(p);
+    g_last_grid = (p.N + rows_per_cta - 1) / rows_per_cta;
     note_launch();
     return check_launch("gemv_generic");
 }
 
 }  // namespace
+
+unsigned last_gemv_grid() { return g_last_grid; }
 
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
                  const SegTable& seg, cudaStream_t st, const GemvFuse* fuse) {
@@ -768,8 +749,7 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     p.x2 = nullptr; p.eps = 0.f; p.x_op = 0; p.accumulate = 0;
     p.xc = Exchange{};
     if (fuse && fuse->xchg) p.xc = *fuse->xchg;
-    if (p.xc.npush > (unsigned)kMaxPeers || (p.xc.nwait && !p.xc.wait_flags) || ((p.xc.npush || p.xc.nwait) && !p.xc.epoch) ||
-        (p.xc.npush && !p.xc.arrive))
+    if (p.xc.npush > (unsigned)kMaxPeers || (p.xc.nwait && (!p.xc.wait_ctrs || !p.xc.wait_ctas || !p.xc.epoch)))
         return fail("gemv: incomplete peer exchange description");
     if (fuse) {
         if (fuse->x_op > 2 || (fuse->x_op != 0 && (!fuse->x2 || (uintptr_t)fuse->x2 % 16))) return fail("gemv: bad fused x transform");

@@ -452,7 +452,7 @@ bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, floa
     const unsigned sms = (unsigned)device_sm_count();
     if (grid > sms) grid = sms;
     const Exchange xc = xchg ? *xchg : Exchange{};
-    if (xc.nwait && (!xc.wait_flags || !xc.epoch)) return fail("argmax: incomplete peer exchange description");
+    if (xc.nwait && (!xc.wait_ctrs || !xc.wait_ctas || !xc.epoch)) return fail("argmax: incomplete peer exchange description");
     if (sample) launch_pdl(choose_kernel<true>, dim3(grid), dim3(256), st, x, out, n, idx, inv_temp, seed, scratch, state, xc, device_status_word());
     else launch_pdl(choose_kernel<false>, dim3(grid), dim3(256), st, x, out, n, idx, 0.f, 0u, scratch, state, xc, device_status_word());
     note_launch();

@@ -29,10 +29,8 @@ bool tm_cuda_peer_arena(size_t bytes, void* handle_out) {
     uint8_t* p = nullptr;
     if (cudaMalloc(&p, want) != cudaSuccess) { cudaGetLastError(); return fail("peer: arena allocation of %zu bytes failed", want); }
     if (cudaMemset(p, 0, want) != cudaSuccess) { cudaFree(p); return check_launch("peer: arena clear"); }
-    if (cudaMalloc(&ps.arrive, kMaxSites * sizeof(unsigned long long)) != cudaSuccess) { cudaGetLastError(); cudaFree(p); return fail("peer: counter allocation failed"); }
-    cudaMemset(ps.arrive, 0, kMaxSites * sizeof(unsigned long long));
     cudaIpcMemHandle_t h;
-    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaFree(p); cudaFree(ps.arrive); ps.arrive = nullptr; return check_launch("peer: cudaIpcGetMemHandle"); }
+    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaFree(p); return check_launch("peer: cudaIpcGetMemHandle"); }
     std::memcpy(handle_out, &h, sizeof h);
     ps.arena = p; ps.bytes = want; ps.used = kFlagBytes;
     return true;
@@ -82,7 +80,6 @@ bool tm_cuda_peer_close(void) {
     tm_cuda_peer_unmap();
     for (Slot& sl : s.slots) if (sl.shared) { sl.ptr = nullptr; sl.bytes = 0; sl.shared = false; }
     cudaFree(ps.arena);
-    if (ps.arrive) cudaFree(ps.arrive);
     ps = PeerState{};
     return check_launch("peer: close");
 }

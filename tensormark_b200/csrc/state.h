@@ -28,7 +28,7 @@ struct Slot {                    // token-lane slot: backend-owned device buffer
 };
 
 // Row-sharded models: this rank's arena (exported to the peers) and the peers' arenas mapped here.
-// The arena starts with the exchange flags, flags[site][rank]; shared slots follow, at the same
+// The arena starts with the exchange counters, counters[site][rank]; shared slots follow, at the same
 // offsets on every rank because every rank reserves them in the same order.
 constexpr int kMaxRanks = 8, kMaxSites = 256;
 constexpr size_t kFlagBytes = (size_t)kMaxSites * kMaxRanks * sizeof(int);
@@ -38,7 +38,7 @@ struct PeerState {
     uint8_t* base[kMaxRanks] = {};                              // base[rank] == arena once opened
     int rank = 0, world = 1;
     bool open = false;
-    unsigned long long* arrive = nullptr;                       // [kMaxSites] finished-CTA counters, local
+    unsigned site_ctas[kMaxSites] = {};                         // CTAs of the launch that pushes to each site (0: none yet)
 };
 
 struct WeightBuf {               // registered weights: handle id = 1000 + index (metal.h:3282-3337)

@@ -498,8 +498,12 @@ static bool make_exchange(Exchange& xc, int wait_site, int push_site, int states
     const int* st = (const int*)slot_ptr(stateslot, 16, who);
     if (!st) return false;
     xc.epoch = st + 3;
-    int* flags = (int*)ps.arena;
-    if (wait_site >= 0) { xc.wait_flags = flags + (size_t)wait_site * kMaxRanks; xc.nwait = (uint32_t)ps.world; xc.self = (uint32_t)ps.rank; }
+    unsigned* ctrs = (unsigned*)ps.arena;
+    if (wait_site >= 0) {
+        if (!ps.site_ctas[wait_site]) { latch("%s: waits on site %d before any launch pushes to it", who, wait_site); return false; }
+        xc.wait_ctrs = ctrs + (size_t)wait_site * kMaxRanks; xc.nwait = (uint32_t)ps.world; xc.self = (uint32_t)ps.rank;
+        xc.wait_ctas = ps.site_ctas[wait_site];
+    }
     if (push_site >= 0) {
         if (!y_base || y_base < ps.arena + kFlagBytes || y_base >= ps.arena + ps.used) { latch("%s: the pushed output must be a shared slot", who); return false; }
         const size_t off = (size_t)(y_base - ps.arena);
@@ -507,11 +511,10 @@ static bool make_exchange(Exchange& xc, int wait_site, int push_site, int states
         for (int q = 0; q < ps.world; ++q) {
             if (q == ps.rank) continue;
             xc.peer_y[n] = (float*)(ps.base[q] + off);
-            xc.peer_flag[n] = (int*)ps.base[q] + (size_t)push_site * kMaxRanks + ps.rank;
+            xc.peer_ctr[n] = (unsigned*)ps.base[q] + (size_t)push_site * kMaxRanks + ps.rank;
             ++n;
         }
         xc.npush = n;
-        xc.arrive = ps.arrive + push_site;
     }
     return true;
 }
@@ -567,7 +570,13 @@ static void gemv_fused_impl(const char* who, int xslot, size_t xoff, int x_op, i
         if (!u) return;
         f.x2 = (const float*)(u + x2off);
     } else if (x_op != 0) { latch("%s: unknown x transform %d", who, x_op); return; }
-    if (!launch_gemv((const float*)(x + xoff), s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream, &f)) s.sticky = true;
+    if (!launch_gemv((const float*)(x + xoff), s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream, &f)) { s.sticky = true; return; }
+    if (push_site >= 0) {
+        // every rank launches the same shapes, so this grid is also what the peers' counters advance by per token
+        unsigned& ctas = s.peer.site_ctas[push_site];
+        if (ctas && ctas != last_gemv_grid()) latch("%s: site %d was pushed to by %u CTAs before, now by %u", who, push_site, ctas, last_gemv_grid());
+        ctas = last_gemv_grid();
+    }
 }
 
 void tm_cuda_tok_gemv_fused(int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,

@@ -98,16 +98,37 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc
         const unsigned long long slot = atomicAdd(trace, 1ull);
         if (slot < (unsigned long long)kTraceLaunches) { tr = trace + 1 + slot * kTraceWords; tr[0] = now_ns(); }
     }
-    pdl_enter();
-    if (tr) tr[1] = now_ns();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int dh = DPL * 32, half = dh / 2;
     const uint32_t kv = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pos_i = st[0];
-    if (pos_i < 0 || (uint32_t)pos_i >= ctx || (uint32_t)pos_i * half + half > tbl_n) return;   // same guard as the separate kernels
-    const uint32_t pos = (uint32_t)pos_i, allow = pos + 1;
+    // The position was written by the previous token's last kernel and the cache rows below it by earlier tokens:
+    // both are safe to read before this token's q|k|v GEMV has finished, and this CTA is resident (and idle) for
+    // several microseconds before that. So the first tile's loads, with their page walks and DRAM latency, are
+    // requested now; only the row of the new position is fetched after it has been written.
+    const int pos_i = *(volatile const int*)st;
+    const bool valid = !(pos_i < 0 || (uint32_t)pos_i >= ctx || (uint32_t)pos_i * half + half > tbl_n);   // same guard as the separate kernels
+    const uint32_t pos = valid ? (uint32_t)pos_i : 0u, allow = pos + 1;
     const uint32_t tiles = (allow + 31) / 32, tps = (tiles + nsplit - 1) / nsplit;
     const uint32_t t0 = min(tiles, split * tps), t1 = min(tiles, t0 + tps);
+    const T* kbase = kc + (size_t)kv * ctx * dh;
+    const T* vbase = vc + (size_t)kv * ctx * dh;
+    Raw8<T> raw[dh / 8];
+    RawV<T, DPL> vraw[32];                                     // rows past the tile's last position repeat it, their weight is 0
+    auto fetch_tile = [&](uint32_t t) {                        // this lane's K row (lane = position) and its dims of the 32 V rows
+        const uint32_t p = t * 32 + lane, np = min(32u, allow - t * 32);
+        const T* krow = kbase + (size_t)min(p, allow - 1) * dh;
+        const T* vrow = vbase + (size_t)t * 32 * dh + lane * DPL;
+#pragma unroll
+        for (int c = 0; c < dh / 8; ++c) fetch8(krow + c * 8, raw[c]);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) fetchv(vrow + (size_t)min((uint32_t)k, np - 1) * dh, vraw[k]);
+    };
+    const uint32_t t_first = t0 + warp;
+    if (valid && t_first < t1) fetch_tile(t_first);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tr) tr[1] = now_ns();
+    if (!valid) return;
 
     __shared__ __align__(16) float qs[REP][dh];
     __shared__ float sm_acc[4][REP][dh];
@@ -148,25 +169,26 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float* qkv, T* kc
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[r][d] = 0.f;
     }
-    const T* kbase = kc + (size_t)kv * ctx * dh;
-    const T* vbase = vc + (size_t)kv * ctx * dh;
-    for (uint32_t t = t0 + warp; t < t1; t += 4) {
+    for (uint32_t t = t_first; t < t1; t += 4) {
         const uint32_t p = t * 32 + lane;
         const bool live = p < allow;
         float s[REP];
 #pragma unroll
         for (int r = 0; r < REP; ++r) s[r] = 0.f;
-        // Every load of the tile is requested before anything is computed: this lane's K row (lane = position)
-        // and this lane's dims of all 32 V rows (lane = dims). One memory latency per tile instead of five.
-        const uint32_t np = min(32u, allow - t * 32);
-        const T* krow = kbase + (size_t)min(p, allow - 1) * dh;
-        const T* vrow = vbase + (size_t)t * 32 * dh + lane * DPL;
-        Raw8<T> raw[dh / 8];
-        RawV<T, DPL> vraw[32];                                 // rows past np repeat the last one, their weight is 0
+        // Every load of a tile is requested before anything is computed on it. The first tile's were requested
+        // before the wait; of those, whatever aliases the new position's row is fetched again now that it is written.
+        if (t != t_first) {
+            fetch_tile(t);
+        } else if (t == tiles - 1) {
+            const uint32_t kpos = pos - t * 32;
+            if (lane >= kpos) {
 #pragma unroll
-        for (int c = 0; c < dh / 8; ++c) fetch8(krow + c * 8, raw[c]);
+                for (int c = 0; c < dh / 8; ++c) fetch8(kbase + (size_t)pos * dh + c * 8, raw[c]);
+            }
 #pragma unroll
-        for (int k = 0; k < 32; ++k) fetchv(vrow + (size_t)min((uint32_t)k, np - 1) * dh, vraw[k]);
+            for (int k = 0; k < 32; ++k)
+                if ((uint32_t)k >= kpos) fetchv(vbase + (size_t)pos * dh + lane * DPL, vraw[k]);
+        }
         if (live) {
 #pragma unroll
             for (int c = 0; c < dh / 8; ++c) {

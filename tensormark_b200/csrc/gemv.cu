@@ -327,19 +327,18 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         cluster_arrive();                                   // x units and partial sums are in place ...
         cluster_wait();                                     // ... in every CTA
     } else {
-        __syncthreads();
-        if (p.x_op == 1u && threadIdx.x == 0) {
-            float tot = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) tot += red[w];
-            xsum[0] = tot;
-        }
-        if (p.x_op == 1u) __syncthreads();
+        __syncthreads();                                    // x units and the warps' partial sums of squares are in place
     }
     float norm_inv = 1.f;
     if (p.x_op == 1u) {
+        // every thread adds the partial sums itself (broadcast reads, fixed order): no second barrier
         float tot = 0.f;
-        for (uint32_t c = 0; c < csize; ++c) tot += xsum[c];
+        if (csize > 1) {
+            for (uint32_t c = 0; c < csize; ++c) tot += xsum[c];
+        } else {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) tot += red[w];
+        }
         norm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
     }
     if (tr) tr[2] = global_ns();

@@ -178,26 +178,22 @@ TM_HD float block_scale(float amax, bool bad, float& inv) {
     inv = 127.0f / amax;
     return amax * (1.0f / 127.0f);                          // s * inv == 1 to within 2^-23, far below the plane truncation
 }
-// The kPlanes signed bytes of one activation under its block's inverse scale.
+// The kPlanes signed bytes of one activation under its block's inverse scale: the activation is rounded once to a
+// multiple of s / 16384 (X = round(v / s * 16384), |X| <= 127 * 16384) and X is split into three signed digits,
+// X = a1 * 16384 + a2 * 128 + a3 with a1 in [-127, 127], a2 in [-64, 64], a3 in [-64, 63]. Integer arithmetic after
+// one rounding, which on the GPU is the add of 1.5 * 2^23 (the integer lands in the low mantissa bits).
 TM_HD void quantize_elem(float v, float inv, int8_t* a) {
+    static_assert(kPlanes == 3, "the digit split below is written for three planes");
     float r = inv == 0.f ? 0.f : v * inv;                   // inv is 0 for empty and for poisoned blocks
     r = r > 127.f ? 127.f : (r < -127.f ? -127.f : r);
-#pragma unroll
-    for (int t = 0; t < kPlanes; ++t) {
 #if defined(__CUDA_ARCH__)
-        // Round to nearest even by adding 1.5 * 2^23: the integer lands in the low mantissa bits, and both the
-        // integer and its float come from full-rate adds instead of two quarter-rate conversions. Same result
-        // as round_int for every |r| <= 127.
-        const float m = __fadd_rn(r, 12582912.0f);
-        const int q = __float_as_int(m) - 0x4B400000;
-        const float qf = __fsub_rn(m, 12582912.0f);
+    const int X = __float_as_int(__fadd_rn(r * 16384.0f, 12582912.0f)) - 0x4B400000;
 #else
-        const int q = round_int(r);
-        const float qf = (float)q;
+    const int X = (int)lrintf(r * 16384.0f);
 #endif
-        a[t] = (int8_t)q;
-        r = (r - qf) * 128.0f;                               // exact: |r - q| <= 0.5 and the factor is a power of two
-    }
+    const int a1 = (X + 8192) >> 14, r1 = X - a1 * 16384;
+    const int a2 = (r1 + 64) >> 7, a3 = r1 - a2 * 128;
+    a[0] = (int8_t)a1; a[1] = (int8_t)a2; a[2] = (int8_t)a3;
 }
 
 // two zero bytes at an even byte offset of the x-unit area

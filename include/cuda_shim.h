@@ -17,7 +17,7 @@
  *     latches a sticky error that makes the next tok_end / tok_flush /
  *     tok_wait_pending return false. tm_cuda_last_error() names it.
  *   - dtype codes are the container's (tensormark/tmq.h:48-60):
- *     0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K, 6 Q6_K.
+ *     0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K, 6 Q6_K, 8 Q4_K.
  *   - Host-pointer entries are blocking and, like the reference's function-local
  *     caches, not thread-safe: one caller thread per process.
  *
@@ -43,6 +43,7 @@ extern "C" {
 #define TM_DT_Q4_1 4u
 #define TM_DT_Q5_K 5u
 #define TM_DT_Q6_K 6u
+#define TM_DT_Q4_K 8u
 
 /* ---- library state ------------------------------------------------------- */
 /* Select the device for this process and create the lane stream. Called lazily

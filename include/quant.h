@@ -11,7 +11,7 @@
 // operation: build host code that includes this header with -ffp-contract=off.
 //
 // dtype ids (tensormark/tmq.h:48-60): 0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K,
-// 6 Q6_K. Geometry (tmq.h:83-115): block_elems / block_bytes below.
+// 6 Q6_K, 8 Q4_K. Geometry (tmq.h:83-115): block_elems / block_bytes below.
 #pragma once
 
 #include <bit>
@@ -38,6 +38,12 @@ struct BlockQ4_1 {             // w = nibble * d + m; byte j: low = elem j, high
     std::uint16_t m_fp16;
     std::uint8_t  qs[16];
 };
+struct BlockQ4_K {             // w = (d*sc)*nibble - (dmin*mn); dtype 8 (tmq.h:57)
+    std::uint16_t d_fp16;
+    std::uint16_t dmin_fp16;
+    std::uint8_t  scales[12];  // 8 (scale, min) pairs, 6 bits each
+    std::uint8_t  qs[128];     // byte 32g+l: low = elem 64g+l, high = elem 64g+32+l
+};
 struct BlockQ5_K {             // w = (d*sc)*code - (dmin*mn), code = nibble + 16*hibit
     std::uint16_t d_fp16;
     std::uint16_t dmin_fp16;
@@ -56,15 +62,16 @@ struct BlockQ6_K {             // w = (d*sc[sub])*(code-32)
 static_assert(sizeof(BlockQ8_0) == 34 && alignof(BlockQ8_0) == 1);
 static_assert(sizeof(BlockQ4_0) == 18 && alignof(BlockQ4_0) == 1);
 static_assert(sizeof(BlockQ4_1) == 20 && alignof(BlockQ4_1) == 1);
+static_assert(sizeof(BlockQ4_K) == 144 && alignof(BlockQ4_K) == 1);
 static_assert(sizeof(BlockQ5_K) == 176 && alignof(BlockQ5_K) == 1);
 static_assert(sizeof(BlockQ6_K) == 210 && alignof(BlockQ6_K) == 1);
 
-enum class Dtype : std::uint32_t { Q8_0 = 0, Q4_0 = 1, F32 = 2, F16 = 3, Q4_1 = 4, Q5_K = 5, Q6_K = 6 };
+enum class Dtype : std::uint32_t { Q8_0 = 0, Q4_0 = 1, F32 = 2, F16 = 3, Q4_1 = 4, Q5_K = 5, Q6_K = 6, Q4_K = 8 };
 
 constexpr std::uint32_t block_elems(std::uint32_t dtype) {
     switch (dtype) {
         case 0: case 1: case 4: return 32;
-        case 5: case 6: return 256;
+        case 5: case 6: case 8: return 256;
         case 2: case 3: return 1;
         default: return 0;
     }
@@ -72,7 +79,7 @@ constexpr std::uint32_t block_elems(std::uint32_t dtype) {
 constexpr std::size_t block_bytes(std::uint32_t dtype) {
     switch (dtype) {
         case 0: return 34; case 1: return 18; case 2: return 4; case 3: return 2;
-        case 4: return 20; case 5: return 176; case 6: return 210;
+        case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144;
         default: return 0;
     }
 }
@@ -180,6 +187,30 @@ inline void dequantize_row_q4_1(const BlockQ4_1* in, float* x, std::size_t n) {
     }
 }
 
+// reference quant.h:282-301
+inline void dequantize_row_q4_K(const BlockQ4_K* in, float* x, std::size_t n) {
+    detail::need_rows(in, x, n, kKBlock);
+    for (std::size_t b = 0; b < n / kKBlock; ++b) {
+        const BlockQ4_K& k = in[b];
+        float* y = x + b * kKBlock;
+        const float d = fp16_to_fp32(k.d_fp16);
+        const float dmin = fp16_to_fp32(k.dmin_fp16);
+        for (int g = 0; g < 4; ++g) {
+            for (int half = 0; half < 2; ++half) {
+                std::uint8_t sc, mn;
+                k_scale_min(2 * g + half, k.scales, sc, mn);
+                const float dl = d * (float)sc;
+                const float ml = dmin * (float)mn;
+                for (int l = 0; l < 32; ++l) {
+                    const int nib = half ? (k.qs[32 * g + l] >> 4) : (k.qs[32 * g + l] & 15);
+                    const float prod = dl * (float)nib;
+                    y[64 * g + 32 * half + l] = prod - ml;
+                }
+            }
+        }
+    }
+}
+
 inline void dequantize_row_q5_K(const BlockQ5_K* in, float* x, std::size_t n) {
     detail::need_rows(in, x, n, kKBlock);
     for (std::size_t b = 0; b < n / kKBlock; ++b) {
@@ -236,6 +267,7 @@ inline void dequantize_row(std::uint32_t dtype, const void* in, float* x, std::s
         case 4: dequantize_row_q4_1(static_cast<const BlockQ4_1*>(in), x, n); break;
         case 5: dequantize_row_q5_K(static_cast<const BlockQ5_K*>(in), x, n); break;
         case 6: dequantize_row_q6_K(static_cast<const BlockQ6_K*>(in), x, n); break;
+        case 8: dequantize_row_q4_K(static_cast<const BlockQ4_K*>(in), x, n); break;
         default: throw std::invalid_argument("dequantize_row: dtype is not a block format");
     }
 }

@@ -20,6 +20,7 @@ __attribute__((visibility("default"))) int tmref_dequant(int dtype, const void* 
             case 4: tmq::dequantize_row_q4_1(static_cast<const tmq::BlockQ4_1*>(blocks), out, n); return 1;
             case 5: tmq::dequantize_row_q5_K(static_cast<const tmq::BlockQ5_K*>(blocks), out, n); return 1;
             case 6: tmq::dequantize_row_q6_K(static_cast<const tmq::BlockQ6_K*>(blocks), out, n); return 1;
+            case 8: tmq::dequantize_row_q4_K(static_cast<const tmq::BlockQ4_K*>(blocks), out, n); return 1;
             default: return 0;
         }
     } catch (...) { return 0; }

@@ -63,10 +63,10 @@ static uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); 
 
 /* ---- geometry (tensormark/tmq.h:83-115) ---------------------------------- */
 TMO_API int tmo_block_elems(int dtype) {
-    switch (dtype) { case 0: case 1: case 4: return 32; case 5: case 6: return 256; default: return 0; }
+    switch (dtype) { case 0: case 1: case 4: return 32; case 5: case 6: case 8: return 256; default: return 0; }
 }
 TMO_API int tmo_block_bytes(int dtype) {
-    switch (dtype) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; default: return 0; }
+    switch (dtype) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
 }
 
 /* ---- dequantizers --------------------------------------------------------- */
@@ -100,6 +100,24 @@ static void scale_min(int j, const uint8_t* q, uint8_t* d, uint8_t* m) {
     else {
         *d = (uint8_t)((q[j + 4] & 0x0fu) | ((q[j - 4] >> 6) << 4));
         *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+/* Q4_K, quant.h:282-301: four groups of 64; low nibbles = sub-block 2g, high nibbles = 2g+1; w = d1*code - m1 */
+static void deq_q4_k(const uint8_t* b, float* x) {
+    float d = tmo_fp16_to_fp32(rd16(b)), dm = tmo_fp16_to_fp32(rd16(b + 2));
+    const uint8_t *scales = b + 4, *qs = b + 16;
+    for (int g = 0; g < 4; g++) {
+        uint8_t sc, mn;
+        scale_min(2 * g, scales, &sc, &mn);
+        float d1 = d * (float)sc, m1 = dm * (float)mn;
+        scale_min(2 * g + 1, scales, &sc, &mn);
+        float d2 = d * (float)sc, m2 = dm * (float)mn;
+        for (int j = 0; j < 32; j++) {
+            uint8_t packed = qs[32 * g + j];
+            float p1 = d1 * (float)(packed & 0x0fu), p2 = d2 * (float)(packed >> 4);
+            x[64 * g + j] = p1 - m1;
+            x[64 * g + 32 + j] = p2 - m2;
+        }
     }
 }
 /* Q5_K, quant.h:304-330: d1 = d*sc, m1 = dmin*mn, w = d1*code - m1 */
@@ -159,6 +177,7 @@ TMO_API int tmo_dequant(int dtype, const void* blocks, float* out, size_t n) {
             case 1: deq_q4_0(p, out); break;
             case 4: deq_q4_1(p, out); break;
             case 5: deq_q5_k(p, out); break;
+            case 8: deq_q4_k(p, out); break;
             default: deq_q6_k(p, out); break;
         }
     }

@@ -8,13 +8,13 @@
 namespace tmc {
 
 // dtype ids of the weight container (tensormark/tmq.h:48-60)
-enum : unsigned { DT_Q8_0 = 0, DT_Q4_0 = 1, DT_F16 = 3, DT_Q4_1 = 4, DT_Q5_K = 5, DT_Q6_K = 6 };
+enum : unsigned { DT_Q8_0 = 0, DT_Q4_0 = 1, DT_F16 = 3, DT_Q4_1 = 4, DT_Q5_K = 5, DT_Q6_K = 6, DT_Q4_K = 8 };
 
 inline __host__ __device__ unsigned block_elems(unsigned dt) {
-    return (dt == 0 || dt == 1 || dt == 4) ? 32u : (dt == 5 || dt == 6) ? 256u : 0u;
+    return (dt == 0 || dt == 1 || dt == 4) ? 32u : (dt == 5 || dt == 6 || dt == 8) ? 256u : 0u;
 }
 inline __host__ __device__ unsigned block_bytes(unsigned dt) {
-    switch (dt) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; default: return 0; }
+    switch (dt) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
 }
 inline size_t weight_bytes(unsigned dt, size_t n_out, size_t n_in) {
     const unsigned e = block_elems(dt);

@@ -52,6 +52,7 @@ bool launch(const uint8_t* W, void* out, unsigned N, unsigned K, unsigned dtype,
         case DT_Q4_0: dequant_rows<1, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         case DT_Q4_1: dequant_rows<4, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         case DT_Q5_K: dequant_rows<5, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
+        case DT_Q4_K: dequant_rows<8, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         default:      dequant_rows<6, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
     }
     note_launch();

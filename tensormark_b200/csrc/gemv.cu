@@ -506,6 +506,25 @@ template <> __device__ float generic_row<5>(const uint8_t* r, const float* x, ui
     }
     return acc;
 }
+template <> __device__ float generic_row<8>(const uint8_t* r, const float* x, uint32_t K, int lane) {
+    float acc = 0.f;
+    for (uint32_t u = lane; u < K / 32; u += 32) {          // one (super-block, sub-block) pair per lane iteration
+        const uint8_t* q = r + (size_t)(u >> 3) * 144;
+        const uint32_t j = u & 7, g = j >> 1, hi = j & 1;
+        const uint8_t* sc = q + 4;
+        uint32_t s6, m6;
+        if (j < 4) { s6 = sc[j] & 63u; m6 = sc[j + 4] & 63u; }
+        else { s6 = (sc[j + 4] & 15u) | ((sc[j - 4] >> 6) << 4); m6 = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+        float s = 0.f, xs = 0.f;
+        for (int l = 0; l < 32; ++l) {
+            const uint32_t code = hi ? (q[16 + 32 * g + l] >> 4) : (q[16 + 32 * g + l] & 15u);
+            const float xv = x[(u >> 3) * 256 + j * 32 + l];
+            s += (float)code * xv; xs += xv;
+        }
+        acc += ldh(q) * (float)s6 * s - ldh(q + 2) * (float)m6 * xs;
+    }
+    return acc;
+}
 template <> __device__ float generic_row<6>(const uint8_t* r, const float* x, uint32_t K, int lane) {
     float acc = 0.f;
     // one 16-weight sub-block per lane iteration: sub = 8h + 2j + (l/16)
@@ -761,6 +780,7 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
         case DT_Q4_0: return launch_dt<1>(p, aligned, st);
         case DT_Q4_1: return launch_dt<4>(p, aligned, st);
         case DT_Q5_K: return launch_dt<5>(p, aligned, st);
+        case DT_Q4_K: return launch_dt<8>(p, aligned, st);
         default: return launch_dt<6>(p, aligned, st);
     }
 }

@@ -436,6 +436,46 @@ template <> struct Lane<5> {
 };
 
 // =============================================================================
+// Q4_K: 144-byte super-blocks of 256 (tensormark/quant.h:222-228, 282-301): the Q5_K block without the
+// high bits. Same lane split (eight lanes per super-block, lane i = group i/2, byte half i%2) and the same
+// x unit as Q5_K; 16-byte aligned reads because 144 is a multiple of 16.
+// =============================================================================
+template <> struct Lane<8> : Lane<5> {
+    static constexpr int STEP_BYTES = 576;                   // four super-blocks per step
+    static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
+        const int sb = lane >> 3;
+        if (sb >= nvalid) return 0.f;
+        const uint32_t g = (uint32_t)(lane & 7) >> 1, q = (uint32_t)lane & 1u;
+        const uint8_t* B = p + 144 * sb;
+        const uint4 hdr = load16a(B);                       // d|dmin, scales[12]
+        const uint4 qs = load16a(B + 16 + 32 * g + 16 * q);
+        float sc[2], mn[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const uint32_t j = 2u * g + (uint32_t)t, sh = 8u * (j & 3u);
+            const uint32_t a = (hdr.y >> sh) & 0xffu, b = (hdr.z >> sh) & 0xffu, c = (hdr.w >> sh) & 0xffu;
+            const uint32_t s_lo = a & 63u, m_lo = b & 63u;
+            const uint32_t s_hi = (c & 15u) | ((a >> 6) << 4), m_hi = (c >> 4) | ((b >> 6) << 4);
+            sc[t] = (float)(j < 4u ? s_lo : s_hi);
+            mn[t] = (float)(j < 4u ? m_lo : m_hi);
+        }
+        const uint32_t wq[4] = {qs.x, qs.y, qs.z, qs.w};
+        int S0[kPlanes], S1[kPlanes];
+#pragma unroll
+        for (int t = 0; t < kPlanes; ++t) {
+            int a = 0, b = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a = dp4a_us(wq[e] & kLo, x.w[4 * t + e], a); b = dp4a_us((wq[e] >> 4) & kLo, x.w[12 + 4 * t + e], b); }
+            S0[t] = a; S1[t] = b;
+        }
+        const float d = half_to_float(hdr.x & 0xffffu), dmin = half_to_float(hdr.x >> 16);
+        const float pos = fma1(sc[0] * as_float(x.w[24]), planes_to_float(S0), sc[1] * as_float(x.w[25]) * planes_to_float(S1));
+        const float neg = fma1(mn[0], as_float(x.w[26]), mn[1] * as_float(x.w[27]));
+        return fma1(d, pos, -(dmin * neg));
+    }
+};
+
+// =============================================================================
 // Q6_K: 210-byte super-blocks of 256, only 2-byte aligned. Four lanes share a
 // super-block; lane i takes l in [8i, 8i+8) of both 128-halves: for each half 8 bytes
 // of ql[l], 8 of ql[l+32], 8 of qh[l] -> 4 runs of 8 weights (elements l + 32j), each

@@ -2,7 +2,7 @@
 //
 // decode_weight<DT>(row, k) returns weight k of a row exactly as the reference's
 // scalar dequantizers produce it (tensormark/quant.h:194-200 Q8_0, 397-408 Q4_0,
-// 267-277 Q4_1, 304-330 Q5_K, 338-365 Q6_K): the same fp32 operations in the
+// 267-277 Q4_1, 282-301 Q4_K, 304-330 Q5_K, 338-365 Q6_K): the same fp32 operations in the
 // same order, each rounded separately (__fmul_rn/__fadd_rn/__fsub_rn keep the
 // compiler from contracting them into FMAs), and the same half->float rule for
 // every encoding including subnormals and NaN payloads (quant.h:58-70).
@@ -54,6 +54,19 @@ template <> __device__ __forceinline__ float decode_weight<5>(const uint8_t* row
     const float m1 = __fmul_rn(rd_half(b + 2), __uint2float_rn(m6));
     return __fsub_rn(__fmul_rn(d1, __uint2float_rn(code)), m1);
 }
+template <> __device__ __forceinline__ float decode_weight<8>(const uint8_t* row, uint32_t k) {   // Q4_K, quant.h:282-301
+    const uint8_t* b = row + (size_t)(k >> 8) * 144;
+    const uint32_t e = k & 255, j = e >> 5, g = j >> 1, l = e & 31;
+    const uint8_t* sc = b + 4;
+    uint32_t s6, m6;
+    if (j < 4) { s6 = sc[j] & 63u; m6 = sc[j + 4] & 63u; }
+    else { s6 = (sc[j + 4] & 15u) | ((uint32_t)(sc[j - 4] >> 6) << 4); m6 = (uint32_t)(sc[j + 4] >> 4) | ((uint32_t)(sc[j] >> 6) << 4); }
+    const uint32_t byte = b[16 + 32 * g + l];
+    const uint32_t code = (j & 1) ? (byte >> 4) : (byte & 15u);
+    const float d1 = __fmul_rn(rd_half(b), __uint2float_rn(s6));
+    const float m1 = __fmul_rn(rd_half(b + 2), __uint2float_rn(m6));
+    return __fsub_rn(__fmul_rn(d1, __uint2float_rn(code)), m1);
+}
 template <> __device__ __forceinline__ float decode_weight<6>(const uint8_t* row, uint32_t k) {
     const uint8_t* b = row + (size_t)(k >> 8) * 210;
     const uint32_t e = k & 255, h = e >> 7, j = (e >> 5) & 3, l = e & 31;
@@ -72,6 +85,7 @@ __device__ __forceinline__ float decode_weight_dt(unsigned dt, const uint8_t* ro
         case 1: return decode_weight<1>(row, k);
         case 4: return decode_weight<4>(row, k);
         case 5: return decode_weight<5>(row, k);
+        case 8: return decode_weight<8>(row, k);
         default: return decode_weight<6>(row, k);
     }
 }

@@ -306,7 +306,7 @@ void tm_cuda_tok_gemv(int xslot, int wid, uint64_t woff, int yslot, size_t yoff,
     gemv_common(xslot, wid, yslot, yoff, N, K, DT_Q4_0, &woff, &N, 1, "tok_gemv");
 }
 bool tm_cuda_tok_gemv_seg_supported(unsigned dtype) {
-    return dtype == DT_Q8_0 || dtype == DT_Q4_0 || dtype == DT_Q4_1 || dtype == DT_Q5_K || dtype == DT_Q6_K;
+    return dtype == DT_Q8_0 || dtype == DT_Q4_0 || dtype == DT_Q4_1 || dtype == DT_Q5_K || dtype == DT_Q6_K || dtype == DT_Q4_K;
 }
 void tm_cuda_tok_gemv_seg(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigned K,
                           const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg) {

@@ -12,10 +12,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_0, F16, Q4_1, Q5_K, Q6_K = 0, 1, 3, 4, 5, 6
-DTYPE_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_K: "Q5_K", Q6_K: "Q6_K"}
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_1: 32, Q5_K: 256, Q6_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_1: 20, Q5_K: 176, Q6_K: 210}
+Q8_0, Q4_0, F16, Q4_1, Q5_K, Q6_K, Q4_K = 0, 1, 3, 4, 5, 6, 8
+DTYPE_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_K: "Q5_K", Q6_K: "Q6_K", Q4_K: "Q4_K"}
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_1: 32, Q5_K: 256, Q6_K: 256, Q4_K: 256}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_1: 20, Q5_K: 176, Q6_K: 210, Q4_K: 144}
 
 
 def weight_bytes(dtype: int, n_out: int, n_in: int) -> int:
@@ -49,6 +49,7 @@ def make_weights(dtype: int, n_out: int, n_in: int, seed: int, stream: int = 1) 
       Q4_1  d = half(|N(0,1)| * 0.02), m = half(N(0, 0.05)), codes uniform in 0..15
       Q5_K  d, dmin = half(|N(0,1)| * 0.001); scales, qh, qs uniform random bytes
       Q6_K  ql, qh uniform bytes; scales int8 uniform in -32..31; d = half(|N(0,1)| * 0.001)
+      Q4_K  d, dmin = half(|N(0,1)| * 0.001); scales, qs uniform random bytes
     """
     g = rng_for(seed, stream)
     nb = n_out * (n_in // BLOCK_ELEMS[dtype])
@@ -68,6 +69,10 @@ def make_weights(dtype: int, n_out: int, n_in: int, seed: int, stream: int = 1) 
         out[:, 0:2] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
         out[:, 2:4] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
         out[:, 4:176] = g.integers(0, 256, size=(nb, 172), dtype=np.uint8)
+    elif dtype == Q4_K:
+        out[:, 0:2] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
+        out[:, 2:4] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
+        out[:, 4:144] = g.integers(0, 256, size=(nb, 140), dtype=np.uint8)
     elif dtype == Q6_K:
         out[:, 0:192] = g.integers(0, 256, size=(nb, 192), dtype=np.uint8)
         out[:, 192:208] = g.integers(-32, 32, size=(nb, 16), dtype=np.int8).view(np.uint8)

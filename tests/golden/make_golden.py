@@ -29,7 +29,7 @@ def special_blocks(dtype: int, rng: np.random.Generator) -> np.ndarray:
     """One block per special scale encoding (zero, subnormal, max, inf, NaN ...) with random codes,
     plus all-min / all-max code blocks."""
     bb = synth.BLOCK_BYTES[dtype]
-    scale_off = {0: [0], 1: [0], 4: [0, 2], 5: [0, 2], 6: [208]}[dtype]
+    scale_off = {0: [0], 1: [0], 4: [0, 2], 5: [0, 2], 6: [208], 8: [0, 2]}[dtype]
     out = []
     for h in SPECIAL_HALVES:
         for off in scale_off:

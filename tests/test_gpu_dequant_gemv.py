@@ -13,7 +13,7 @@ from tensormark_b200 import lib, synth
 from tests.gpu_util import dev_bytes, dev_f32, gemv_dev, ptr, stream_ptr
 
 pytestmark = pytest.mark.gpu
-DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K]
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
 TOL = 1e-3      # relative to sum_k |w_k x_k| per output, the bar the path is judged by
 
 
@@ -83,7 +83,7 @@ def test_config2_tinyllama_sweep(cuda, torch_mod, orc, dt, seed, shape):
     _check_gemv(cuda, torch_mod, orc, dt, shape[0], shape[1], seed=seed)
 
 
-@pytest.mark.parametrize("dt", [synth.Q5_K, synth.Q6_K])
+@pytest.mark.parametrize("dt", [synth.Q5_K, synth.Q6_K, synth.Q4_K])
 @pytest.mark.parametrize("shape", synth.LLAMA3_8B_SHAPES)
 def test_config3_kquant_llama3_shapes(cuda, torch_mod, orc, dt, shape):
     _check_gemv(cuda, torch_mod, orc, dt, shape[0], shape[1], seed=3)

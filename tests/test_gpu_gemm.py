@@ -45,6 +45,7 @@ def _check_samples(orc, dt, W, A, Cm, n, k, ns=4096, seed=0):
     (synth.Q8_0, 50, 128, 256),
     (synth.Q4_1, 50, 128, 256),
     (synth.Q5_K, 50, 128, 512),
+    (synth.Q4_K, 50, 128, 512),
 ])
 def test_small_shapes_full_check(cuda, torch_mod, orc, dt, m, n, k):
     W = synth.make_weights(dt, n, k, seed=4)

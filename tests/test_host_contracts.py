@@ -12,7 +12,7 @@ import pytest
 from tensormark_b200 import synth
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K]
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
 _f32p = C.POINTER(C.c_float)
 
 
@@ -91,6 +91,7 @@ def test_gemv_pool_rows(hc, orc, dt):
     (synth.Q4_1, [(5, 2048), (3, 5632), (2, 160)]),
     (synth.Q5_K, [(4, 4096), (2, 14336), (3, 256), (2, 768)]),
     (synth.Q6_K, [(4, 4096), (2, 14336), (3, 2048), (2, 256), (2, 5632)]),
+    (synth.Q4_K, [(4, 4096), (2, 14336), (3, 256), (2, 768)]),
 ])
 def test_gemv_lane_maps_on_cpu(lanes, orc, dt, shapes):
     """The kernel's lane decomposition, replayed on the CPU, against the fp64 reference.

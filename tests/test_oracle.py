@@ -7,7 +7,7 @@ import pytest
 from oracle import binding
 from tensormark_b200 import synth
 
-DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K]
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
 
 
 @pytest.mark.parametrize("dt", DTYPES)

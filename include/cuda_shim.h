@@ -217,6 +217,11 @@ void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int ou
 void tm_cuda_tok_attn_fused_at(int qkvslot, int kcslot, int vcslot, int probslot, int outslot, unsigned H, unsigned KVH,
                                unsigned dh, unsigned ctx, float scale, float theta, int stateslot);
 void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot);
+/* Chain form of tok_sample (Gumbel-max, metal.h:2349-2379): the noise is the reference's hash of (seed, token
+ * index, vocabulary index), the token index coming from the chain state; inv_temp <= 0 is the plain argmax.
+ * wait_site >= 0: wait for that gather first (row-sharded models), -1 otherwise. */
+void tm_cuda_tok_sample_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, float inv_temp, unsigned seed, int stateslot,
+                           int wait_site);
 /* x = row tok[index] of the embedding table. */
 void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
                           int stateslot);

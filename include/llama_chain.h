@@ -85,6 +85,7 @@ public:
     }
     ~CudaLlama() {
         if (graph_ >= 0) tm_cuda_tok_graph_destroy(graph_);
+        if (sgraph_ >= 0) tm_cuda_tok_graph_destroy(sgraph_);
     }
     CudaLlama(const CudaLlama&) = delete;
     CudaLlama& operator=(const CudaLlama&) = delete;
@@ -269,7 +270,8 @@ public:
         } else {
             tm_cuda_tok_gemv_fused(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, 0, Vn, (unsigned)d_.D, d_.dt_head, &head_.woff, &Vn, 1, 0);
         }
-        tm_cuda_tok_argmax_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE);
+        if (inv_temp_ > 0.f) tm_cuda_tok_sample_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, inv_temp_, seed_, SLOT_STATE, -1);
+        else tm_cuda_tok_argmax_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE);
         tm_cuda_tok_advance(SLOT_STATE);
     }
 
@@ -306,7 +308,8 @@ public:
         const size_t hd_yoff[1] = {rk * Vs * 4};
         tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, hd_yoff, Vs, Dn, d_.dt_head, &head_.woff, &Vs, 1, 0,
                               2 * d_.L - 1, 2 * d_.L, SLOT_STATE);
-        tm_cuda_tok_argmax_xchg(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE, 2 * d_.L);
+        if (inv_temp_ > 0.f) tm_cuda_tok_sample_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, inv_temp_, seed_, SLOT_STATE, 2 * d_.L);
+        else tm_cuda_tok_argmax_xchg(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE, 2 * d_.L);
         tm_cuda_tok_advance(SLOT_STATE);
     }
 
@@ -328,6 +331,14 @@ public:
 
     // Greedy chain (tensormark/llama.h:6047-6165): feeds `first` at the current position and
     // chooses n tokens on the GPU, chosen tokens 0..n-2 being fed by the following steps.
+    // The same chain with Gumbel-max sampling on the GPU (tensormark/metal.h:2349-2379: noise = hash of seed, token
+    // index and vocabulary index; inv_temp = 1 / temperature). Every rank of a sharded model draws the same tokens.
+    void gpu_chain_begin_sampled(int first, int n, float inv_temp, unsigned seed) {
+        if (!(inv_temp > 0.f) || !std::isfinite(inv_temp)) throw std::invalid_argument("llama: sampling needs a positive, finite inverse temperature");
+        inv_temp_ = inv_temp; seed_ = seed;
+        try { gpu_chain_begin(first, n); } catch (...) { inv_temp_ = 0.f; throw; }
+        inv_temp_ = 0.f;                                       // the launches are enqueued; later chains are greedy again
+    }
     void gpu_chain_begin(int first, int n) {
         if (n <= 0) throw std::invalid_argument("llama: chain needs n >= 1");
         if (first < 0 || first >= d_.V) throw std::invalid_argument("llama: token id out of range");
@@ -347,7 +358,8 @@ public:
                 if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
                 tm_cuda_tok_embed_kq(SLOT_TOK, (unsigned)i, embed_.id, embed_.woff, SLOT_X, (unsigned)d_.D, d_.dt_embed);
                 encode_gpu_token(seen + i);
-                tm_cuda_tok_argmax(SLOT_LOGITS, SLOT_TOK, (unsigned)(i + 1), (unsigned)d_.V);
+                if (inv_temp_ > 0.f) tm_cuda_tok_sample(SLOT_LOGITS, SLOT_TOK, (unsigned)(i + 1), (unsigned)d_.V, inv_temp_, seed_);
+                else tm_cuda_tok_argmax(SLOT_LOGITS, SLOT_TOK, (unsigned)(i + 1), (unsigned)d_.V);
                 if (!tm_cuda_tok_end_async()) throw std::runtime_error("cuda: token commit failed");
             }
         }
@@ -417,17 +429,22 @@ private:
         const int st[3] = {seen, 0, forced};
         if (!tm_cuda_tok_upload(SLOT_STATE, 0, st, sizeof st)) throw std::runtime_error("cuda: chain state upload failed");
         int left = n;
-        if (graph_ < 0) {
+        // one graph for greedy chains, one for sampled chains (it holds the temperature and the seed)
+        const bool sampling = inv_temp_ > 0.f;
+        int& g = sampling ? sgraph_ : graph_;
+        if (sampling && g >= 0 && (sg_inv_temp_ != inv_temp_ || sg_seed_ != seed_)) { tm_cuda_tok_graph_destroy(g); g = -1; }
+        if (g < 0) {
             if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
             encode_chain_token(cap);
             if (!tm_cuda_tok_flush()) throw std::runtime_error(std::string("cuda: chain token failed: ") + tm_cuda_last_error());
             if (!tm_cuda_tok_graph_begin()) throw std::runtime_error("cuda: graph capture failed");
             encode_chain_token(cap);
-            graph_ = tm_cuda_tok_graph_end();
-            if (graph_ < 0) throw std::runtime_error(std::string("cuda: graph capture failed: ") + tm_cuda_last_error());
+            g = tm_cuda_tok_graph_end();
+            if (g < 0) throw std::runtime_error(std::string("cuda: graph capture failed: ") + tm_cuda_last_error());
+            if (sampling) { sg_inv_temp_ = inv_temp_; sg_seed_ = seed_; }
             left -= 1;
         }
-        if (left > 0 && !tm_cuda_tok_graph_launch(graph_, (unsigned)left)) throw std::runtime_error("cuda: graph launch failed");
+        if (left > 0 && !tm_cuda_tok_graph_launch(g, (unsigned)left)) throw std::runtime_error("cuda: graph launch failed");
     }
 
     struct Handle { int id = -1; uint64_t woff = 0; };
@@ -440,7 +457,9 @@ private:
     Handle embed_, head_;
     std::vector<float> logits_;
     bool ready_ = false, use_graph_ = true;
-    int graph_ = -1, chain_n_ = 0, chain_seen0_ = 0;
+    int graph_ = -1, sgraph_ = -1, chain_n_ = 0, chain_seen0_ = 0;
+    float inv_temp_ = 0.f, sg_inv_temp_ = 0.f;                 // > 0 only while a sampled chain is being encoded
+    unsigned seed_ = 0, sg_seed_ = 0;
 };
 
 }  // namespace tmllama

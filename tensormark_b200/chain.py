@@ -28,6 +28,7 @@ def load() -> C.CDLL:
         L.tmchain_greedy.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
         L.tmchain_feed.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.tmchain_chain_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.tmchain_chain_begin_sampled.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_uint, C.c_int]
         L.tmchain_chain_poll.argtypes = [C.c_void_p, C.c_int]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         _lib = L
@@ -131,6 +132,10 @@ class Chain:
 
     def chain_begin(self, first: int, n: int, graph: bool = True):
         self._check(self.L.tmchain_chain_begin(self.h, int(first), n, int(graph)))
+
+    def chain_begin_sampled(self, first: int, n: int, inv_temp: float, seed: int, graph: bool = True):
+        """Gumbel-max sampling on the GPU instead of the greedy choice (inv_temp = 1 / temperature)."""
+        self._check(self.L.tmchain_chain_begin_sampled(self.h, int(first), n, float(inv_temp), int(seed), int(graph)))
 
     def chain_poll(self, i: int) -> int:
         return self.L.tmchain_chain_poll(self.h, i)

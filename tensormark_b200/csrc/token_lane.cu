@@ -642,7 +642,8 @@ void tm_cuda_tok_attn_fused_at(int qkvslot, int kcslot, int vcslot, int probslot
     if (!launch_attn_fused(qkv, kc, vc, s.kv_half, probs, s.slots[probslot].bytes, out, H, KVH, dh, ctx, scale, s.rope_tbl,
                            s.rope_cap * (dh / 2), st, s.stream)) s.sticky = true;
 }
-static void argmax_at_impl(const char* who, int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site) {
+static void argmax_at_impl(const char* who, int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site,
+                           bool sample = false, float inv_temp = 0.f, unsigned seed = 0u) {
     if (!ensure_init(-1)) return;
     State& s = state();
     const float* x = (const float*)slot_ptr(xslot, (size_t)n * 4, who);
@@ -652,7 +653,11 @@ static void argmax_at_impl(const char* who, int xslot, int tokslot, unsigned n, 
     if (!x || !t || !st || !sc) return;
     Exchange xc;
     if (!make_exchange(xc, wait_site, -1, stateslot, nullptr, who)) return;
-    if (!launch_choose(x, t, n, 0, 0.f, 0u, false, sc, s.stream, st, xc.nwait ? &xc : nullptr)) s.sticky = true;
+    if (!launch_choose(x, t, n, 0, inv_temp, seed, sample, sc, s.stream, st, xc.nwait ? &xc : nullptr)) s.sticky = true;
+}
+void tm_cuda_tok_sample_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, float inv_temp, unsigned seed, int stateslot,
+                           int wait_site) {
+    argmax_at_impl("tok_sample_at", xslot, tokslot, n, max_tokens, stateslot, wait_site, true, inv_temp, seed);
 }
 void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot) {
     argmax_at_impl("tok_argmax_at", xslot, tokslot, n, max_tokens, stateslot, -1);

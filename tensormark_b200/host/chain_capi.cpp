@@ -82,6 +82,15 @@ TMCHAIN_API int tmchain_chain_begin(void* p, int first, int n, int use_graph) {
         return 1;
     } catch (const std::exception& e) { g_err = e.what(); return 0; }
 }
+// The same with Gumbel-max sampling (inv_temp = 1 / temperature).
+TMCHAIN_API int tmchain_chain_begin_sampled(void* p, int first, int n, float inv_temp, unsigned seed, int use_graph) {
+    try {
+        auto& m = *static_cast<Holder*>(p)->m;
+        m.set_graph_lane(use_graph != 0);
+        m.gpu_chain_begin_sampled(first, n, inv_temp, seed);
+        return 1;
+    } catch (const std::exception& e) { g_err = e.what(); return 0; }
+}
 TMCHAIN_API int tmchain_chain_poll(void* p, int i) { return static_cast<Holder*>(p)->m->gpu_chain_poll(i); }
 TMCHAIN_API int tmchain_chain_end(void* p, int keep, int* out, int cap) {
     try {

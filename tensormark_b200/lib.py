@@ -78,6 +78,7 @@ SIGNATURES = {
     "tm_cuda_tok_qkv_post_at": (None, [C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_int]),
     "tm_cuda_tok_attn_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, _u, C.c_float, _u, C.c_int]),
     "tm_cuda_tok_attn_fused_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_float, C.c_int]),
+    "tm_cuda_tok_sample_at": (None, [C.c_int, C.c_int, _u, _u, C.c_float, _u, C.c_int, C.c_int]),
     "tm_cuda_tok_argmax_at": (None, [C.c_int, C.c_int, _u, _u, C.c_int]),
     "tm_cuda_tok_embed_at": (None, [C.c_int, C.c_int, _u64, C.c_int, _u, _u, _u, C.c_int]),
     "tm_cuda_tok_advance": (None, [C.c_int]),

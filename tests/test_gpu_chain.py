@@ -106,3 +106,50 @@ def test_chain_polling_and_argument_errors(cuda, tiny):
     with pytest.raises(RuntimeError):
         gpu.forward(cfg["V"])                                 # token id out of range
     gpu.close()
+
+
+def _gumbel_choice(logits: np.ndarray, idx: int, inv_temp: float, seed: int) -> int:
+    """The reference's sampler restated with numpy (tensormark/metal.h:2349-2379): noise = hash(seed, idx, i)."""
+    def h32(x):
+        x = x.astype(np.uint64) & 0xFFFFFFFF
+        x ^= x >> 16; x = (x * 0x7feb352d) & 0xFFFFFFFF
+        x ^= x >> 15; x = (x * 0x846ca68b) & 0xFFFFFFFF
+        x ^= x >> 16
+        return x
+    base = h32(np.array([(seed * 0x9e3779b9 + idx * 0x85ebca6b + 0x1234567) & 0xFFFFFFFF], dtype=np.uint64))[0]
+    i = np.arange(logits.size, dtype=np.uint64)
+    h = h32(np.uint64(base) ^ ((i * 0x27d4eb2f + 0x165667b1) & 0xFFFFFFFF))
+    u = ((h >> 8).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
+    v = logits.astype(np.float32) * np.float32(inv_temp) - np.log(-np.log(u.astype(np.float64))).astype(np.float32)
+    return int(np.argmax(v)), np.sort(v)[-2:]
+
+
+def test_sampled_chain(cuda, tiny):
+    cfg, w = tiny
+    a = chain.Chain(cfg, w)
+    logits = a.forward(5)                                     # position 0; the chain below re-feeds token 5 at position 1
+    a.seen = 0
+    a.chain_begin_sampled(5, 6, 1.3, 77, graph=True)
+    ta = a.chain_end(6)
+    a.seen = 0
+    a.chain_begin_sampled(5, 6, 1.3, 77, graph=False)        # one lane call per op, reference order
+    tb = a.chain_end(6)
+    assert list(ta) == list(tb)
+    # first sampled token against the reference's formula on the same logits (index 1 of the token slot)
+    want, top2 = _gumbel_choice(logits, 1, 1.3, 77)
+    assert int(ta[0]) == want or abs(float(top2[1] - top2[0])) < 1e-4
+    # another seed or temperature is another graph; a very low temperature is the greedy chain
+    a.seen = 0
+    a.chain_begin_sampled(5, 6, 1.3, 78, graph=True)
+    tc = a.chain_end(6)
+    a.seen = 0
+    a.chain_begin_sampled(5, 6, 1e4, 78, graph=True)
+    td = a.chain_end(6)
+    a.seen = 0
+    a.chain_begin(5, 6, graph=True)
+    te = a.chain_end(6)
+    assert list(td) == list(te)
+    assert list(tc) != list(ta) or list(tc) != list(te)       # 6 draws from 1024 tokens at T = 0.77: not all equal by chance
+    with pytest.raises(RuntimeError):
+        a.chain_begin_sampled(5, 2, 0.0, 1)
+    a.close()

@@ -166,6 +166,11 @@ bool tm_cuda_tok_kv_download(int slot, size_t elem_off, float* dst, size_t n);
  * The reference declares woff_out as a C++ reference; a pointer is the same ABI. */
 int tm_cuda_tok_wbuf(const void* tensor_ptr, size_t bytes, const void* map_base, size_t map_size,
                      int zero_copy, uint64_t* woff_out);
+/* n tensors into one device buffer at 256-byte aligned offsets, one handle for all (no counterpart in the
+ * reference, whose unified memory aliases the file mapping): for tensors that lie at arbitrary offsets of a
+ * container file but must be row-aligned on the device and share a handle for segmented GEMVs. Afterwards
+ * tm_cuda_tok_wbuf(tensor_ptrs[i], ...) returns this handle and woff_out[i]. Returns the handle or -1. */
+int tm_cuda_tok_wbuf_pack(const void* const* tensor_ptrs, const size_t* bytes, unsigned n, uint64_t* woff_out);
 bool tm_cuda_tok_probe_copy(int srcslot, size_t src_off, int dstslot, unsigned n);   /* metal.h:3338-3351 */
 void tm_cuda_tok_gemv(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K);
 bool tm_cuda_tok_gemv_seg_supported(unsigned dtype);             /* metal.h:3513-3518 */

@@ -30,6 +30,8 @@ def load() -> C.CDLL:
         L.tmchain_chain_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.tmchain_chain_begin_sampled.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_uint, C.c_int]
         L.tmchain_chain_poll.argtypes = [C.c_void_p, C.c_int]
+        L.tmq_upload.argtypes = [C.c_char_p, C.POINTER(C.c_char_p), C.c_int, C.POINTER(C.c_ulonglong), C.POINTER(C.c_uint),
+                                 C.POINTER(C.c_ulonglong)]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         _lib = L
     return _lib
@@ -77,6 +79,19 @@ def init_peer(cuda_lib, rank: int, world: int, arena_bytes: int) -> None:
     raw = b"".join(bytes(t.cpu().tolist()) for t in every)
     if not cuda_lib.tm_cuda_peer_open(rank, world, (C.c_ubyte * len(raw)).from_buffer_copy(raw)):
         raise RuntimeError(cuda_lib.tm_cuda_last_error().decode())
+
+
+def tmq_upload(path: str, names: list[str]):
+    """Tensors of a .tmq container onto the GPU under one weight handle (include/tmq_reader.h). Returns
+    (handle, {name: (byte offset, dtype, nblocks)})."""
+    L = load()
+    n = len(names)
+    arr = (C.c_char_p * n)(*[s.encode() for s in names])
+    woff, dt, nb = (C.c_ulonglong * n)(), (C.c_uint * n)(), (C.c_ulonglong * n)()
+    wid = L.tmq_upload(path.encode(), arr, n, woff, dt, nb)
+    if wid < 0:
+        raise RuntimeError(L.tmchain_error().decode())
+    return wid, {names[i]: (int(woff[i]), int(dt[i]), int(nb[i])) for i in range(n)}
 
 
 class Chain:

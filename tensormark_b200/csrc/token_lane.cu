@@ -289,6 +289,33 @@ int tm_cuda_tok_wbuf(const void* tensor_ptr, size_t bytes, const void* map_base,
     return id;
 }
 
+// Several tensors into ONE device buffer, each at a 256-byte aligned offset: the tensors of a container file lie
+// at arbitrary byte offsets (records follow one another without padding), which a mirror of the mapping would
+// inherit, and the streaming GEMV wants 16-byte aligned rows. One handle for all of them keeps the segmented
+// launches (q|k|v, gate|up) possible. Returns the handle, fills woff_out[i]; -1 on failure. Tensors already
+// registered keep their old registration and are copied again under the new handle.
+int tm_cuda_tok_wbuf_pack(const void* const* tensor_ptrs, const size_t* bytes, unsigned n, uint64_t* woff_out) {
+    if (!ensure_init(-1) || !tensor_ptrs || !bytes || !woff_out || n == 0) { fail("tok_wbuf_pack: bad arguments"); return -1; }
+    State& s = state();
+    size_t total = 0;
+    for (unsigned i = 0; i < n; ++i) {
+        if (!tensor_ptrs[i] || !bytes[i]) { fail("tok_wbuf_pack: tensor %u is empty", i); return -1; }
+        woff_out[i] = total;
+        total += (bytes[i] + 32 + 255) / 256 * 256;          // 32 bytes of slack after every tensor, as for single tensors
+    }
+    uint8_t* d = nullptr;
+    if (cudaMalloc(&d, total) != cudaSuccess) { cudaGetLastError(); fail("tok_wbuf_pack: %zu bytes of device memory unavailable", total); return -1; }
+    cudaMemsetAsync(d, 0, total, s.stream);
+    for (unsigned i = 0; i < n; ++i)
+        if (cudaMemcpyAsync(d + woff_out[i], tensor_ptrs[i], bytes[i], cudaMemcpyHostToDevice, s.stream) != cudaSuccess) {
+            cudaStreamSynchronize(s.stream); cudaFree(d); check_launch("tok_wbuf_pack: upload"); return -1;
+        }
+    s.wbufs.push_back({d, total});
+    const int id = kFirstWeight + (int)s.wbufs.size() - 1;
+    for (unsigned i = 0; i < n; ++i) s.wreg[tensor_ptrs[i]] = {id, woff_out[i]};
+    return id;
+}
+
 bool tm_cuda_tok_probe_copy(int srcslot, size_t src_off, int dstslot, unsigned n) {
     if (!tm_cuda_tok_begin()) return false;
     State& s = state();

@@ -4,6 +4,7 @@
 // gives it a flat C surface so that programs without a C++ toolchain at hand (the Python tests
 // and the benchmark, through ctypes) can drive the same object. No arithmetic lives here.
 #include "llama_chain.h"
+#include "tmq_reader.h"
 
 #include <cstring>
 #include <memory>
@@ -103,4 +104,26 @@ TMCHAIN_API int tmchain_chain_end(void* p, int keep, int* out, int cap) {
 TMCHAIN_API int tmchain_feed(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_feed(toks, n); }
     catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+// ---- .tmq containers (include/tmq_reader.h) ---------------------------------------------------------------
+// Open a container, make the named tensors resident under one weight handle with aligned offsets, and keep the
+// mapping alive (registrations are keyed by addresses inside it). Returns the handle (>= 1000) or -1; fills, per
+// tensor, the byte offset inside the handle, the dtype and the number of blocks.
+TMCHAIN_API int tmq_upload(const char* path, const char* const* names, int n, unsigned long long* woff, unsigned* dtype,
+                           unsigned long long* nblocks) {
+    try {
+        static std::vector<std::unique_ptr<tmmq::Mapped>> keep;
+        auto m = std::make_unique<tmmq::Mapped>();
+        if (!m->open(path)) { g_err = std::string("tmq: cannot open or parse ") + path; return -1; }
+        std::vector<std::string> nm(names, names + n);
+        std::vector<std::uint64_t> off;
+        const int id = tmmq::upload_tensors(*m, nm, &off);
+        for (int i = 0; i < n; ++i) {
+            const tmmq::TensorInfo* t = m->find(nm[(size_t)i]);
+            woff[i] = off[(size_t)i]; dtype[i] = t->dtype; nblocks[i] = t->nblocks;
+        }
+        keep.push_back(std::move(m));
+        return id;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }

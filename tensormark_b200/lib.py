@@ -54,6 +54,7 @@ SIGNATURES = {
     "tm_cuda_tok_kv_upload": (C.c_bool, [C.c_int, _sz, _vp, _sz]),
     "tm_cuda_tok_kv_download": (C.c_bool, [C.c_int, _sz, _vp, _sz]),
     "tm_cuda_tok_wbuf": (C.c_int, [_vp, _sz, _vp, _sz, C.c_int, C.POINTER(_u64)]),
+    "tm_cuda_tok_wbuf_pack": (C.c_int, [C.POINTER(_vp), C.POINTER(_sz), _u, C.POINTER(_u64)]),
     "tm_cuda_tok_probe_copy": (C.c_bool, [C.c_int, _sz, C.c_int, _u]),
     "tm_cuda_tok_gemv": (None, [C.c_int, C.c_int, _u64, C.c_int, _sz, _u, _u]),
     "tm_cuda_tok_gemv_seg_supported": (C.c_bool, [_u]),

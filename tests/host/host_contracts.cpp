@@ -42,7 +42,26 @@ void pool_kernel(const tmllama::GemvArgs& a, int o0, int o1) {
 }
 }  // namespace
 
+#include "tmq_reader.h"
+
 extern "C" {
+// .tmq container: number of tensors of a file, or -1 when the reader rejects it
+__attribute__((visibility("default"))) int hc_tmq_count(const char* path) {
+    tmmq::Mapped m;
+    if (!m.open(path)) return -1;
+    return (int)m.tensors().size();
+}
+// one tensor by name: dtype, nblocks, payload offset in the file, rank and up to 4 dims; 0 when absent
+__attribute__((visibility("default"))) int hc_tmq_tensor(const char* path, const char* name, unsigned* dtype, unsigned long long* nblocks,
+                                                         unsigned long long* payload, unsigned* rank, unsigned* dims) {
+    tmmq::Mapped m;
+    if (!m.open(path)) return 0;
+    const tmmq::TensorInfo* t = m.find(name);
+    if (!t) return 0;
+    *dtype = t->dtype; *nblocks = t->nblocks; *payload = (unsigned long long)(t->blocks - m.base()); *rank = (unsigned)t->shape.size();
+    for (std::size_t i = 0; i < t->shape.size() && i < 4; ++i) dims[i] = t->shape[i];
+    return 1;
+}
 __attribute__((visibility("default"))) int hc_dequant(unsigned dtype, const void* blocks, float* out, std::size_t n) {
     try { tmq::dequantize_row(dtype, blocks, out, n); return 1; } catch (...) { return 0; }
 }

@@ -341,3 +341,42 @@ def test_fused_chain_attention_equals_the_separate_launches(cuda, dh, pos):
         lib.check(cuda.tm_cuda_tok_kv_download(a, 0, ka.ctypes.data, ka.size), "kv_download")
         lib.check(cuda.tm_cuda_tok_kv_download(b, 0, kb.ctypes.data, kb.size), "kv_download")
         assert np.array_equal(ka.view(np.uint32), kb.view(np.uint32))
+
+
+def test_tmq_container_to_lane(cuda, orc, tmp_path):
+    """A .tmq file (records without padding, so payloads at odd offsets) -> one aligned weight handle -> GEMVs,
+    single and segmented, equal to the oracle on the same bytes."""
+    import struct
+
+    from tensormark_b200 import chain as chain_mod
+    k = 2048
+    spec = [("blk.q", synth.Q4_0, 96), ("blk.k", synth.Q4_0, 32), ("blk.v", synth.Q4_0, 32), ("head", synth.Q6_K, 100)]
+    out = [b"TMQ1", struct.pack("<I", len(spec))]
+    Ws = {}
+    for i, (name, dt, n) in enumerate(spec):
+        W = synth.make_weights(dt, n, k, seed=300 + i)
+        Ws[name] = W
+        out += [struct.pack("<I", len(name)), name.encode(), struct.pack("<II", dt, 2), struct.pack("<II", n, k),
+                struct.pack("<Q", n * k // synth.BLOCK_ELEMS[dt]), W.tobytes()]
+    path = tmp_path / "model.tmq"
+    path.write_bytes(b"".join(out))
+    wid, info = chain_mod.tmq_upload(str(path), [s[0] for s in spec])
+    assert wid >= 1000 and all(off % 256 == 0 for off, _, _ in info.values())
+    x = synth.make_activations(k, seed=77)
+    up(cuda, X, x)
+    assert cuda.tm_cuda_tok_reserve(T1, 4 * 160)
+    assert cuda.tm_cuda_tok_begin()
+    offs = (C.c_uint64 * 3)(info["blk.q"][0], info["blk.k"][0], info["blk.v"][0])
+    rows = (C.c_uint * 3)(96, 32, 32)
+    cuda.tm_cuda_tok_gemv_seg_dt(X, wid, T1, 0, 160, k, synth.Q4_0, offs, rows, 3)
+    assert cuda.tm_cuda_tok_flush(), lib.last_error()
+    y = down(cuda, T1, 160)
+    want = np.concatenate([orc.gemv_f64(synth.Q4_0, Ws[n], x, Ws[n].shape[0], k)[0] for n in ("blk.q", "blk.k", "blk.v")])
+    wabs = np.concatenate([orc.gemv_f64(synth.Q4_0, Ws[n], x, Ws[n].shape[0], k)[1] for n in ("blk.q", "blk.k", "blk.v")])
+    assert np.all(np.abs(y - want) <= 1e-3 * wabs)
+    assert cuda.tm_cuda_tok_begin()
+    cuda.tm_cuda_tok_gemv_kq(X, wid, info["head"][0], T1, 0, 100, k, synth.Q6_K)
+    assert cuda.tm_cuda_tok_flush(), lib.last_error()
+    y = down(cuda, T1, 100)
+    want, wabs = orc.gemv_f64(synth.Q6_K, Ws["head"], x, 100, k)
+    assert np.all(np.abs(y - want) <= 1e-3 * wabs)

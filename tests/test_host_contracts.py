@@ -136,3 +136,55 @@ def test_c_abi_exports_every_declared_symbol():
     # pure host arithmetic works without a device
     assert L.tm_cuda_weight_bytes(1, 2048, 2048) == 2048 * 64 * 18
     assert L.tm_cuda_weight_bytes(6, 4, 100) == 0
+
+
+# ---- .tmq container reader (include/tmq_reader.h) ---------------------------------------------------------
+def _tmq_bytes(tensors) -> bytes:
+    """Serialize [(name, dtype, shape, payload bytes)] as the format tensormark/tmq.h:4-6 describes."""
+    import struct
+    out = [b"TMQ1", struct.pack("<I", len(tensors))]
+    for name, dt, shape, payload in tensors:
+        nb = name.encode()
+        n = int(np.prod(shape))
+        be = {0: 32, 1: 32, 2: 1, 3: 1, 4: 32, 5: 256, 6: 256, 7: 128, 8: 256}[dt]
+        out += [struct.pack("<I", len(nb)), nb, struct.pack("<II", dt, len(shape)),
+                struct.pack("<%dI" % len(shape), *shape), struct.pack("<Q", n // be), payload]
+    return b"".join(out)
+
+
+def test_tmq_reader_accepts_and_rejects(hc, tmp_path):
+    hc.hc_tmq_count.argtypes = [C.c_char_p]
+    hc.hc_tmq_tensor.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong),
+                                 C.POINTER(C.c_uint), C.POINTER(C.c_uint)]
+    w1 = synth.make_weights(synth.Q4_0, 6, 64, seed=1).tobytes()
+    w2 = synth.make_weights(synth.Q6_K, 3, 512, seed=2).tobytes()
+    f16 = np.arange(10, dtype=np.float16).tobytes()
+    good = _tmq_bytes([("layers.0.q", 1, (6, 64), w1), ("head", 6, (3, 512), w2), ("norm", 3, (10,), f16)])
+
+    def count(data: bytes) -> int:
+        p = tmp_path / "t.tmq"
+        p.write_bytes(data)
+        return hc.hc_tmq_count(str(p).encode())
+
+    assert count(good) == 3
+    dt, nb, off, rank = C.c_uint(), C.c_ulonglong(), C.c_ulonglong(), C.c_uint()
+    dims = (C.c_uint * 4)()
+    assert hc.hc_tmq_tensor(str(tmp_path / "t.tmq").encode(), b"head", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims)
+    assert (dt.value, nb.value, rank.value, dims[0], dims[1]) == (6, 6, 2, 3, 512)
+    assert good[off.value: off.value + len(w2)] == w2                 # the view points at the tensor's blocks
+    assert not hc.hc_tmq_tensor(str(tmp_path / "t.tmq").encode(), b"absent", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims)
+    # the reference parser's rejections (tensormark/tmq.h:157-161): trailing bytes, truncation, bad magic, unknown
+    # dtype, zero dimension, block count that does not match the shape, a count larger than the file can hold
+    assert count(good + b"\0") == -1
+    assert count(good[:-1]) == -1
+    assert count(b"TMQ2" + good[4:]) == -1
+    assert count(_tmq_bytes([("x", 8, (256,), b"\0" * 144)])) == -1   # Q4_K only comes from the GGUF-native reader
+    import struct
+    bad_dim = b"TMQ1" + struct.pack("<I", 1) + struct.pack("<I", 1) + b"x" + struct.pack("<II", 1, 2) + struct.pack("<II", 0, 32) + struct.pack("<Q", 0)
+    assert count(bad_dim) == -1
+    wrong_blocks = bytearray(_tmq_bytes([("x", 1, (2, 32), w1[:36])]))
+    i = wrong_blocks.index(struct.pack("<Q", 2))
+    wrong_blocks[i: i + 8] = struct.pack("<Q", 1)
+    assert count(bytes(wrong_blocks)) == -1
+    assert count(b"TMQ1" + struct.pack("<I", 1000)) == -1
+    assert count(b"TMQ1" + struct.pack("<I", 0)) == 0                 # an empty container is a valid one

@@ -202,11 +202,26 @@ bool tm_cuda_gemv_q(const float* x, const void* W, float* y, unsigned N, unsigne
     const uint8_t* dW = cached_weights(W, wb);
     if (!dW) return false;
     float* dx = (float*)s.io_x.get((size_t)K * 4);
-    float* dy = (float*)s.io_y.get((size_t)N * 4);
-    if (!dx || !dy) return fail("gemv: out of device memory");
+    if (!dx) return fail("gemv: out of device memory");
+    // A short y in page-locked host memory is written by the kernel itself (the device sees such memory): that saves
+    // the copy back and its DMA latency, a fifth of a small call. Long outputs keep the DMA, which moves them faster
+    // than row-by-row stores over PCIe.
+    float* dy = nullptr;
+    bool direct = false;
+    static const unsigned direct_rows = [] { const char* e = std::getenv("TM_DIRECT_Y_ROWS"); return e && *e ? (unsigned)std::atoi(e) : 8192u; }();
+    if (N <= direct_rows) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, y) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer) {
+            dy = (float*)at.devicePointer; direct = true;
+        } else {
+            cudaGetLastError();
+        }
+    }
+    if (!direct) dy = (float*)s.io_y.get((size_t)N * 4);
+    if (!dy) return fail("gemv: out of device memory");
     if (cudaMemcpyAsync(dx, x, (size_t)K * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("gemv: x upload");
     if (!launch_gemv(dx, dW, dy, N, K, dtype, one_segment(N), s.stream)) return false;
-    if (cudaMemcpyAsync(y, dy, (size_t)N * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("gemv: y download");
+    if (!direct && cudaMemcpyAsync(y, dy, (size_t)N * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("gemv: y download");
     return sync_stream(s.stream, "gemv");
 }
 

@@ -39,13 +39,16 @@ __device__ __forceinline__ void exchange_wait(const Exchange& xc, int* status) {
 }
 // Producer side, end of a CTA: every row this CTA computed has been stored here and on the peers by the
 // threads that computed it; after the barrier one thread adds this CTA to the rank's counter on every peer.
-// The reduction is a release at system scope, so a peer that sees the count sees the rows.
+// A system-scope fence before the (relaxed) reductions orders the rows before every count: a peer that sees the
+// count sees the rows. One fence for all peers, where a release per peer waited for the stores once per peer.
 __device__ __forceinline__ void exchange_signal(const Exchange& xc) {
     if (!xc.npush) return;
     __syncthreads();
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0) {
+        __threadfence_system();                                 // one wait for the rows on every peer, then the counts
         for (uint32_t q = 0; q < xc.npush; ++q)
-            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(xc.peer_ctr[q]) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(xc.peer_ctr[q]) : "memory");
+    }
 }
 
 }  // namespace tmc

@@ -251,20 +251,53 @@ TMO_API int tmo_gemv_f64(int dtype, const void* W, const float* x, double* y64, 
 
 /* ---- row-chunk pool (tensormark/gemv_pool.h:253-264, 296-315) -------------
  * The reference splits a GEMV into 64-row chunks claimed from an atomic counter
- * by the pool's threads, the caller included. Restated with one-shot pthreads. */
+ * by the pool's threads, the caller included; its workers are persistent: a job is
+ * published under a generation counter, the workers wake, claim chunks until none
+ * is left, and the caller (which claims chunks too) waits for the last one. Restated
+ * with pthreads: workers are created on first use and sleep on a condition variable
+ * between jobs. One job at a time (the reference's dispatch is single-caller too). */
 typedef struct {
     int dtype; const uint8_t* W; const float* x; float* y; int n_in, n_out, chunk;
     atomic_ulong next;
 } gemv_job;
 
-static void* gemv_worker(void* p) {
-    gemv_job* j = (gemv_job*)p;
+static void gemv_claim(gemv_job* j) {
     for (;;) {
         unsigned long start = atomic_fetch_add(&j->next, 1ul) * (unsigned long)j->chunk;
         if (start >= (unsigned long)j->n_out) break;
         unsigned long end = start + (unsigned long)j->chunk;
         if (end > (unsigned long)j->n_out) end = (unsigned long)j->n_out;
         gemv_rows(j->dtype, j->W, j->x, j->y, j->n_in, (int)start, (int)end);
+    }
+}
+
+#define TMO_POOL_MAX 256
+static struct {
+    pthread_mutex_t mu; pthread_cond_t wake, idle;
+    pthread_t th[TMO_POOL_MAX];
+    int nthreads;                 /* workers alive */
+    unsigned long generation;     /* bumped per job */
+    int want;                     /* workers asked to join the current job */
+    int joined, finished;         /* of the current job */
+    gemv_job* job;
+} g_pool = { PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER, PTHREAD_COND_INITIALIZER, {0}, 0, 0ul, 0, 0, 0, NULL };
+
+static void* pool_worker(void* arg) {
+    (void)arg;
+    unsigned long seen = 0;
+    pthread_mutex_lock(&g_pool.mu);
+    for (;;) {
+        while (g_pool.generation == seen || g_pool.joined >= g_pool.want) {
+            if (g_pool.generation != seen) seen = g_pool.generation;   /* job full: sit this one out */
+            pthread_cond_wait(&g_pool.wake, &g_pool.mu);
+        }
+        seen = g_pool.generation;
+        g_pool.joined++;
+        gemv_job* j = g_pool.job;
+        pthread_mutex_unlock(&g_pool.mu);
+        gemv_claim(j);
+        pthread_mutex_lock(&g_pool.mu);
+        if (++g_pool.finished == g_pool.want) pthread_cond_signal(&g_pool.idle);
     }
     return NULL;
 }
@@ -274,12 +307,24 @@ TMO_API int tmo_gemv_mt(int dtype, const void* W, const float* x, float* y, int 
     if (!be || n_in % be || threads < 1) return 0;
     gemv_job j = { dtype, (const uint8_t*)W, x, y, n_in, n_out, 64 };
     atomic_init(&j.next, 0ul);
-    pthread_t* t = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)threads);
-    int started = 0;
-    for (int i = 1; i < threads; i++) if (pthread_create(&t[started], NULL, gemv_worker, &j) == 0) started++;
-    gemv_worker(&j);
-    for (int i = 0; i < started; i++) pthread_join(t[i], NULL);
-    free(t);
+    int helpers = threads - 1;
+    if (helpers > TMO_POOL_MAX) helpers = TMO_POOL_MAX;
+    pthread_mutex_lock(&g_pool.mu);
+    while (g_pool.nthreads < helpers) {
+        if (pthread_create(&g_pool.th[g_pool.nthreads], NULL, pool_worker, NULL) != 0) break;
+        pthread_detach(g_pool.th[g_pool.nthreads]);
+        g_pool.nthreads++;
+    }
+    if (helpers > g_pool.nthreads) helpers = g_pool.nthreads;
+    g_pool.job = &j; g_pool.want = helpers; g_pool.joined = 0; g_pool.finished = 0;
+    g_pool.generation++;
+    if (helpers) pthread_cond_broadcast(&g_pool.wake);
+    pthread_mutex_unlock(&g_pool.mu);
+    gemv_claim(&j);                                     /* the caller works too */
+    pthread_mutex_lock(&g_pool.mu);
+    while (g_pool.finished < g_pool.want) pthread_cond_wait(&g_pool.idle, &g_pool.mu);
+    g_pool.job = NULL; g_pool.want = 0;
+    pthread_mutex_unlock(&g_pool.mu);
     return 1;
 }
 

@@ -33,6 +33,7 @@ def load() -> C.CDLL:
         L.tmq_upload.argtypes = [C.c_char_p, C.POINTER(C.c_char_p), C.c_int, C.POINTER(C.c_ulonglong), C.POINTER(C.c_uint),
                                  C.POINTER(C.c_ulonglong)]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+        L.tmchain_logits.argtypes = [C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
 
@@ -160,6 +161,12 @@ class Chain:
         got = self.L.tmchain_chain_end(self.h, keep, out.ctypes.data, n)
         self._check(got >= 0)
         return out[:got]
+
+    def logits(self) -> np.ndarray:
+        """Logits of the most recent forward or finished chain."""
+        out = np.empty(self.cfg["V"], np.float32)
+        self.L.tmchain_logits(self.h, out.ctypes.data)
+        return out
 
     def close(self):
         if self.h:

@@ -100,6 +100,12 @@ TMCHAIN_API int tmchain_chain_end(void* p, int keep, int* out, int cap) {
         return (int)t.size();
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
+// The logits of the most recent forward / finished chain (V floats).
+TMCHAIN_API int tmchain_logits(void* p, float* out) {
+    const std::vector<float>& l = static_cast<Holder*>(p)->m->logits();
+    std::memcpy(out, l.data(), l.size() * sizeof(float));
+    return (int)l.size();
+}
 // Feed a prompt token by token through the graph lane; returns the model's next token or -1.
 TMCHAIN_API int tmchain_feed(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_feed(toks, n); }

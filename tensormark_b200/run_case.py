@@ -27,6 +27,122 @@ def cfg_for(args) -> dict:
     return cfg
 
 
+def summarize_trace(L, per: int):
+    """Per-shape averages of the library's kernel timeline (TM_CUDA_TRACE=1 in the environment) over the last
+    tokens of the chain: for every GEMV the time from CTA start to the end of the wait for its predecessor, the
+    x phase, the row phase and start -> end; for the fused attention its phases. None when tracing is off."""
+    import collections
+    cap = 8192
+    buf = (C.c_ulonglong * (6 * cap))()
+    n = int(L.tm_cuda_trace_read(buf, cap))
+    if n == 0:
+        return None
+    a = np.frombuffer(buf, dtype=np.uint64)[: n * 6].reshape(n, 6).astype(np.int64)
+    a = a[np.argsort(a[:, 0])]
+    whole = n // per                                        # whole tokens in the log (it keeps the first 8192 launches)
+    if whole == 0:
+        return None
+    tail = a[per * max(0, whole - 4): per * whole]
+    agg = collections.defaultdict(lambda: [0, 0.0, 0.0, 0.0, 0.0])
+    for r in tail:
+        if r[5] >= r[0]:                                   # attention record: words 4 and 5 are timestamps
+            g = agg["attn_fused"]
+            g[0] += 1; g[1] += r[1] - r[0]; g[2] += r[2] - r[1]; g[3] += r[4] - r[2]; g[4] += r[5] - r[0]
+        else:
+            key = "gemv %dx%d dt%d xop%d" % (r[4] >> 32, r[4] & 0xffffffff, r[5] & 255, (r[5] >> 8) & 255)
+            g = agg[key]
+            g[0] += 1; g[1] += r[1] - r[0]; g[2] += r[2] - r[1]; g[3] += r[3] - r[2]; g[4] += r[3] - r[0]
+    span = (tail[-1, 3] - tail[0, 0]) / 1e3 / max(1, len(tail) // per)
+    return {"records": n, "launches_per_token": per, "token_span_us": round(float(span), 1),
+            "per_kernel_us": {k: {"n": g[0], "wait": round(g[1] / g[0] / 1e3, 2), "x": round(g[2] / g[0] / 1e3, 2),
+                                  "rows": round(g[3] / g[0] / 1e3, 2), "total": round(g[4] / g[0] / 1e3, 2)} for k, g in agg.items()}}
+
+
+def chain_weight_bytes(cfg: dict) -> int:
+    """Block bytes one token streams: every projection of every layer plus the LM head."""
+    QD, KVD = cfg["H"] * cfg["dh"], cfg["KVH"] * cfg["dh"]
+    per_layer = sum(synth.weight_bytes(cfg["dt_proj"], n, k) for n, k in
+                    ((QD, cfg["D"]), (KVD, cfg["D"]), (KVD, cfg["D"]), (cfg["D"], QD), (cfg["F"], cfg["D"]), (cfg["F"], cfg["D"]), (cfg["D"], cfg["F"])))
+    return cfg["L"] * per_layer + synth.weight_bytes(cfg["dt_head"], cfg["V"], cfg["D"])
+
+
+def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank: int = 0, world: int = 1, gather: str = "peer",
+                  dist=None, graph: bool = True, trace: bool = False) -> dict:
+    """Feed `prompt_n` tokens, then time `steps` greedy tokens chosen on the GPU (CUDA events on the lane stream, max over
+    ranks). world > 1: FFN and LM-head rows sharded over the ranks; the communicator (and, for gather == "peer", the peer
+    arena) must exist already and `dist` is the initialised torch.distributed module (any backend). Returns the record
+    every rank computes; "logits" (numpy) is the last step's logits of this rank."""
+    import hashlib
+    import time
+
+    from . import chain
+    cuda_group = dist is not None and dist.get_backend() == "nccl"
+
+    def reduce(t, op):
+        if cuda_group:
+            t = t.cuda()
+        dist.all_reduce(t, op=op)
+        return t.cpu()
+
+    m = chain.Chain(cfg, w, rank=rank, world=world, peer_gather=world > 1 and gather == "peer")
+    prompt = synth.make_tokens(prompt_n, cfg["V"], seed=5).astype(np.int32)
+    stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
+    t0 = time.perf_counter()
+    if not graph:
+        last = None
+        for t in prompt:
+            last = m.forward(int(t))
+        nxt = int(np.argmax(last))
+    else:
+        nxt = m.feed(prompt)
+    t_prompt = time.perf_counter() - t0
+    if dist is not None and world > 1:
+        dist.barrier()
+    if trace:                                               # drop the prompt's records: the log holds 8192 launches
+        L.tm_cuda_trace_read((C.c_ulonglong * (6 * 8192))(), 8192)
+    launches0 = int(L.tm_cuda_launch_count())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    t0 = time.perf_counter()
+    m.chain_begin(nxt, steps, graph=graph)
+    e1.record(stream)
+    toks = m.chain_end(steps)
+    wall = time.perf_counter() - t0
+    dev_ms = e0.elapsed_time(e1)
+    same = True
+    # The greedy trajectory of a random-init model can sit on one repeated token, so equal tokens say little:
+    # the last step's logits are compared across the ranks (and, by the caller, with the one-GPU run).
+    logits = m.logits()
+    logits_diff_ranks = 0.0
+    if dist is not None and world > 1:
+        dev_ms = float(reduce(torch.tensor([dev_ms], dtype=torch.float64), dist.ReduceOp.MAX).item())
+        mine = torch.tensor([int(x) for x in toks], dtype=torch.int64)
+        same = bool((reduce(mine.clone(), dist.ReduceOp.MIN) == reduce(mine.clone(), dist.ReduceOp.MAX)).all())
+        llo = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MIN)
+        lhi = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MAX)
+        logits_diff_ranks = float((lhi - llo).max())
+    tr = summarize_trace(L, 5 * cfg["L"] + 1) if trace and rank == 0 else None
+    wbytes = chain_weight_bytes(cfg)
+    rec = {"n_gpus": world,
+           "sharding": "none" if world == 1 else "FFN and LM-head rows over ranks, " +
+           ("rows stored into the peers' buffers by the GEMVs, flags" if gather == "peer" else "NCCL all-gather after each"),
+           "tokens_equal_on_all_ranks": same,
+           "lane": "CUDA graph per token" if graph else "host call per op",
+           "decode_tok_per_s": round(steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / steps, 4),
+           "wall_tok_per_s": round(steps / wall, 1),
+           "prompt_tok_per_s": round(prompt_n / t_prompt, 1),
+           "weight_bytes_per_token": wbytes,
+           "weight_GBps": round(wbytes * steps / (dev_ms * 1e-3) / 1e9, 1),
+           "kernels_encoded_per_chain_call": int(L.tm_cuda_launch_count()) - launches0,
+           "first_tokens": [int(t) for t in toks[:8]], "distinct_tokens": len({int(t) for t in toks}),
+           "last_logits_sha256": hashlib.sha256(logits.tobytes()).hexdigest()[:16],
+           "last_logits_max_abs": float(np.abs(logits).max()),
+           "last_logits_max_abs_diff_across_ranks": logits_diff_ranks,
+           "trace": tr, "logits": logits}
+    m.close()
+    return rec
+
+
 def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
     """Greedy decode chain of a random-init model: `--prompt` tokens fed one by one, then `--steps` chosen on the GPU.
     Under torch.distributed.run (world > 1) the FFN and LM-head rows are sharded over the ranks."""
@@ -44,57 +160,13 @@ def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
     t0 = time.perf_counter()
     w = synth.make_llama(cfg, seed=5)
     t_gen = time.perf_counter() - t0
-    m = chain.Chain(cfg, w, rank=rank, world=world, peer_gather=world > 1 and args.gather == "peer")
-    prompt = synth.make_tokens(args.prompt, cfg["V"], seed=5).astype(np.int32)
-    stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
-    t0 = time.perf_counter()
-    if args.no_graph:
-        last = None
-        for t in prompt:
-            last = m.forward(int(t))
-        nxt = int(np.argmax(last))
-    else:
-        nxt = m.feed(prompt)
-    t_prompt = time.perf_counter() - t0
-    if dist:
-        dist.barrier()
-    launches0 = int(L.tm_cuda_launch_count())
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    t0 = time.perf_counter()
-    m.chain_begin(nxt, args.steps, graph=not args.no_graph)
-    e1.record(stream)
-    toks = m.chain_end(args.steps)
-    wall = time.perf_counter() - t0
-    dev_ms = e0.elapsed_time(e1)
-    same = True
-    if dist:
-        t = torch.tensor([dev_ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms = float(t.item())
-        mine = torch.tensor([int(x) for x in toks], dtype=torch.int64)
-        lo, hi = mine.clone(), mine.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        same = bool((lo == hi).all())
-    QD, KVD = cfg["H"] * cfg["dh"], cfg["KVH"] * cfg["dh"]
-    per_layer = sum(synth.weight_bytes(cfg["dt_proj"], n, k) for n, k in
-                    ((QD, cfg["D"]), (KVD, cfg["D"]), (KVD, cfg["D"]), (cfg["D"], QD), (cfg["F"], cfg["D"]), (cfg["F"], cfg["D"]), (cfg["D"], cfg["F"])))
-    wbytes = cfg["L"] * per_layer + synth.weight_bytes(cfg["dt_head"], cfg["V"], cfg["D"])
+    rec = measure_chain(L, torch, cfg, w, args.prompt, args.steps, rank, world, args.gather, dist, not args.no_graph, args.trace)
+    logits = rec.pop("logits")
+    if args.dump_logits and rank == 0:
+        np.save(args.dump_logits, logits)
     if rank == 0:
-        print(json.dumps({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps, "n_gpus": world,
-                      "sharding": "none" if world == 1 else "FFN and LM-head rows over ranks, " +
-                      ("rows stored into the peers' buffers by the GEMVs, flags" if args.gather == "peer" else "NCCL all-gather after each"),
-                      "tokens_equal_on_all_ranks": same,
-                      "lane": "host call per op" if args.no_graph else "CUDA graph per token",
-                      "decode_tok_per_s": round(args.steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / args.steps, 4),
-                      "wall_tok_per_s": round(args.steps / wall, 1),
-                      "prompt_tok_per_s": round(args.prompt / t_prompt, 1),
-                      "weight_bytes_per_token": wbytes,
-                      "weight_GBps": round(wbytes * args.steps / (dev_ms * 1e-3) / 1e9, 1),
-                      "kernels_encoded_per_chain_call": int(L.tm_cuda_launch_count()) - launches0,
-                      "first_tokens": [int(t) for t in toks[:8]], "model_build_s": round(t_gen, 1)}), flush=True)
-    m.close()
+        print(json.dumps(dict({"op": "chain", "model": args.model, "prompt": args.prompt, "steps": args.steps}, **rec,
+                              model_build_s=round(t_gen, 1))), flush=True)
     if dist:
         dist.barrier()
         lib.check(L.tm_cuda_comm_destroy(), "tm_cuda_comm_destroy")
@@ -113,6 +185,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--gather", choices=["nccl", "peer"], default="peer", help="--op chain on several GPUs: how shards are gathered")
     ap.add_argument("--no-graph", action="store_true", help="--op chain: one host call per op instead of the graph lane")
+    ap.add_argument("--dump-logits", default="", help="--op chain: rank 0 saves the last step's logits to this .npy file")
+    ap.add_argument("--trace", action="store_true", help="--op chain with TM_CUDA_TRACE=1: add the per-kernel timeline summary")
     ap.add_argument("--dtype", default="Q8_0", choices=sorted(NAMES))
     ap.add_argument("--m", type=int, default=2000)
     ap.add_argument("--n", type=int, default=32000)

@@ -66,6 +66,13 @@ unsigned long long tm_cuda_launch_count(void);
 size_t tm_cuda_trace_read(unsigned long long* out, size_t cap_launches);
 /* Number of multiprocessors of the selected device. */
 int tm_cuda_sm_count(void);
+/* Limit, in milliseconds, of every device-side wait on another GPU (the peer gather's counters). Default 2000, or
+ * TM_CUDA_WAIT_LIMIT_MS at tm_cuda_init. A wait that runs out does not hang or fault: the kernel goes on, the next
+ * synchronising entry (tok_flush / tok_end / tok_wait_pending) returns false and tm_cuda_last_error() says that a
+ * kernel gave up on a bounded wait; later waits of the same token stream return at once until then. The analogue
+ * of the reference's 30 s deadline on its GPU/CPU hand-off (metal_llama.h:856-876). ms == 0 only reads.
+ * Returns the previous limit. Applies to launches encoded afterwards. */
+unsigned tm_cuda_set_wait_limit_ms(unsigned ms);
 
 /* ---- per-tensor projection, host pointers -------------------------------- */
 /* y[N] = W[N x K] . x[K], W Q4_0 blocks. Weights are cached on the device keyed
@@ -257,10 +264,11 @@ void tm_cuda_tok_all_gather(int srcslot, size_t src_off, int dstslot, size_t dst
 
 /* The same gather without a collective kernel: each rank's arena is mapped into every peer (CUDA
  * IPC) and the GEMV that produces a shard stores each finished row into the peers' copies of the
- * output slot over NVLink as well as its own; every CTA then adds 1 to the rank's counter of the
- * gather "site" on every peer (release at system scope). The kernel that consumes the gathered vector
- * waits until the other ranks' counters have reached epoch * CTAs-of-the-producer (bounded: 2 s, then
- * the status word reports it) before it reads.
+ * output slot over NVLink as well as its own; every CTA then (barrier, one system-scope fence that orders
+ * its rows before what follows) adds 1 to the rank's counter of the gather "site" on every peer with relaxed
+ * reductions. The kernel that consumes the gathered vector waits until the other ranks' counters have reached
+ * epoch * CTAs-of-the-producer (bounded: tm_cuda_set_wait_limit_ms, 2 s by default; then the status word
+ * reports it and a sticky abort word stops every later wait on every rank) before it reads.
  * Set-up on every rank: tm_cuda_peer_arena -> exchange the handles -> tm_cuda_peer_open ->
  * tm_cuda_tok_reserve_shared for the gathered slots, in the same order on every rank. A site is an
  * index < 256 naming one gather per token; the chain state's fourth int is the token epoch
@@ -268,6 +276,9 @@ void tm_cuda_tok_all_gather(int srcslot, size_t src_off, int dstslot, size_t dst
 size_t tm_cuda_peer_handle_bytes(void);
 bool tm_cuda_peer_arena(size_t bytes, void* handle_out);
 bool tm_cuda_peer_open(int rank, int world, const void* handles);
+/* Rehearsal on ONE GPU (tests): every peer arena is this GPU's own arena, so pushes land locally and the other
+ * ranks' counters never advance; a kernel that waits for them runs into the wait limit. */
+bool tm_cuda_peer_open_loopback(int rank, int world);
 int tm_cuda_peer_world(void);
 int tm_cuda_peer_rank(void);
 bool tm_cuda_peer_unmap(void);                                   /* then a barrier between the ranks, then: */

@@ -42,11 +42,14 @@ struct SegTable {                           // rows [row_end[s-1], row_end[s]) s
 
 // Peer-memory all-gather fused into the kernels of a row-sharded model (one process per GPU). A
 // producer stores each finished row of y into the same place of every peer's copy of the buffer as
-// well as its own; when a CTA is done it adds 1 to this rank's counter of the gather "site" in every
-// peer's memory (a release at system scope, so the rows are visible before the count). A consumer
-// waits until the site's counters of all other ranks have reached epoch * ctas, where ctas is the
-// producer's grid size, before it reads the gathered vector. Counters only grow, every wait is bounded
-// and reports through the status word.
+// well as its own; when a CTA is done (a barrier, then ONE system-scope fence, which orders the whole
+// CTA's row stores before what follows) it adds 1 to this rank's counter of the gather "site" in every
+// peer's memory with relaxed reductions. A consumer waits until the site's counters of all other ranks
+// have reached epoch * ctas, where ctas is the producer's grid size, before it reads the gathered
+// vector. Counters only grow and every wait is bounded (limit_ns). A wait that runs out sets the status
+// word and a sticky abort word in this rank's arena and in every peer's: every later wait, here and
+// there, returns at once instead of spending its own limit, so a stalled rank costs one limit, not one
+// per kernel. The host clears the abort word when it harvests the status.
 constexpr int kMaxPeers = 7;
 struct Exchange {
     const int* epoch;                       // device int; the current token's epoch is *epoch + 1
@@ -56,8 +59,21 @@ struct Exchange {
     uint32_t npush;                         // producer: number of peers (0 = no push)
     float* peer_y[kMaxPeers];               // producer: y as mapped from each peer
     unsigned* peer_ctr[kMaxPeers];          // producer: this rank's counter of the site in each peer's memory
+    unsigned long long limit_ns;            // consumer: how long one wait may last
+    int* abort_local;                       // sticky abort word of this rank's arena (nullptr: none)
+    int* abort_peer[kMaxPeers];             // the same word in each peer's arena
+    uint32_t npeers;
 };
 unsigned last_gemv_grid();                  // CTAs of the most recent GEMV launch of this process
+
+// x in the GEMV lanes' unit form, in global memory, written once per launch (xprep kernel) instead of once per CTA:
+// kXqHeaderWords words of header ([0] = the RMSNorm factor as a float, 1.0 without a norm), then the units of
+// Lane<dtype>. It pays where staging is heavy (SiLU*up over a long K); for K = 4096 the extra dependent kernel costs
+// what it saves, and a variant in which the producing GEMV's last CTA staged its own output was slower still (two
+// more dependent L2 round trips at the end of the producer): measured on the 8B decode chain, 2.24 / 2.03 / 1.94 ms
+// per token with tails + staging kernels / staging kernels everywhere / neither.
+constexpr int kXqHeaderWords = 16;
+size_t xq_bytes(unsigned K, unsigned dtype);            // size of such an image; 0 for an unknown format
 
 // ---- kernel launchers (one per .cu) -----------------------------------------
 struct GemvFuse {                           // optional fusions of the decode chain
@@ -66,7 +82,12 @@ struct GemvFuse {                           // optional fusions of the decode ch
     float eps;
     bool accumulate;                        // y[row] += dot instead of y[row] = dot
     const Exchange* xchg;                   // nullptr: single GPU
+    const uint32_t* xq;                     // x (after x_op) already in unit form for this dtype and K; the fp32 x is
+                                            // still passed: rows that are not 16-byte aligned take the plain kernel
 };
+// x (after x_op) in unit form for a GEMV of `dtype`; xchg: wait for a peer gather first.
+bool launch_xprep(uint32_t* out, const float* x, const float* x2, unsigned x_op, float eps, unsigned K, unsigned dtype,
+                  const Exchange* xchg, cudaStream_t st);
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
                  const SegTable& seg, cudaStream_t st, const GemvFuse* fuse = nullptr);
 bool launch_dequant(const uint8_t* W, float* out, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);

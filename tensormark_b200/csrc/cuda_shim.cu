@@ -90,6 +90,8 @@ bool ensure_init(int device) {
     }
     const char* v = std::getenv("TM_CUDA_VERBOSE");
     s.verbose = v && *v == '1';
+    const char* wl = std::getenv("TM_CUDA_WAIT_LIMIT_MS");
+    if (wl && *wl && std::atoll(wl) > 0) s.wait_limit_ns = (unsigned long long)std::atoll(wl) * 1000000ull;
     const char* kh = std::getenv("TM_CUDA_KV_HALF");
     s.kv_half = !(kh && *kh == '0');
     s.ready = true;
@@ -102,6 +104,8 @@ bool harvest_status(const char* where) {
     const int h = *s.status_host;                        // the caller has just synchronised with the kernels
     if (h != 0) {
         *s.status_host = 0;
+        // lower this rank's sticky abort word, so that the next token's waits are real waits again
+        if (s.peer.arena) cudaMemsetAsync((int*)s.peer.arena + kAbortWord, 0, sizeof(int), s.stream);
         return fail("%s: a kernel gave up on a bounded wait (status %d)", where, h);
     }
     return true;
@@ -170,6 +174,13 @@ const char* tm_cuda_last_error(void) { return state().last_error.c_str(); }
 unsigned long long tm_cuda_fallback_count(void) { return state().fallbacks; }
 unsigned long long tm_cuda_launch_count(void) { return state().launches; }
 int tm_cuda_sm_count(void) { return ensure_init(-1) ? state().sm_count : 0; }
+unsigned tm_cuda_set_wait_limit_ms(unsigned ms) {
+    if (!ensure_init(-1)) return 0;
+    State& s = state();
+    const unsigned before = (unsigned)(s.wait_limit_ns / 1000000ull);
+    if (ms) s.wait_limit_ns = (unsigned long long)ms * 1000000ull;
+    return before;
+}
 
 size_t tm_cuda_weight_bytes(unsigned dtype, size_t N, size_t K) { return weight_bytes(dtype, N, K); }
 
@@ -324,6 +335,7 @@ void tm_cuda_release_weights(void) {
     s.shared_base = nullptr; s.shared_id = -1;
     for (auto& kv : s.norm_w) cudaFree(kv.second);
     s.norm_w.clear();
+    s.x_prep.stamp = ~0ull;                               // the staged x image named norm weights that are gone
 }
 
 // ---- the reference's symbol names ----------------------------------------------

@@ -58,6 +58,10 @@ struct GemvParams {
     Exchange xc;                // row-sharded models: wait for peers before x, push y to peers after
     unsigned long long* trace;  // kernel timeline, nullptr when off
     int* status;
+    // x already in the lanes' unit form (written once per launch by xprep_kernel): the CTA bulk-copies the image
+    // instead of staging x itself. Layout: 16 header words ([0] = the RMSNorm
+    // factor as a float, 1.0 when none), then the units.
+    const uint32_t* xq;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -134,6 +138,144 @@ template <int DT> __device__ __forceinline__ int lane_valid(int lane, int units_
     }
 }
 
+
+// ---- staging of x: block floating point planes in the lanes' byte layout -------
+// Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and the run sums come from
+// three shuffle stages, the plane bytes leave as packed stores. A warp stages eight blocks (256 activations, one
+// "group") per pass; it takes groups g_first, g_first + g_step, ... below g_end. `units` is shared memory (a CTA
+// staging for itself) or global memory (staging once for every CTA of a later launch). Returns this lane's share
+// of sum(x^2) for x_op 1 (RMSNorm: x * w is staged, the factor rsqrt(mean(x^2) + eps) is one number for the whole
+// vector and multiplies the finished row sums instead); x_op 2 stages silu(x) * x2.
+template <int DT>
+__device__ __forceinline__ float stage_groups(uint32_t* units, const float* x, const float* x2, uint32_t x_op, uint32_t K,
+                                              uint32_t g_first, uint32_t g_end, uint32_t g_step, int lane) {
+    using L = Lane<DT>;
+    constexpr int B = 2;
+    const uint32_t nblk = K / 32, li = lane & 7u, sub = lane >> 3;
+    const float4* xg4 = reinterpret_cast<const float4*>(x);
+    const float4* x24 = reinterpret_cast<const float4*>(x2);
+    float ss = 0.f;
+    // The loads of the next group are issued before the current group is quantized: a warp's passes are
+    // otherwise a chain of L2 latencies.
+    float4 nv[B], nw[B];
+    auto fetch = [&](uint32_t g) {
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const uint32_t b = g * (4 * B) + 4 * j + sub;
+            const bool in = g < g_end && b < nblk;
+            nv[j] = in ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+            nw[j] = (in && x_op != 0u) ? __ldcg(x24 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    fetch(g_first);
+    for (uint32_t g = g_first; g < g_end; g += g_step) {
+        const uint32_t b0 = g * (4 * B);
+        float4 v[B];
+        float am[B], s8[B], s16[B], s32[B];
+        bool bad[B];
+        float4 w2s[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j) { v[j] = nv[j]; w2s[j] = nw[j]; }
+        fetch(g + g_step);
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const uint32_t b = b0 + 4 * j + sub;
+            if (x_op != 0u && b < nblk) {
+                const float4 w2 = w2s[j];
+                if (x_op == 1u) {
+                    ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+                    v[j].x *= w2.x; v[j].y *= w2.y; v[j].z *= w2.z; v[j].w *= w2.w;
+                } else {
+                    // silu(x) * up with the hardware exponential and reciprocal: relative error 2^-21, inside what the
+                    // fixed-point planes that follow keep
+                    v[j].x = __fdividef(v[j].x, 1.0f + __expf(-v[j].x)) * w2.x; v[j].y = __fdividef(v[j].y, 1.0f + __expf(-v[j].y)) * w2.y;
+                    v[j].z = __fdividef(v[j].z, 1.0f + __expf(-v[j].z)) * w2.z; v[j].w = __fdividef(v[j].w, 1.0f + __expf(-v[j].w)) * w2.w;
+                }
+            }
+            am[j] = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+            const float any_nan = (v[j].x + v[j].y) + (v[j].z + v[j].w);         // NaN if any element is NaN
+            bad[j] = !(am[j] <= 3.0e38f) || any_nan != any_nan;
+            s8[j] = (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        }
+#pragma unroll
+        for (int o = 1; o <= 4; o <<= 1)
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                am[j] = fmaxf(am[j], __shfl_xor_sync(0xffffffffu, am[j], o));
+                bad[j] = bad[j] || __shfl_xor_sync(0xffffffffu, (int)bad[j], o);
+            }
+        if (L::NEEDS_SUMS) {
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                s8[j] += __shfl_xor_sync(0xffffffffu, s8[j], 1);                  // 8 activations
+                s16[j] = s8[j] + __shfl_xor_sync(0xffffffffu, s8[j], 2);          // 16
+                s32[j] = s16[j] + __shfl_xor_sync(0xffffffffu, s16[j], 4);        // 32
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < B; ++j) s16[j] = s32[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const uint32_t b = b0 + 4 * j + sub;
+            if (b < nblk) {
+                float inv;
+                const float sc = block_scale(am[j], bad[j], inv);
+                int8_t q0[kPlanes], q1[kPlanes], q2[kPlanes], q3[kPlanes];
+                quantize_elem(v[j].x, inv, q0); quantize_elem(v[j].y, inv, q1);
+                quantize_elem(v[j].z, inv, q2); quantize_elem(v[j].w, inv, q3);
+#pragma unroll
+                for (int t = 0; t < kPlanes; ++t)
+                    L::store_quad(units, b * 32 + 4 * li, t,
+                                  (uint32_t)(uint8_t)q0[t] | ((uint32_t)(uint8_t)q1[t] << 8) |
+                                  ((uint32_t)(uint8_t)q2[t] << 16) | ((uint32_t)(uint8_t)q3[t] << 24));
+                L::scalars(units, b, (int)(4 * li), (int)li, sc, s8[j], s16[j], s32[j]);
+            }
+        }
+    }
+    return ss;
+}
+
+// One CTA stages the whole vector x (K activations) for a consumer of format CDT into `out` (global memory: 16 header
+// words, then the units), and writes the RMSNorm factor into out[0]. Warp w takes groups w, w + nwarps, ... so the
+// sum of squares is added in the same order as when a GEMV CTA stages x for itself.
+template <int CDT>
+__device__ __forceinline__ void stage_vector(uint32_t* out, const float* x, const float* x2, uint32_t x_op, float eps, uint32_t K, float* red) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const uint32_t ngroups = (K + 255u) / 256u;
+    float ss = stage_groups<CDT>(out + kXqHeaderWords, x, x2, x_op, K, (uint32_t)warp, ngroups, (uint32_t)nwarps, lane);
+    if (x_op == 1u) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.f;
+            for (int w = 0; w < nwarps; ++w) tot += red[w];
+            out[0] = __float_as_uint(1.0f / sqrtf(tot / (float)K + eps));
+        }
+    } else if (threadIdx.x == 0) {
+        out[0] = __float_as_uint(1.0f);
+    }
+}
+// x in unit form, once per launch. RMSNorm needs the
+// sum over the whole vector and runs as ONE CTA of 16 warps; the other transforms have no cross-group term and run
+// as many small CTAs as there are groups to cover.
+template <int CDT>
+__global__ void __launch_bounds__(512) xprep_kernel(uint32_t* out, const float* x, const float* x2, uint32_t x_op, float eps, uint32_t K,
+                                                    const Exchange xc, int* status) {
+    __shared__ float red[16];
+    // The GEMV that follows may become resident and prefetch its weights at once; it waits for this grid itself.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    exchange_wait(xc, status);
+    if (gridDim.x == 1) { stage_vector<CDT>(out, x, x2, x_op, eps, K, red); return; }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const uint32_t ngroups = (K + 255u) / 256u, g = blockIdx.x * nwarps + warp;
+    if (g < ngroups) (void)stage_groups<CDT>(out + kXqHeaderWords, x, x2, x_op, K, g, g + 1, 1u, lane);
+    if (blockIdx.x == 0 && threadIdx.x == 0) out[0] = __float_as_uint(1.0f);
+}
+
 // Shared memory: [x units: one per lane and step][mbarriers][stages]
 //
 // Work split: the rows are cut into one contiguous range per CTA (rows_per_cta =
@@ -207,105 +349,31 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     exchange_wait(p.xc, p.status);                          // sharded models: x is complete once every peer has pushed
     if (tr) tr[1] = global_ns();
 
-    // ---- stage x: block floating point planes in the lanes' byte layout -------
-    // Eight lanes per 32-block, four activations (one float4) per lane: the block maximum and
-    // the run sums come from three shuffle stages, the plane bytes leave as packed stores.
-    // A warp stages eight blocks (256 activations, one "group") per pass.
-    //
-    // Every CTA needs all of x, and staging it costs as much as streaming a few hundred KB of
-    // weights, so the CTAs of a cluster share the work: CTA r of C stages groups [r*gpc, (r+1)*gpc)
-    // into ITS shared memory, and after the cluster barrier every warp reads its unit from the CTA
-    // that staged it (distributed shared memory). A launch without clusters is the case C = 1.
+    // ---- x units into shared memory --------------------------------------------
+    // Either the image was written once for the whole launch (p.xq: one bulk copy per CTA), or this CTA stages x
+    // itself. Every CTA needs all of x, and staging it costs as much as streaming a few hundred KB of weights, so the
+    // CTAs of a cluster share the work: CTA r of C stages groups [r*gpc, (r+1)*gpc) into ITS shared memory, and after
+    // the cluster barrier every warp reads its unit from the CTA that staged it (distributed shared memory). A launch
+    // without clusters is the case C = 1.
     const uint32_t ngroups = (p.K + 255u) / 256u, gpc = (ngroups + csize - 1) / csize;
     const uint32_t g_lo = min(ngroups, crank * gpc), g_hi = min(ngroups, g_lo + gpc);
     __shared__ float xsum[8];                               // RMSNorm: one partial sum of squares per CTA of the cluster
     __shared__ float red[kWarps];
-    {
-        constexpr int B = 2;
-        const uint32_t nblk = p.K / 32, li = lane & 7u, sub = lane >> 3;
-        const float4* xg4 = reinterpret_cast<const float4*>(p.x);
-        const float4* x24 = reinterpret_cast<const float4*>(p.x2);
-        float ss = 0.f;
-        // The loads of the next group are issued before the current group is quantized: a warp's passes are
-        // otherwise a chain of L2 latencies.
-        float4 nv[B], nw[B];
-        auto fetch = [&](uint32_t g) {
-#pragma unroll
-            for (int j = 0; j < B; ++j) {
-                const uint32_t b = g * (4 * B) + 4 * j + sub;
-                const bool in = g < g_hi && b < nblk;
-                nv[j] = in ? __ldcg(xg4 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
-                nw[j] = (in && p.x_op != 0u) ? __ldcg(x24 + b * 8 + li) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        };
-        fetch(g_lo + warp);
-        for (uint32_t g = g_lo + warp; g < g_hi; g += kWarps) {
-            const uint32_t b0 = g * (4 * B);
-            float4 v[B];
-            float am[B], s8[B], s16[B], s32[B];
-            bool bad[B];
-            float4 w2s[B];
-#pragma unroll
-            for (int j = 0; j < B; ++j) { v[j] = nv[j]; w2s[j] = nw[j]; }
-            fetch(g + kWarps);
-#pragma unroll
-            for (int j = 0; j < B; ++j) {
-                const uint32_t b = b0 + 4 * j + sub;
-                if (p.x_op != 0u && b < nblk) {
-                    const float4 w2 = w2s[j];
-                    if (p.x_op == 1u) {
-                        // RMSNorm: x * w is staged; the factor rsqrt(mean(x^2) + eps) is one number for the whole
-                        // vector and multiplies the finished row sums instead
-                        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss); ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
-                        v[j].x *= w2.x; v[j].y *= w2.y; v[j].z *= w2.z; v[j].w *= w2.w;
-                    } else {
-                        // silu(x) * up with the hardware exponential and reciprocal: relative error 2^-21, far inside
-                        // what the three-plane quantization that follows keeps
-                        v[j].x = __fdividef(v[j].x, 1.0f + __expf(-v[j].x)) * w2.x; v[j].y = __fdividef(v[j].y, 1.0f + __expf(-v[j].y)) * w2.y;
-                        v[j].z = __fdividef(v[j].z, 1.0f + __expf(-v[j].z)) * w2.z; v[j].w = __fdividef(v[j].w, 1.0f + __expf(-v[j].w)) * w2.w;
-                    }
-                }
-                am[j] = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
-                const float any_nan = (v[j].x + v[j].y) + (v[j].z + v[j].w);         // NaN if any element is NaN
-                bad[j] = !(am[j] <= 3.0e38f) || any_nan != any_nan;
-                s8[j] = (v[j].x + v[j].y) + (v[j].z + v[j].w);
-            }
-#pragma unroll
-            for (int o = 1; o <= 4; o <<= 1)
-#pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    am[j] = fmaxf(am[j], __shfl_xor_sync(0xffffffffu, am[j], o));
-                    bad[j] = bad[j] || __shfl_xor_sync(0xffffffffu, (int)bad[j], o);
-                }
-            if (L::NEEDS_SUMS) {
-#pragma unroll
-                for (int j = 0; j < B; ++j) {
-                    s8[j] += __shfl_xor_sync(0xffffffffu, s8[j], 1);                  // 8 activations
-                    s16[j] = s8[j] + __shfl_xor_sync(0xffffffffu, s8[j], 2);          // 16
-                    s32[j] = s16[j] + __shfl_xor_sync(0xffffffffu, s16[j], 4);        // 32
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < B; ++j) s16[j] = s32[j] = 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < B; ++j) {
-                const uint32_t b = b0 + 4 * j + sub;
-                if (b < nblk) {
-                    float inv;
-                    const float sc = block_scale(am[j], bad[j], inv);
-                    int8_t q0[kPlanes], q1[kPlanes], q2[kPlanes], q3[kPlanes];
-                    quantize_elem(v[j].x, inv, q0); quantize_elem(v[j].y, inv, q1);
-                    quantize_elem(v[j].z, inv, q2); quantize_elem(v[j].w, inv, q3);
-#pragma unroll
-                    for (int t = 0; t < kPlanes; ++t)
-                        L::store_quad(units, b * 32 + 4 * li, t,
-                                      (uint32_t)(uint8_t)q0[t] | ((uint32_t)(uint8_t)q1[t] << 8) |
-                                      ((uint32_t)(uint8_t)q2[t] << 16) | ((uint32_t)(uint8_t)q3[t] << 24));
-                    L::scalars(units, b, (int)(4 * li), (int)li, sc, s8[j], s16[j], s32[j]);
-                }
-            }
+    __shared__ __align__(8) uint64_t xbar;
+    float xq_norm = 1.f;
+    if (p.xq) {
+        const uint32_t xbytes = nunits * (uint32_t)L::XW * 4u;
+        if (threadIdx.x == 0) {
+            mbar_init(&xbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            mbar_expect_tx(&xbar, xbytes);
+            bulk_g2s(units, p.xq + kXqHeaderWords, xbytes, &xbar);
+            xq_norm = __uint_as_float(__ldcg(p.xq));
+            if (!mbar_wait(&xbar, 0)) *(volatile int*)p.status = 1;
+            red[0] = xq_norm;
         }
+    } else {
+        float ss = stage_groups<DT>(units, p.x, p.x2, p.x_op, p.K, g_lo + (uint32_t)warp, g_hi, (uint32_t)kWarps, lane);
         if (p.x_op == 1u) {
             // this CTA's share of sum(x^2), handed to every CTA of the cluster below
 #pragma unroll
@@ -330,7 +398,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         __syncthreads();                                    // x units and the warps' partial sums of squares are in place
     }
     float norm_inv = 1.f;
-    if (p.x_op == 1u) {
+    if (p.xq) {
+        norm_inv = red[0];                                  // written with the units by whoever staged them
+    } else if (p.x_op == 1u) {
         // every thread adds the partial sums itself (broadcast reads, fixed order): no second barrier
         float tot = 0.f;
         if (csize > 1) {
@@ -681,7 +751,7 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
         // but the time from staged x to the last row grew by 6 us). TM_GEMV_CLUSTER=2 or 4 turns them on.
         static const int force_c = env_int("TM_GEMV_CLUSTER", 1);
         unsigned cluster = 1u;
-        if (force_c == 2 || force_c == 4) cluster = (unsigned)force_c;
+        if ((force_c == 2 || force_c == 4) && !p.xq) cluster = (unsigned)force_c;
         unsigned sms_c = sms;
         while (cluster > 1) {
             sms_c = warps_cta == 16 ? cluster_sms<DT, 16>(cluster, sms) : cluster_sms<DT, 8>(cluster, sms);
@@ -731,6 +801,7 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
             }
         }
     }
+    p.xq = nullptr;                                         // the plain kernel reads the fp32 x
     const unsigned rows_per_cta = 8;
     const size_t xsmem = p.x_op ? (size_t)p.K * 4 : 0;
     if (xsmem > 48 * 1024) {
@@ -746,6 +817,16 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
     return check_launch("gemv_generic");
 }
 
+bool launch_any(const GemvParams& p, unsigned dtype, bool aligned, cudaStream_t st) {
+    switch (dtype) {
+        case DT_Q8_0: return launch_dt<0>(p, aligned, st);
+        case DT_Q4_0: return launch_dt<1>(p, aligned, st);
+        case DT_Q4_1: return launch_dt<4>(p, aligned, st);
+        case DT_Q5_K: return launch_dt<5>(p, aligned, st);
+        case DT_Q4_K: return launch_dt<8>(p, aligned, st);
+        default: return launch_dt<6>(p, aligned, st);
+    }
+}
 }  // namespace
 
 unsigned last_gemv_grid() { return g_last_grid; }
@@ -766,22 +847,69 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     p.seg = seg; p.status = device_status_word(); p.trace = device_trace();
     p.x2 = nullptr; p.eps = 0.f; p.x_op = 0; p.accumulate = 0;
     p.xc = Exchange{};
+    p.xq = nullptr;
     if (fuse && fuse->xchg) p.xc = *fuse->xchg;
     if (p.xc.npush > (unsigned)kMaxPeers || (p.xc.nwait && (!p.xc.wait_ctrs || !p.xc.wait_ctas || !p.xc.epoch)))
         return fail("gemv: incomplete peer exchange description");
     if (fuse) {
         if (fuse->x_op > 2 || (fuse->x_op != 0 && (!fuse->x2 || (uintptr_t)fuse->x2 % 16))) return fail("gemv: bad fused x transform");
         p.x2 = fuse->x2; p.eps = fuse->eps; p.x_op = fuse->x_op; p.accumulate = fuse->accumulate ? 1u : 0u;
+        if (fuse->xq) {
+            if ((uintptr_t)fuse->xq % 16) return fail("gemv: the staged x image must be 16-byte aligned");
+            p.xq = fuse->xq;
+        }
     }
     bool aligned = ((uintptr_t)W % 16 == 0) && (p.row_bytes % 16 == 0);
     for (unsigned s = 0; s < seg.nseg; ++s) aligned = aligned && (seg.woff[s] % 16 == 0);
+    return launch_any(p, dtype, aligned, st);
+}
+
+size_t xq_bytes(unsigned K, unsigned dtype) {
+    auto sz = [&](unsigned step_w, unsigned xw) { return (size_t)kXqHeaderWords * 4 + (size_t)((K + step_w - 1) / step_w) * 32u * xw * 4u; };
     switch (dtype) {
-        case DT_Q8_0: return launch_dt<0>(p, aligned, st);
-        case DT_Q4_0: return launch_dt<1>(p, aligned, st);
-        case DT_Q4_1: return launch_dt<4>(p, aligned, st);
-        case DT_Q5_K: return launch_dt<5>(p, aligned, st);
-        case DT_Q4_K: return launch_dt<8>(p, aligned, st);
-        default: return launch_dt<6>(p, aligned, st);
+        case DT_Q8_0: return sz(Lane<0>::STEP_W, Lane<0>::XW);
+        case DT_Q4_0: return sz(Lane<1>::STEP_W, Lane<1>::XW);
+        case DT_Q4_1: return sz(Lane<4>::STEP_W, Lane<4>::XW);
+        case DT_Q5_K: return sz(Lane<5>::STEP_W, Lane<5>::XW);
+        case DT_Q4_K: return sz(Lane<8>::STEP_W, Lane<8>::XW);
+        case DT_Q6_K: return sz(Lane<6>::STEP_W, Lane<6>::XW);
+        default: return 0;
+    }
+}
+
+namespace {
+template <int CDT>
+bool launch_xprep_dt(uint32_t* out, const float* x, const float* x2, unsigned x_op, float eps, unsigned K, const Exchange& xc, cudaStream_t st) {
+    const unsigned ngroups = (K + 255u) / 256u;
+    // RMSNorm sums over the whole vector: one CTA of 16 warps. Otherwise four groups per CTA.
+    const unsigned threads = x_op == 1u ? 512u : 128u, grid = x_op == 1u ? 1u : (ngroups + 3u) / 4u;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, xprep_kernel<CDT>, out, x, x2, (uint32_t)x_op, eps, (uint32_t)K, xc, device_status_word()) != cudaSuccess)
+        return check_launch("xprep");
+    note_launch();
+    return true;
+}
+}  // namespace
+
+bool launch_xprep(uint32_t* out, const float* x, const float* x2, unsigned x_op, float eps, unsigned K, unsigned dtype,
+                  const Exchange* xchg, cudaStream_t st) {
+    if (!out || !x || (uintptr_t)out % 16 || (uintptr_t)x % 16 || x_op > 2 || (x_op && (!x2 || (uintptr_t)x2 % 16)))
+        return fail("xprep: bad arguments");
+    const unsigned be = block_elems(dtype);
+    if (!be || dtype == DT_F16 || K == 0 || K % be) return fail("xprep: K=%u is not whole blocks of dtype %u", K, dtype);
+    const Exchange xc = xchg ? *xchg : Exchange{};
+    switch (dtype) {
+        case DT_Q8_0: return launch_xprep_dt<0>(out, x, x2, x_op, eps, K, xc, st);
+        case DT_Q4_0: return launch_xprep_dt<1>(out, x, x2, x_op, eps, K, xc, st);
+        case DT_Q4_1: return launch_xprep_dt<4>(out, x, x2, x_op, eps, K, xc, st);
+        case DT_Q5_K: return launch_xprep_dt<5>(out, x, x2, x_op, eps, K, xc, st);
+        case DT_Q4_K: return launch_xprep_dt<8>(out, x, x2, x_op, eps, K, xc, st);
+        default: return launch_xprep_dt<6>(out, x, x2, x_op, eps, K, xc, st);
     }
 }
 

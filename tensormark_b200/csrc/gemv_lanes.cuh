@@ -9,16 +9,19 @@
 //
 // Arithmetic. The integer codes of a block are never converted one by one. The
 // activations of every 32-block are re-expressed once per kernel as block floating
-// point: a scale s = max|x|/127 and three signed 8-bit planes with
-//     x[i] ~= s * (a1[i] + a2[i]/128 + a3[i]/16384),   error <= 2^-22 * max|x|,
-// which is the precision of an fp32 product chain. A block's dot product is then
-// three exact integer dot products sum(code * a_t) on the dp4a unit (four
+// point: a scale s = max|x|/127 and kPlanes signed 8-bit planes with
+//     x[i] ~= s * (a1[i] + a2[i]/128 [+ a3[i]/16384]),
+// error <= 2^-15 * max|x| per activation with two planes (the default: 3.1e-5 of the block maximum, which for
+// activations of one scale is below 1e-4 * sum|w x| even if every rounding error lined up with the sign of its
+// weight, an order inside the 1e-3 contract; measured ~2e-6), <= 2^-22 * max|x| with three (TM_GEMV_PLANES=3
+// at build time: the precision of an fp32 product chain, at 1.5x the integer work). A block's dot product is then
+// kPlanes exact integer dot products sum(code * a_t) on the dp4a unit (four
 // multiply-adds per instruction, the code bytes used as they lie in the block),
 // combined in fp32, multiplied by the fp16 block scale and added to the row's fp32
 // accumulator: exact within a block, fp32 across blocks, like the reference's
 // per-block partial sums (tensormark/llama.h:1877-1895). Zero points and mins are
 // applied with the true fp32 sums of x, so nothing depends on the planes' rounding
-// beyond the 2^-22 above. NaN or infinite activations poison the block scale and
+// beyond the bound above. NaN or infinite activations poison the block scale and
 // therefore the output, as a floating-point chain would.
 //
 // The x planes are laid out to mirror the BYTE positions of the weight block a lane
@@ -51,7 +54,11 @@ struct uint4 { unsigned x, y, z, w; };
 
 namespace tmc {
 
-constexpr int kPlanes = 3;
+#ifndef TM_GEMV_PLANES
+#define TM_GEMV_PLANES 2
+#endif
+constexpr int kPlanes = TM_GEMV_PLANES;
+static_assert(kPlanes == 2 || kPlanes == 3, "two or three int8 planes");
 
 // ---- primitives with host emulation ----------------------------------------
 TM_HD float as_float(uint32_t u) {
@@ -127,7 +134,7 @@ TM_HD int round_int(float v) {
     return (int)lrintf(v);
 #endif
 }
-// S1 + S2/128 + S3/16384 in fp32 (each S_t is an exact integer below 2^24)
+// S1 + S2/128 [+ S3/16384] in fp32 (each S_t is an exact integer below 2^24)
 TM_HD float planes_to_float(const int* S) {
     float f = (float)S[0];
     if (kPlanes > 1) f = fma1((float)S[1], 1.0f / 128.0f, f);
@@ -179,21 +186,27 @@ TM_HD float block_scale(float amax, bool bad, float& inv) {
     return amax * (1.0f / 127.0f);                          // s * inv == 1 to within 2^-23, far below the plane truncation
 }
 // The kPlanes signed bytes of one activation under its block's inverse scale: the activation is rounded once to a
-// multiple of s / 16384 (X = round(v / s * 16384), |X| <= 127 * 16384) and X is split into three signed digits,
-// X = a1 * 16384 + a2 * 128 + a3 with a1 in [-127, 127], a2 in [-64, 64], a3 in [-64, 63]. Integer arithmetic after
-// one rounding, which on the GPU is the add of 1.5 * 2^23 (the integer lands in the low mantissa bits).
+// multiple of s / 128^(kPlanes-1) (X = round(v / s * 128^(kPlanes-1))) and X is split into signed digits base 128,
+// X = a1 * 16384 + a2 * 128 + a3 (three planes) or a1 * 128 + a2 (two), a1 in [-127, 127], the others in [-64, 64].
+// Integer arithmetic after one rounding, which on the GPU is the add of 1.5 * 2^23 (the integer lands in the low
+// mantissa bits).
 TM_HD void quantize_elem(float v, float inv, int8_t* a) {
-    static_assert(kPlanes == 3, "the digit split below is written for three planes");
     float r = inv == 0.f ? 0.f : v * inv;                   // inv is 0 for empty and for poisoned blocks
     r = r > 127.f ? 127.f : (r < -127.f ? -127.f : r);
+    constexpr float kUnit = kPlanes == 3 ? 16384.0f : 128.0f;
 #if defined(__CUDA_ARCH__)
-    const int X = __float_as_int(__fadd_rn(r * 16384.0f, 12582912.0f)) - 0x4B400000;
+    const int X = __float_as_int(__fadd_rn(r * kUnit, 12582912.0f)) - 0x4B400000;
 #else
-    const int X = (int)lrintf(r * 16384.0f);
+    const int X = (int)lrintf(r * kUnit);
 #endif
-    const int a1 = (X + 8192) >> 14, r1 = X - a1 * 16384;
-    const int a2 = (r1 + 64) >> 7, a3 = r1 - a2 * 128;
-    a[0] = (int8_t)a1; a[1] = (int8_t)a2; a[2] = (int8_t)a3;
+    if (kPlanes == 3) {
+        const int a1 = (X + 8192) >> 14, r1 = X - a1 * 16384;
+        const int a2 = (r1 + 64) >> 7, a3 = r1 - a2 * 128;
+        a[0] = (int8_t)a1; a[1] = (int8_t)a2; a[kPlanes - 1] = (int8_t)a3;
+    } else {
+        const int a1 = (X + 64) >> 7, a2 = X - a1 * 128;
+        a[0] = (int8_t)a1; a[1] = (int8_t)a2;
+    }
 }
 
 // two zero bytes at an even byte offset of the x-unit area
@@ -211,10 +224,11 @@ template <int DT> struct Lane;
 // ---- Q8_0: 34-byte blocks [d:2][q:32], w = q * d --------------------------------
 // Lane bytes: 68 = 17 words. Block A's codes sit at unit bytes 2..33, block B's at
 // 36..67 (its scale at 34..35). x unit: plane t words [17t, 17t+17) mirror those byte
-// positions (zeros under the scale bytes); [51] = sA, [52] = sB.
+// positions (zeros under the scale bytes); [17 P] = sA, [17 P + 1] = sB (P = kPlanes).
 template <> struct Lane<0> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 2176, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 68;
-    static constexpr int XW = 60;                           // words per x unit; this stride is bank-conflict free for 16-byte loads
+    static constexpr int SC = 17 * kPlanes;                 // first scalar word
+    static constexpr int XW = kPlanes == 3 ? 60 : 36;       // words per x unit; an odd multiple of 4, so 16-byte loads of 8 lanes hit 8 bank groups
     static constexpr bool NEEDS_SUMS = false;               // no zero point, no min: the plain sums of x are not used
     struct X { uint32_t w[XW]; };
 
@@ -233,7 +247,7 @@ template <> struct Lane<0> {
     // start there), `zl` = the caller's index 0..7 among the threads staging this block
     static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
         (void)s8; (void)s16; (void)s32;
-        if (lane == 0) units[(b >> 1) * XW + 51 + (b & 1u)] = as_uint(s);
+        if (lane == 0) units[(b >> 1) * XW + SC + (b & 1u)] = as_uint(s);
         // the two bytes of every plane image that lie under this block's fp16 scale must read as zero
         if (zl < kPlanes) zero2(units, (b >> 1) * (XW * 4u) + 68u * (uint32_t)zl + ((b & 1u) ? 34u : 0u));
     }
@@ -252,8 +266,8 @@ template <> struct Lane<0> {
             for (int i = 9; i < 17; ++i) b = dp4a_ss(w[i], x.w[17 * t + i], b);
             SA[t] = a; SB[t] = b;
         }
-        float acc = half_to_float(w[0] & 0xffffu) * (as_float(x.w[51]) * planes_to_float(SA));
-        if (nvalid > 1) acc = fma1(half_to_float(w[8] >> 16), as_float(x.w[52]) * planes_to_float(SB), acc);
+        float acc = half_to_float(w[0] & 0xffffu) * (as_float(x.w[SC]) * planes_to_float(SA));
+        if (nvalid > 1) acc = fma1(half_to_float(w[8] >> 16), as_float(x.w[SC + 1]) * planes_to_float(SB), acc);
         return acc;
     }
 };
@@ -261,10 +275,11 @@ template <> struct Lane<0> {
 // ---- Q4_0: 18-byte blocks [d:2][qs:16], byte j = elements 2j (low) | 2j+1 (high), w = (n-8)*d
 // Lane bytes: 36 = 9 words. x unit: per plane t an "even" 9-word image (element 2j under
 // byte j) at [18t, 18t+9) and an "odd" image (element 2j+1) at [18t+9, 18t+18);
-// [54] = sA, [55] = sB, [56] = sum(xA), [57] = sum(xB).
+// [18 P] = sA, [18 P + 1] = sB, [18 P + 2] = sum(xA), [18 P + 3] = sum(xB) (P = kPlanes).
 template <> struct Lane<1> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 1152, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 36;
-    static constexpr int XW = 60;
+    static constexpr int SC = 18 * kPlanes;
+    static constexpr int XW = kPlanes == 3 ? 60 : 44;
     static constexpr bool NEEDS_SUMS = true;
     struct X { uint32_t w[XW]; };
 
@@ -279,7 +294,7 @@ template <> struct Lane<1> {
     }
     static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
         (void)s8; (void)s16;
-        if (lane == 0) { units[(b >> 1) * XW + 54 + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + 56 + (b & 1u)] = as_uint(s32); }
+        if (lane == 0) { units[(b >> 1) * XW + SC + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + SC + 2 + (b & 1u)] = as_uint(s32); }
         // zero the bytes under this block's fp16 scale in the even and odd image of every plane
         if (zl < 2 * kPlanes) zero2(units, (b >> 1) * (XW * 4u) + 36u * (uint32_t)zl + ((b & 1u) ? 18u : 0u));
     }
@@ -305,26 +320,27 @@ template <> struct Lane<1> {
             SA[t] = al + (ah >> 4);
             SB[t] = bl + (bh >> 4);
         }
-        float acc = half_to_float(w0 & 0xffffu) * fma1(as_float(x.w[54]), planes_to_float(SA), -8.f * as_float(x.w[56]));
+        float acc = half_to_float(w0 & 0xffffu) * fma1(as_float(x.w[SC]), planes_to_float(SA), -8.f * as_float(x.w[SC + 2]));
         if (nvalid > 1)
-            acc = fma1(half_to_float(w4 >> 16), fma1(as_float(x.w[55]), planes_to_float(SB), -8.f * as_float(x.w[57])), acc);
+            acc = fma1(half_to_float(w4 >> 16), fma1(as_float(x.w[SC + 1]), planes_to_float(SB), -8.f * as_float(x.w[SC + 3])), acc);
         return acc;
     }
 };
 
 // ---- Q4_1: 20-byte blocks [d:2][m:2][qs:16], byte j = elements j (low) | j+16 (high), w = n*d + m
 // Lane bytes: 40 = 10 words. x unit: per block b and plane t a "low" 4-word image at
-// [24b + 8t, +4) and a "high" image at [24b + 8t + 4, +4); [48] = sA, [49] = sB,
-// [50] = sum(xA), [51] = sum(xB).
+// [8P b + 8t, +4) and a "high" image at [8P b + 8t + 4, +4); [16 P] = sA, [16 P + 1] = sB,
+// [16 P + 2] = sum(xA), [16 P + 3] = sum(xB) (P = kPlanes).
 template <> struct Lane<4> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 1280, UNIT_W = 32, LANE_UNITS = 2, LANE_BYTES = 40;
-    static constexpr int XW = 52;
+    static constexpr int BW = 8 * kPlanes, SC = 16 * kPlanes;
+    static constexpr int XW = kPlanes == 3 ? 52 : 36;
     static constexpr bool NEEDS_SUMS = true;
     struct X { uint32_t w[XW]; };
 
     static TM_HD uint32_t plane_byte(uint32_t e, int t) {
         const uint32_t b = e >> 5, i = e & 31u;
-        return (b >> 1) * (XW * 4u) + 4u * (24u * (b & 1u) + 8u * (uint32_t)t + 4u * (i >> 4)) + (i & 15u);
+        return (b >> 1) * (XW * 4u) + 4u * ((uint32_t)BW * (b & 1u) + 8u * (uint32_t)t + 4u * (i >> 4)) + (i & 15u);
     }
     static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
@@ -332,7 +348,7 @@ template <> struct Lane<4> {
     static TM_HD void scalars(uint32_t* units, uint32_t b, int lane, int zl, float s, float s8, float s16, float s32) {
         (void)zl;
         (void)s8; (void)s16;
-        if (lane == 0) { units[(b >> 1) * XW + 48 + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + 50 + (b & 1u)] = as_uint(s32); }
+        if (lane == 0) { units[(b >> 1) * XW + SC + (b & 1u)] = as_uint(s); units[(b >> 1) * XW + SC + 2 + (b & 1u)] = as_uint(s32); }
     }
     template <int B>
     static TM_HD float block(const uint8_t* p, const X& x) {
@@ -345,11 +361,11 @@ template <> struct Lane<4> {
         for (int t = 0; t < kPlanes; ++t) {
             int l = 0, h = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { l = dp4a_us(lo[i], x.w[24 * B + 8 * t + i], l); h = dp4a_us(hi[i], x.w[24 * B + 8 * t + 4 + i], h); }
+            for (int i = 0; i < 4; ++i) { l = dp4a_us(lo[i], x.w[BW * B + 8 * t + i], l); h = dp4a_us(hi[i], x.w[BW * B + 8 * t + 4 + i], h); }
             S[t] = l + (h >> 4);
         }
         const float d = half_to_float(hdr & 0xffffu), m = half_to_float(hdr >> 16);
-        return fma1(d * as_float(x.w[48 + B]), planes_to_float(S), m * as_float(x.w[50 + B]));
+        return fma1(d * as_float(x.w[SC + B]), planes_to_float(S), m * as_float(x.w[SC + 2 + B]));
     }
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
         (void)lane;
@@ -363,12 +379,13 @@ template <> struct Lane<4> {
 // Q5_K: 176-byte super-blocks of 256. Eight lanes share a super-block; lane i takes
 // group g = i/2 (64 weights: sub-blocks 2g and 2g+1) and byte half q = i%2: bytes
 // 16q..16q+15 of the group's qs, i.e. a run of 16 weights in each sub-block.
-// x unit: run0 plane t at [4t, 4t+4), run1 plane t at [12+4t, +4); [24] = scale of
-// sub-block 2g, [25] = scale of 2g+1, [26] = sum(x run0), [27] = sum(x run1).
+// x unit: run0 plane t at [4t, 4t+4), run1 plane t at [4P + 4t, +4); [8 P] = scale of
+// sub-block 2g, [8 P + 1] = scale of 2g+1, [8 P + 2] = sum(x run0), [8 P + 3] = sum(x run1) (P = kPlanes).
 // =============================================================================
 template <> struct Lane<5> {
     static constexpr int STEP_W = 1024, STEP_BYTES = 704, UNIT_W = 256, LANE_UNITS = 1, LANE_BYTES = 0;
-    static constexpr int XW = 28;
+    static constexpr int RW = 4 * kPlanes, SC = 8 * kPlanes;
+    static constexpr int XW = kPlanes == 3 ? 28 : 20;
     static constexpr bool NEEDS_SUMS = true;
     struct X { uint32_t w[XW]; };
 
@@ -376,7 +393,7 @@ template <> struct Lane<5> {
     static TM_HD uint32_t plane_byte(uint32_t e, int t) {
         const uint32_t S = e >> 8, w = e & 255u, g = w >> 6, half = (w >> 5) & 1u, l = w & 31u;
         const uint32_t u = 8u * S + 2u * g + (l >> 4);
-        return u * (XW * 4u) + 4u * (12u * half + 4u * (uint32_t)t) + (l & 15u);
+        return u * (XW * 4u) + 4u * ((uint32_t)RW * half + 4u * (uint32_t)t) + (l & 15u);
     }
     static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
@@ -387,8 +404,8 @@ template <> struct Lane<5> {
         const uint32_t S = b >> 3, j = b & 7u, g = j >> 1, half = j & 1u;
         if ((lane & 15) == 0) {                              // lanes 0 and 16 hold the sums of the two 16-runs
             const uint32_t u = 8u * S + 2u * g + (uint32_t)(lane >> 4);
-            units[u * XW + 24 + half] = as_uint(s);
-            units[u * XW + 26 + half] = as_uint(s16);
+            units[u * XW + SC + half] = as_uint(s);
+            units[u * XW + SC + 2 + half] = as_uint(s16);
         }
     }
     // p: start of the warp's row chunk (16-byte aligned); nvalid: super-blocks present in it
@@ -425,12 +442,12 @@ template <> struct Lane<5> {
         for (int t = 0; t < kPlanes; ++t) {
             int a = 0, b = 0;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { a = dp4a_us(c0[e], x.w[4 * t + e], a); b = dp4a_us(c1[e], x.w[12 + 4 * t + e], b); }
+            for (int e = 0; e < 4; ++e) { a = dp4a_us(c0[e], x.w[4 * t + e], a); b = dp4a_us(c1[e], x.w[RW + 4 * t + e], b); }
             S0[t] = a; S1[t] = b;
         }
         const float d = half_to_float(hdr.x & 0xffffu), dmin = half_to_float(hdr.x >> 16);
-        const float pos = fma1(sc[0] * as_float(x.w[24]), planes_to_float(S0), sc[1] * as_float(x.w[25]) * planes_to_float(S1));
-        const float neg = fma1(mn[0], as_float(x.w[26]), mn[1] * as_float(x.w[27]));
+        const float pos = fma1(sc[0] * as_float(x.w[SC]), planes_to_float(S0), sc[1] * as_float(x.w[SC + 1]) * planes_to_float(S1));
+        const float neg = fma1(mn[0], as_float(x.w[SC + 2]), mn[1] * as_float(x.w[SC + 3]));
         return fma1(d, pos, -(dmin * neg));
     }
 };
@@ -465,12 +482,12 @@ template <> struct Lane<8> : Lane<5> {
         for (int t = 0; t < kPlanes; ++t) {
             int a = 0, b = 0;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { a = dp4a_us(wq[e] & kLo, x.w[4 * t + e], a); b = dp4a_us((wq[e] >> 4) & kLo, x.w[12 + 4 * t + e], b); }
+            for (int e = 0; e < 4; ++e) { a = dp4a_us(wq[e] & kLo, x.w[4 * t + e], a); b = dp4a_us((wq[e] >> 4) & kLo, x.w[RW + 4 * t + e], b); }
             S0[t] = a; S1[t] = b;
         }
         const float d = half_to_float(hdr.x & 0xffffu), dmin = half_to_float(hdr.x >> 16);
-        const float pos = fma1(sc[0] * as_float(x.w[24]), planes_to_float(S0), sc[1] * as_float(x.w[25]) * planes_to_float(S1));
-        const float neg = fma1(mn[0], as_float(x.w[26]), mn[1] * as_float(x.w[27]));
+        const float pos = fma1(sc[0] * as_float(x.w[SC]), planes_to_float(S0), sc[1] * as_float(x.w[SC + 1]) * planes_to_float(S1));
+        const float neg = fma1(mn[0], as_float(x.w[SC + 2]), mn[1] * as_float(x.w[SC + 3]));
         return fma1(d, pos, -(dmin * neg));
     }
 };
@@ -480,12 +497,13 @@ template <> struct Lane<8> : Lane<5> {
 // super-block; lane i takes l in [8i, 8i+8) of both 128-halves: for each half 8 bytes
 // of ql[l], 8 of ql[l+32], 8 of qh[l] -> 4 runs of 8 weights (elements l + 32j), each
 // run inside one 16-weight sub-block with its own int8 scale.
-// x unit: run r = 4h + j: plane t words at [6r + 2t, +2); [48 + r] = scale of the
-// 32-block holding the run, [56 + r] = sum(x) over the run.
+// x unit: run r = 4h + j: plane t words at [2P r + 2t, +2); [16 P + r] = scale of the
+// 32-block holding the run, [16 P + 8 + r] = sum(x) over the run (P = kPlanes).
 // =============================================================================
 template <> struct Lane<6> {
     static constexpr int STEP_W = 2048, STEP_BYTES = 1680, UNIT_W = 256, LANE_UNITS = 1, LANE_BYTES = 0;
-    static constexpr int XW = 68;
+    static constexpr int RW = 2 * kPlanes, SC = 16 * kPlanes;
+    static constexpr int XW = kPlanes == 3 ? 68 : 52;
     static constexpr bool NEEDS_SUMS = true;
     struct X { uint32_t w[XW]; };
 
@@ -493,7 +511,7 @@ template <> struct Lane<6> {
     static TM_HD uint32_t plane_byte(uint32_t e, int t) {
         const uint32_t S = e >> 8, w = e & 255u, r = w >> 5, l = w & 31u;
         const uint32_t u = 4u * S + (l >> 3);
-        return u * (XW * 4u) + 4u * (6u * r + 2u * (uint32_t)t) + (l & 7u);
+        return u * (XW * 4u) + 4u * ((uint32_t)RW * r + 2u * (uint32_t)t) + (l & 7u);
     }
     static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t)) = packed;
@@ -504,16 +522,16 @@ template <> struct Lane<6> {
         const uint32_t S = b >> 3, r = b & 7u;
         if ((lane & 7) == 0) {                               // lanes 0, 8, 16, 24 hold the sums of the four 8-runs
             const uint32_t u = 4u * S + (uint32_t)(lane >> 3);
-            units[u * XW + 48 + r] = as_uint(s);
-            units[u * XW + 56 + r] = as_uint(s8);
+            units[u * XW + SC + r] = as_uint(s);
+            units[u * XW + SC + 8 + r] = as_uint(s8);
         }
     }
     static TM_HD float run_dot(uint32_t c0, uint32_t c1, const X& x, int r, float sc) {
         int S[kPlanes];
 #pragma unroll
-        for (int t = 0; t < kPlanes; ++t) S[t] = dp4a_us(c1, x.w[6 * r + 2 * t + 1], dp4a_us(c0, x.w[6 * r + 2 * t], 0));
+        for (int t = 0; t < kPlanes; ++t) S[t] = dp4a_us(c1, x.w[RW * r + 2 * t + 1], dp4a_us(c0, x.w[RW * r + 2 * t], 0));
         // codes carry a zero point of 32: sum (c - 32) x = s * S - 32 * sum(x)
-        return sc * fma1(as_float(x.w[48 + r]), planes_to_float(S), -32.f * as_float(x.w[56 + r]));
+        return sc * fma1(as_float(x.w[SC + r]), planes_to_float(S), -32.f * as_float(x.w[SC + 8 + r]));
     }
     static TM_HD float dot(const uint8_t* p, const X& x, int lane, int nvalid) {
         const int sb = lane >> 2;

@@ -57,6 +57,20 @@ bool tm_cuda_peer_open(int rank, int world, const void* handles) {
     return true;
 }
 
+// Single-GPU rehearsal of the sharded lane: every "peer" arena is this GPU's own arena. Pushed rows and counts land
+// in local memory; the counters of the other ranks never advance, so a kernel that waits for them runs into its
+// limit, which is how the give-up path (status word, abort word) is exercised without a second GPU.
+bool tm_cuda_peer_open_loopback(int rank, int world) {
+    if (!ensure_init(-1)) return false;
+    PeerState& ps = state().peer;
+    if (!ps.arena) return fail("peer: create the arena first");
+    if (ps.open) return fail("peer: already open");
+    if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world) return fail("peer: rank %d of %d is not valid (2..%d ranks)", rank, world, kMaxRanks);
+    for (int q = 0; q < world; ++q) ps.base[q] = ps.arena;
+    ps.rank = rank; ps.world = world; ps.open = true; ps.loopback = true;
+    return true;
+}
+
 int tm_cuda_peer_world(void) { return state().peer.open ? state().peer.world : 1; }
 int tm_cuda_peer_rank(void) { return state().peer.open ? state().peer.rank : 0; }
 
@@ -67,9 +81,11 @@ bool tm_cuda_peer_unmap(void) {
     PeerState& ps = s.peer;
     if (!ps.open) return true;
     if (s.ready) cudaStreamSynchronize(s.stream);
-    for (int q = 0; q < ps.world; ++q)
-        if (q != ps.rank && ps.base[q]) { cudaIpcCloseMemHandle(ps.base[q]); ps.base[q] = nullptr; }
-    ps.open = false;
+    for (int q = 0; q < ps.world; ++q) {
+        if (q != ps.rank && ps.base[q] && !ps.loopback) cudaIpcCloseMemHandle(ps.base[q]);
+        if (q != ps.rank) ps.base[q] = nullptr;
+    }
+    ps.open = false; ps.loopback = false;
     return check_launch("peer: unmap");
 }
 

@@ -31,13 +31,15 @@ struct Slot {                    // token-lane slot: backend-owned device buffer
 // The arena starts with the exchange counters, counters[site][rank]; shared slots follow, at the same
 // offsets on every rank because every rank reserves them in the same order.
 constexpr int kMaxRanks = 8, kMaxSites = 256;
-constexpr size_t kFlagBytes = (size_t)kMaxSites * kMaxRanks * sizeof(int);
+constexpr size_t kAbortWord = (size_t)kMaxSites * kMaxRanks;      // index (in ints) of the arena's sticky abort word
+constexpr size_t kFlagBytes = (kAbortWord + 64) * sizeof(int);
 struct PeerState {
     uint8_t* arena = nullptr;
     size_t bytes = 0, used = 0;
     uint8_t* base[kMaxRanks] = {};                              // base[rank] == arena once opened
     int rank = 0, world = 1;
     bool open = false;
+    bool loopback = false;                                      // every peer base is this GPU's own arena (single-GPU rehearsal)
     unsigned site_ctas[kMaxSites] = {};                         // CTAs of the launch that pushes to each site (0: none yet)
 };
 
@@ -48,6 +50,7 @@ struct WeightBuf {               // registered weights: handle id = 1000 + index
 
 struct State {
     bool ready = false, verbose = false, kv_half = true;
+    unsigned long long wait_limit_ns = 2000000000ull;           // bounded device waits on other GPUs (TM_CUDA_WAIT_LIMIT_MS)
     int device = -1, sm_count = 0;
     cudaStream_t stream = nullptr;
     int* status_dev = nullptr;                                  // device view of status_host
@@ -76,6 +79,17 @@ struct State {
     float rope_theta = 0.f;
     unsigned* peek_host = nullptr;                              // pinned mirror for tok_peek
     PeerState peer;
+
+    // x image of the chain forms: x in the GEMV lanes' unit form, written once per launch by the xprep kernel.
+    // A fixed-size buffer, so that captured graphs keep a valid pointer.
+    struct XImage {
+        uint32_t* buf = nullptr;
+        const float* x = nullptr; const float* x2 = nullptr;    // what the image holds: x after (x_op, x2, eps), for (K, dtype)
+        unsigned x_op = 0, K = 0, dtype = 0;
+        float eps = 0.f;
+        unsigned long long stamp = ~0ull;                       // value of `launches` up to which the image is known to be current
+    };
+    XImage x_prep;
 };
 
 State& state();

@@ -525,6 +525,10 @@ static bool make_exchange(Exchange& xc, int wait_site, int push_site, int states
     const int* st = (const int*)slot_ptr(stateslot, 16, who);
     if (!st) return false;
     xc.epoch = st + 3;
+    xc.limit_ns = s.wait_limit_ns;
+    xc.abort_local = (int*)ps.arena + kAbortWord;
+    for (int q = 0; q < ps.world; ++q)
+        if (q != ps.rank) xc.abort_peer[xc.npeers++] = (int*)ps.base[q] + kAbortWord;
     unsigned* ctrs = (unsigned*)ps.arena;
     if (wait_site >= 0) {
         if (!ps.site_ctas[wait_site]) { latch("%s: waits on site %d before any launch pushes to it", who, wait_site); return false; }
@@ -544,6 +548,37 @@ static bool make_exchange(Exchange& xc, int wait_site, int push_site, int states
         xc.npush = n;
     }
     return true;
+}
+
+// RMSNorm weights are cached on the device by host pointer (as tok_rmsnorm does).
+static const float* norm_weights_dev(const void* norm_w, unsigned K, const char* who) {
+    State& s = state();
+    auto it = s.norm_w.find(norm_w);
+    if (it == s.norm_w.end()) {
+        float* dw = nullptr;
+        if (cudaMalloc(&dw, (size_t)K * 4) != cudaSuccess) { cudaGetLastError(); latch("%s: weight allocation failed", who); return nullptr; }
+        cudaMemcpyAsync(dw, norm_w, (size_t)K * 4, cudaMemcpyHostToDevice, s.stream);
+        it = s.norm_w.emplace(norm_w, dw).first;
+    }
+    return it->second;
+}
+
+// x image (state.h): a fixed buffer, created on first use.
+constexpr size_t kXImageBytes = 256 * 1024;
+static bool x_images_ready() {
+    State& s = state();
+    static const bool on = !(std::getenv("TM_GEMV_XQ") && *std::getenv("TM_GEMV_XQ") == '0');   // A/B knob: 0 = every CTA stages x itself
+    if (!on) return false;
+    if (s.x_prep.buf) return true;
+    uint8_t* p = nullptr;
+    if (cudaMalloc(&p, kXImageBytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    cudaMemsetAsync(p, 0, kXImageBytes, s.stream);
+    s.x_prep.buf = (uint32_t*)p;
+    return true;
+}
+static bool image_holds(const State::XImage& im, const float* x, unsigned x_op, const float* x2, float eps, unsigned K, unsigned dtype) {
+    return im.buf && im.stamp == state().launches && im.x == x && im.x_op == x_op && im.K == K && im.dtype == dtype &&
+           (x_op == 0 || im.x2 == x2) && (x_op != 1 || im.eps == eps);
 }
 
 static void gemv_fused_impl(const char* who, int xslot, size_t xoff, int x_op, int x2slot, size_t x2off, const void* norm_w, float eps,
@@ -584,20 +619,37 @@ static void gemv_fused_impl(const char* who, int xslot, size_t xoff, int x_op, i
     f.xchg = (xc.nwait || xc.npush) ? &xc : nullptr;
     if (x_op == 1) {
         if (!norm_w) { latch("%s: rmsnorm needs its weights", who); return; }
-        auto it = s.norm_w.find(norm_w);
-        if (it == s.norm_w.end()) {
-            float* dw = nullptr;
-            if (cudaMalloc(&dw, (size_t)K * 4) != cudaSuccess) { cudaGetLastError(); latch("%s: weight allocation failed", who); return; }
-            cudaMemcpyAsync(dw, norm_w, (size_t)K * 4, cudaMemcpyHostToDevice, s.stream);
-            it = s.norm_w.emplace(norm_w, dw).first;
-        }
-        f.x2 = it->second;
+        f.x2 = norm_weights_dev(norm_w, K, who);
+        if (!f.x2) return;
     } else if (x_op == 2) {
         const uint8_t* u = slot_ptr(x2slot, x2off + (size_t)K * 4, who);
         if (!u) return;
         f.x2 = (const float*)(u + x2off);
     } else if (x_op != 0) { latch("%s: unknown x transform %d", who, x_op); return; }
-    if (!launch_gemv((const float*)(x + xoff), s.wbufs[i].ptr, (float*)(y + yoff), N, K, dtype, t, s.stream, &f)) { s.sticky = true; return; }
+    // Heavy staging (SiLU * up, or a long K) is done once per launch by a small kernel ahead of the GEMV instead of by
+    // every CTA; a GEMV that follows on the same x (k and v after q) reuses the image. Light staging stays in the CTAs:
+    // there the extra dependent kernel costs what it saves.
+    const float* xp = (const float*)(x + xoff);
+    float* yp = (float*)(y + yoff);
+    State::XImage* used = nullptr;
+    const size_t img = xq_bytes(K, dtype);
+    if ((f.x_op == 2 || K >= 8192) && img && img <= kXImageBytes && x_images_ready()) {
+        if (!(wait_site < 0 && image_holds(s.x_prep, xp, f.x_op, f.x2, eps, K, dtype))) {
+            Exchange xw = xc;
+            xw.npush = 0;                                    // the staging kernel only waits for the gather, it pushes nothing
+            if (!launch_xprep(s.x_prep.buf, xp, f.x2, f.x_op, eps, K, dtype, xw.nwait ? &xw : nullptr, s.stream)) { s.sticky = true; return; }
+            s.x_prep.x = xp; s.x_prep.x2 = f.x2; s.x_prep.x_op = f.x_op; s.x_prep.K = K; s.x_prep.dtype = dtype; s.x_prep.eps = eps;
+        }
+        used = &s.x_prep;
+        f.xq = used->buf;
+    }
+    if (!launch_gemv(xp, s.wbufs[i].ptr, yp, N, K, dtype, t, s.stream, &f)) { s.sticky = true; return; }
+    // The image stays current while the launches that follow its producer only read it: this GEMV did, unless its output
+    // overlaps the x the image was made from.
+    if (used) {
+        const bool clobbers = (const uint8_t*)yp < (const uint8_t*)xp + (size_t)K * 4 && (const uint8_t*)xp < y + y_need;
+        used->stamp = clobbers ? ~0ull : s.launches;
+    }
     if (push_site >= 0) {
         // every rank launches the same shapes, so this grid is also what the peers' counters advance by per token
         unsigned& ctas = s.peer.site_ctas[push_site];

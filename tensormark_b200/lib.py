@@ -22,6 +22,8 @@ SIGNATURES = {
     "tm_cuda_fallback_count": (C.c_ulonglong, []),
     "tm_cuda_launch_count": (C.c_ulonglong, []),
     "tm_cuda_sm_count": (C.c_int, []),
+    "tm_cuda_set_wait_limit_ms": (C.c_uint, [C.c_uint]),
+    "tm_cuda_peer_open_loopback": (C.c_bool, [C.c_int, C.c_int]),
     "tm_cuda_q4_gemv": (C.c_bool, [_vp, _vp, _vp, _u, _u]),
     "tm_cuda_sgemm_q4": (C.c_bool, [_vp, _vp, _vp, _u, _u, _u]),
     "tm_cuda_q4_prefill": (C.c_bool, [_vp, C.POINTER(_vp), C.POINTER(_u), _u, _vp, _u, _u]),

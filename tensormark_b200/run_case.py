@@ -261,6 +261,20 @@ def main() -> None:
         stream.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / args.reps
     lib.check(L.tm_cuda_tok_flush(), "device status")
+    if args.trace and args.op == "gemv":
+        # CTA 0's timeline of the last `reps` launches (TM_CUDA_TRACE=1): phases and the gap to the previous launch's end
+        buf = (C.c_ulonglong * (6 * 8192))()
+        nrec = int(L.tm_cuda_trace_read(buf, 8192))
+        if nrec:
+            a = np.frombuffer(buf, dtype=np.uint64)[: nrec * 6].reshape(nrec, 6).astype(np.int64)
+            a = a[np.argsort(a[:, 0])][-args.reps:]
+            gap = (a[1:, 0] - a[:-1, 3]) / 1e3
+            print(json.dumps({"trace_us": {"wait": round(float((a[:, 1] - a[:, 0]).mean()) / 1e3, 2),
+                                           "x": round(float((a[:, 2] - a[:, 1]).mean()) / 1e3, 2),
+                                           "rows": round(float((a[:, 3] - a[:, 2]).mean()) / 1e3, 2),
+                                           "start_to_end": round(float((a[:, 3] - a[:, 0]).mean()) / 1e3, 2),
+                                           "end_to_next_start": round(float(gap.mean()), 2) if gap.size else None,
+                                           "start_to_next_start": round(float((a[1:, 0] - a[:-1, 0]).mean()) / 1e3, 2) if gap.size else None}}))
     print(json.dumps({"op": args.op, "dtype": args.dtype, "m": m if args.op == "gemm" else None, "n": n, "k": k,
                       "us_per_launch": round(us, 3), "rate": round(work / (us * 1e-6), 2), "unit": unit,
                       "launches": int(L.tm_cuda_launch_count())}))

@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 
 from tensormark_b200 import lib, synth
+from tests.bounds import activation_rounding_bound
 from tests.gpu_util import dev_bytes, dev_f32, gemv_dev, ptr, stream_ptr
 
 pytestmark = pytest.mark.gpu
@@ -69,12 +70,14 @@ def _check_gemv(cuda, torch, orc, dt, n, k, seed, wseed=None):
     y64, yabs = orc.gemv_f64(dt, W, x, n, k)
     err = np.abs(y - y64)
     assert np.all(err <= TOL * yabs), (synth.DTYPE_NAMES[dt], n, k, float((err / yabs).max()))
+    # ... and inside what the kernel's activation format can lose (tests/bounds.py) plus fp32 accumulation noise
+    assert np.all(err <= activation_rounding_bound(orc, dt, W, x, n, k) + 2e-6 * yabs), (synth.DTYPE_NAMES[dt], n, k)
     return float((err / np.maximum(yabs, 1e-30)).max())
 
 
 def test_config1_q4_0_2048(cuda, torch_mod, orc):
     worst = _check_gemv(cuda, torch_mod, orc, synth.Q4_0, 2048, 2048, seed=0)
-    assert worst < 1e-5          # fp32 accumulation leaves far more room than the bar
+    assert worst < 2e-5          # two-digit activations: derived worst case 9e-5 for one-scale inputs, a few 1e-6 in practice
 
 
 @pytest.mark.parametrize("dt,seed", [(synth.Q8_0, 1), (synth.Q4_1, 2)])
@@ -170,16 +173,24 @@ def test_empty_output_is_a_no_op(cuda, torch_mod):
     assert cuda.tm_cuda_gemv_q_dev(ptr(x), ptr(W), ptr(y), 0, 2048, synth.Q4_0, stream_ptr(torch_mod))
 
 
-def test_full_size_property_scaling_and_linearity(cuda, torch_mod):
-    """At the largest configured sizes the oracle is not rerun; instead a size-independent property:
-    W(a*x1 + x2) == a*W(x1) + W(x2) within rounding, for every output row."""
+def test_full_size_property_scaling_and_linearity(cuda, torch_mod, orc):
+    """At the largest configured sizes the oracle is not rerun on every row; instead a size-independent property:
+    W(a*x1 + x2) == a*W(x1) + W(x2) within rounding, for every output row. Each of the three results may be off
+    by its own rounding, a small fraction of sum|w x| (the contract is 1e-3 of it); sum|w x| itself comes from the
+    oracle on a sample of rows and, as rows of one random tensor have similar norms, bounds the others with slack."""
     torch = torch_mod
     for dt, (n, k) in [(synth.Q8_0, (32000, 2048)), (synth.Q6_K, (14336, 4096)), (synth.Q5_K, (4096, 14336))]:
-        W = dev_bytes(torch, synth.make_weights(dt, n, k, seed=5))
+        Wh = synth.make_weights(dt, n, k, seed=5)
+        W = dev_bytes(torch, Wh)
         x1 = synth.make_activations(k, seed=5)
         x2 = synth.make_activations(k, seed=6)
+        x3 = (2.0 * x1 + x2).astype(np.float32)
         y1 = gemv_dev(cuda, torch, dt, W, dev_f32(torch, x1), n, k).astype(np.float64)
         y2 = gemv_dev(cuda, torch, dt, W, dev_f32(torch, x2), n, k).astype(np.float64)
-        y = gemv_dev(cuda, torch, dt, W, dev_f32(torch, (2.0 * x1 + x2).astype(np.float32)), n, k).astype(np.float64)
-        scale = np.abs(y1) * 2 + np.abs(y2) + 1e-3
-        assert np.all(np.abs(y - (2 * y1 + y2)) <= 2e-4 * scale + 2e-4)
+        y = gemv_dev(cuda, torch, dt, W, dev_f32(torch, x3), n, k).astype(np.float64)
+        rows = np.unique(np.random.default_rng(0).integers(0, n, size=128))
+        sub = np.ascontiguousarray(Wh[rows])
+        yabs = sum(c * orc.gemv_f64(dt, sub, x, rows.size, k)[1] for c, x in ((2.0, x1), (1.0, x2), (1.0, x3)))
+        dev = np.abs(y - (2 * y1 + y2))
+        assert np.all(dev[rows] <= 1e-4 * yabs)                     # sampled rows against their own sum|w x|
+        assert np.all(dev <= 2e-4 * float(yabs.max()))              # every row against the sample's largest

@@ -95,14 +95,18 @@ def test_gemv_pool_rows(hc, orc, dt):
 ])
 def test_gemv_lane_maps_on_cpu(lanes, orc, dt, shapes):
     """The kernel's lane decomposition, replayed on the CPU, against the fp64 reference.
-    Tolerance: 1e-3 * sum|w x| is the path's bar; the lane arithmetic itself stays below 2e-6."""
+    Tolerance: 1e-3 * sum|w x| is the path's bar; the lane arithmetic must also stay inside the bound derived
+    from its activation format (tests/bounds.py) plus fp32 accumulation noise."""
+    from tests.bounds import activation_rounding_bound
     for n, k in shapes:
         W = synth.make_weights(dt, n, k, seed=11)
         x = synth.make_activations(k, seed=12)
         y = np.zeros(n, np.float32)
         assert lanes.lane_emul_gemv(dt, W.ctypes.data, x.ctypes.data_as(_f32p), y.ctypes.data_as(_f32p), n, k)
         y64, yabs = orc.gemv_f64(dt, W, x, n, k)
-        assert np.all(np.abs(y - y64) <= 2e-6 * yabs), (synth.DTYPE_NAMES[dt], n, k)
+        err = np.abs(y - y64)
+        assert np.all(err <= 1e-3 * yabs), (synth.DTYPE_NAMES[dt], n, k)
+        assert np.all(err <= activation_rounding_bound(orc, dt, W, x, n, k) + 2e-6 * yabs), (synth.DTYPE_NAMES[dt], n, k)
 
 
 def _declared_symbols():

@@ -24,6 +24,8 @@
 #pragma once
 
 #include "cuda_shim.h"
+#include "llama_gpu_api.h"
+#include "quant.h"
 
 #include <cmath>
 #include <cstdint>
@@ -86,6 +88,7 @@ public:
     ~CudaLlama() {
         if (graph_ >= 0) tm_cuda_tok_graph_destroy(graph_);
         if (sgraph_ >= 0) tm_cuda_tok_graph_destroy(sgraph_);
+        if (stack_) tm_cuda_llama_destroy(stack_);
     }
     CudaLlama(const CudaLlama&) = delete;
     CudaLlama& operator=(const CudaLlama&) = delete;
@@ -391,6 +394,54 @@ public:
         return (int)next;
     }
 
+    // A prompt of n >= 2 tokens through the batched layer stack (tensormark/llama.h:6305-6352: embed the rows on the
+    // host, tm_*_llama_prefill, final norm + LM head on the last row), then the stack's K/V rows into the decode lane's
+    // caches so that a chain continues from position seen + n. Returns the token the model chooses after the prompt.
+    // Single GPU (the stack does not shard).
+    int gpu_prefill(const int* toks, int n) {
+        if (n < 2) throw std::invalid_argument("llama: the layer stack takes batches of two or more tokens");
+        if (seen + n > d_.ctx) throw std::invalid_argument("llama: prompt exceeds context");
+        if (chain_n_) throw std::runtime_error("llama: chain already running");
+        if (d_.world > 1) throw std::invalid_argument("llama: the layer stack runs on one GPU");
+        gpu_token_prologue();
+        ensure_stack();
+        const size_t D = (size_t)d_.D, row_bytes = tm_cuda_weight_bytes(d_.dt_embed, 1, D);
+        std::vector<float> x((size_t)n * D);
+        for (int i = 0; i < n; ++i) {
+            if (toks[i] < 0 || toks[i] >= d_.V) throw std::invalid_argument("llama: token id out of range");
+            tmq::dequantize_row(d_.dt_embed, (const uint8_t*)d_.embed + (size_t)toks[i] * row_bytes, x.data() + (size_t)i * D, D);
+        }
+        if (!tm_cuda_llama_prefill(stack_, x.data(), n, seen))
+            throw std::runtime_error(std::string("cuda: layer stack prefill failed: ") + tm_cuda_last_error());
+        for (int l = 0; l < d_.L; ++l)
+            if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, n))
+                throw std::runtime_error(std::string("cuda: K/V hand-over failed: ") + tm_cuda_last_error());
+        // last row -> final norm -> LM head -> greedy choice, on the lane
+        const unsigned cap = (unsigned)d_.ctx + 1;
+        std::vector<unsigned> t((size_t)cap, 0xFFFFFFFFu);
+        if (!tm_cuda_tok_reserve(SLOT_TOK, sizeof(unsigned) * (size_t)cap) ||
+            !tm_cuda_tok_upload(SLOT_TOK, 0, t.data(), sizeof(unsigned) * (size_t)cap) ||
+            !tm_cuda_tok_upload(SLOT_X, 0, x.data() + (size_t)(n - 1) * D, D * 4))
+            throw std::runtime_error("cuda: prompt result upload failed");
+        if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
+        tm_cuda_tok_rmsnorm(SLOT_X, d_.rmsf, SLOT_XF, (unsigned)d_.D, d_.eps);
+        tm_cuda_tok_gemv_kq(SLOT_XF, head_.id, head_.woff, SLOT_LOGITS, 0, (unsigned)d_.V, (unsigned)d_.D, d_.dt_head);
+        tm_cuda_tok_argmax(SLOT_LOGITS, SLOT_TOK, 0, (unsigned)d_.V);
+        if (!tm_cuda_tok_end(SLOT_LOGITS, logits_.data(), (unsigned)d_.V))
+            throw std::runtime_error(std::string("cuda: prompt head failed: ") + tm_cuda_last_error());
+        unsigned next = 0;
+        if (!tm_cuda_tok_download(SLOT_TOK, 0, &next, sizeof next)) throw std::runtime_error("cuda: token download failed");
+        seen += n;
+        return (int)next;
+    }
+    double last_prefill_gpu_ms() const { return tm_cuda_llama_prefill_gpu_ms(); }
+    // Creates the layer stack ahead of the first gpu_prefill (it is otherwise created by it).
+    void gpu_prefill_prepare() {
+        if (d_.world > 1) throw std::invalid_argument("llama: the layer stack runs on one GPU");
+        gpu_token_prologue();
+        ensure_stack();
+    }
+
     // Chosen token i as soon as it has landed, -1 while pending.
     int gpu_chain_poll(int i) const {
         if (i < 0 || i >= chain_n_) return -1;
@@ -421,6 +472,29 @@ public:
     }
 
 private:
+    // The layer stack of this model, with the fp32 host K/V arrays its contract asks the caller to own.
+    void ensure_stack() {
+        if (stack_) return;
+        const size_t kv = (size_t)d_.KVH * d_.ctx * d_.dh;
+        host_kc_.assign((size_t)d_.L, std::vector<float>());
+        host_vc_.assign((size_t)d_.L, std::vector<float>());
+        stack_layers_.resize((size_t)d_.L);
+        for (int l = 0; l < d_.L; ++l) {
+            host_kc_[(size_t)l].assign(kv, 0.f); host_vc_[(size_t)l].assign(kv, 0.f);
+            const CudaLlamaLayer& s = layers_[(size_t)l];
+            tm_llama_gpu_layer& g = stack_layers_[(size_t)l];
+            g = tm_llama_gpu_layer{};
+            g.q = s.q; g.k = s.k; g.v = s.v; g.o = s.o; g.gate = s.gate; g.up = s.up; g.down = s.down;
+            g.rms1 = s.rms1; g.rms2 = s.rms2;
+            g.kc = host_kc_[(size_t)l].data(); g.vc = host_vc_[(size_t)l].data();
+        }
+        tm_llama_gpu_desc gd{};
+        gd.L = d_.L; gd.D = d_.D; gd.H = d_.H; gd.KVH = d_.KVH; gd.dh = d_.dh; gd.F = d_.F; gd.ctx = d_.ctx;
+        gd.theta = d_.theta; gd.eps = d_.eps; gd.map_base = d_.map_base; gd.map_size = d_.map_size; gd.layers = stack_layers_.data();
+        stack_ = tm_cuda_llama_create_dt(&gd, d_.dt_proj);
+        if (!stack_) throw std::runtime_error(std::string("cuda: layer stack creation failed: ") + tm_cuda_last_error());
+    }
+
     // Launch the captured token graph `n` times from position `seen`; the first `forced` entries of the
     // token slot are inputs. The very first call runs one token eagerly (which creates every cached
     // resource) and captures the second encoding.
@@ -458,6 +532,9 @@ private:
     std::vector<float> logits_;
     bool ready_ = false, use_graph_ = true;
     int graph_ = -1, sgraph_ = -1, chain_n_ = 0, chain_seen0_ = 0;
+    void* stack_ = nullptr;
+    std::vector<tm_llama_gpu_layer> stack_layers_;
+    std::vector<std::vector<float>> host_kc_, host_vc_;
     float inv_temp_ = 0.f, sg_inv_temp_ = 0.f;                 // > 0 only while a sampled chain is being encoded
     unsigned seed_ = 0, sg_seed_ = 0;
 };

@@ -155,13 +155,14 @@ class _ModelStruct(C.Structure):
         ("rms1", C.POINTER(C.c_void_p)), ("rms2", C.POINTER(C.c_void_p)), ("rmsf", C.c_void_p),
         ("kc", C.c_void_p), ("vc", C.c_void_p),
         ("kv_half", C.c_int), ("threads", C.c_int),
+        ("qb", C.POINTER(C.c_void_p)), ("kb", C.POINTER(C.c_void_p)), ("vb", C.POINTER(C.c_void_p)),
     ]
 
 
 class ChainModel:
     """CPU decode chain over a dict of numpy weights (see tmo_chain_step)."""
 
-    def __init__(self, orc: Oracle, cfg: dict, weights: dict, kv_half: bool = False, threads: int = 1):
+    def __init__(self, orc: Oracle, cfg: dict, weights: dict, kv_half: bool = False, threads: int = 1, biases: dict | None = None):
         self.orc, self.cfg, self.weights = orc, cfg, weights
         L = cfg["L"]
         self.kc = np.zeros((L, cfg["KVH"], cfg["ctx"], cfg["dh"]), dtype=np.float32)
@@ -189,6 +190,13 @@ class ChainModel:
         s.rmsf = weights["rmsf"].ctypes.data
         s.kc, s.vc = self.kc.ctypes.data, self.vc.ctypes.data
         s.kv_half, s.threads = int(kv_half), threads
+        if biases:
+            for field, name in (("qb", "q_bias"), ("kb", "k_bias"), ("vb", "v_bias")):
+                arrs = [np.ascontiguousarray(biases[f"l{l}.{name}"], np.float32) for l in range(L)]
+                self._keep.append(arrs)
+                a = (C.c_void_p * L)(*[x.ctypes.data for x in arrs])
+                self._keep.append(a)
+                setattr(s, field, C.cast(a, C.POINTER(C.c_void_p)))
         self.s = s
 
     def tap_size(self):

@@ -485,6 +485,9 @@ typedef struct {
     float* kc; float* vc;                   /* L x [KVH][ctx][dh] */
     int kv_half;
     int threads;
+    /* optional attention bias per layer (Qwen2-style; metal_llama.h:577-590, llama.h tok_bias_qkv): QD / KVD / KVD floats,
+     * added to q, k, v before rope. NULL arrays: none. */
+    const float* const* qb; const float* const* kb; const float* const* vb;
 } tmo_model;
 
 static void chain_gemv(const tmo_model* m, int dtype, const void* W, const float* x, float* y, int n_out, int n_in) {
@@ -517,6 +520,10 @@ TMO_API int tmo_chain_step(const tmo_model* m, unsigned tok, int pos, float* log
         chain_gemv(m, m->dt_proj, m->wq[l], h, qkv, QD, D);
         chain_gemv(m, m->dt_proj, m->wk[l], h, qkv + QD, KVD, D);
         chain_gemv(m, m->dt_proj, m->wv[l], h, qkv + QD + KVD, KVD, D);
+        if (m->qb && m->kb && m->vb && m->qb[l]) {
+            for (int i = 0; i < QD; i++) qkv[i] += m->qb[l][i];
+            for (int i = 0; i < KVD; i++) { qkv[QD + i] += m->kb[l][i]; qkv[QD + KVD + i] += m->vb[l][i]; }
+        }
         for (int hd = 0; hd < m->H; hd++) tmo_rope_head(qkv + (size_t)hd * m->dh, m->dh, pos, m->theta);
         for (int kv = 0; kv < m->KVH; kv++) {
             float* kr = qkv + QD + (size_t)kv * m->dh;

@@ -81,7 +81,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError("link failed")
     # the C++ host driver of the decode chain, behind a flat C surface
     chain_src = os.path.join(HERE, "host", "chain_capi.cpp")
-    chain_deps = [chain_src, os.path.join(INCLUDE, "llama_chain.h"), os.path.join(INCLUDE, "cuda_shim.h"), LIB]
+    chain_deps = [chain_src, LIB] + [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE) if f.endswith(".h")]
     if force or _stale(CHAIN_LIB, chain_deps):
         cmd = ["g++", "-std=c++23", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I" + INCLUDE, "-o", CHAIN_LIB,
                chain_src, "-L" + HERE, "-ltm_cuda", "-Wl,-rpath,$ORIGIN"]

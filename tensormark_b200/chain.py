@@ -34,6 +34,10 @@ def load() -> C.CDLL:
                                  C.POINTER(C.c_ulonglong)]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         L.tmchain_logits.argtypes = [C.c_void_p, C.c_void_p]
+        L.tmchain_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.tmchain_prefill_prepare.argtypes = [C.c_void_p]
+        L.tmchain_prefill_gpu_ms.argtypes = [C.c_void_p]
+        L.tmchain_prefill_gpu_ms.restype = C.c_double
         _lib = L
     return _lib
 
@@ -145,6 +149,20 @@ class Chain:
         nxt = self.L.tmchain_feed(self.h, t.ctypes.data, t.size)
         self._check(nxt >= 0)
         return nxt
+
+    def prefill(self, tokens) -> int:
+        """Run a prompt (two or more tokens) through the batched layer stack; returns the token chosen after it."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        nxt = self.L.tmchain_prefill(self.h, t.ctypes.data, t.size)
+        self._check(nxt >= 0)
+        return nxt
+
+    def prefill_prepare(self) -> None:
+        """Create the layer stack ahead of the first prefill (device K/V caches, page-locked host arrays)."""
+        self._check(self.L.tmchain_prefill_prepare(self.h))
+
+    def prefill_gpu_ms(self) -> float:
+        return float(self.L.tmchain_prefill_gpu_ms(self.h))
 
     def chain_begin(self, first: int, n: int, graph: bool = True):
         self._check(self.L.tmchain_chain_begin(self.h, int(first), n, int(graph)))

@@ -1,0 +1,591 @@
+// llama_stack.cu — the GPU prefill layer stack behind include/llama_gpu_api.h.
+//
+// CUDA counterpart of the reference's Metal stack (tensormark/metal_llama.h): encode_layer 521-719 (same op order),
+// create 727-775, prefill 897-950 and the begin / wait_layer / end form 826-998, with the glue kernels it needs
+// (ll_rmsnorm 35-54, ll_rope 61-75, ll_kv_append 78-87, the per-group attention 630-690, ll_silu_mul / ll_add 139-147,
+// ll_bias 420-426). The seven projections of a layer are the tensor-core GEMM of gemm.cu; everything between them is
+// fp32, which is the reference's "kernel-exactness" mode (bar 1e-3, test_llama_gpu_stack.cpp:10-14).
+//
+// Where the reference shares the caller's K/V arrays with the GPU through unified memory, this stack keeps fp32 device
+// caches [KVH][ctx][dh] per layer, reads rows [0, pos0) from the caller's arrays when a call starts at pos0 > 0, and
+// copies the rows it computes back (on a second stream, one event per layer, which is what wait_layer(l) waits for,
+// with the reference's 30 s deadline).
+//
+// Attention: one kernel per layer. A CTA takes one K/V head and a block of query tokens, i.e. 64 query rows
+// (tokens x the REP query heads of the group, which share every K/V tile), and walks the keys [0, pos] in tiles of
+// 32 with an online softmax. Q K^T and P V are tf32 tensor-core products with fp32 accumulation; scores, softmax
+// statistics (one lane per key, warp shuffles) and the running output are fp32.
+#include "cuda_shim.h"
+#include "llama_gpu_api.h"
+#include "common.cuh"
+#include "gemm.h"
+#include "glue.h"
+#include "state.h"
+
+#include <cuda_fp16.h>
+
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+namespace tmc {
+namespace {
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * w, one CTA per token row (ll_rmsnorm, metal_llama.h:35-54).
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           float* __restrict__ out, uint32_t D, float eps) {
+    __shared__ float part[8];
+    __shared__ float inv_s;
+    const float* xr = x + (size_t)blockIdx.x * D;
+    float* o = out + (size_t)blockIdx.x * D;
+    float p = 0.f;
+    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i]; p = fmaf(v, v, p); }
+    p = wsum(p);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = p;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int i = 0; i < 8; ++i) s += part[i];
+        inv_s = 1.0f / sqrtf(s / (float)D + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) o[i] = xr[i] * inv * w[i];
+}
+
+// y[t][c] += bias[c] (ll_bias, metal_llama.h:420-426); y rows have stride ld.
+__global__ void bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, uint32_t n, uint32_t ld, uint32_t T) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * n) return;
+    const uint32_t t = (uint32_t)(i / n), c = (uint32_t)(i % n);
+    y[(size_t)t * ld + c] += bias[c];
+}
+
+// For every token t of the batch (position pos0 + t): rotate q in place, rotate k into the K cache row, copy v into the
+// V cache row (ll_rope + ll_kv_append, metal_llama.h:61-87; pairs (j, j + dh/2), angles from the shared table).
+__global__ void rope_append_kernel(float* __restrict__ qkv, uint32_t ld, float* __restrict__ kc, float* __restrict__ vc,
+                                   uint32_t H, uint32_t KVH, uint32_t dh, uint32_t ctx, uint32_t pos0, uint32_t T,
+                                   const float2* __restrict__ tbl, uint32_t tbl_n) {
+    const uint32_t half = dh / 2, per_tok = (H + KVH) * half + KVH * dh;
+    const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (size_t)T * per_tok) return;
+    const uint32_t t = (uint32_t)(gid / per_tok), e = (uint32_t)(gid % per_tok), pos = pos0 + t;
+    float* row = qkv + (size_t)t * ld;
+    if (e < (H + KVH) * half) {
+        const uint32_t h = e / half, j = e % half;
+        if ((size_t)pos * half + j >= tbl_n) return;
+        const float2 cs = tbl[(size_t)pos * half + j];
+        float* r = row + (size_t)h * dh;                       // q heads, then k heads, are contiguous in the row
+        const float a = r[j], b = r[j + half];
+        const float ra = a * cs.x - b * cs.y, rb = b * cs.x + a * cs.y;
+        if (h < H) { r[j] = ra; r[j + half] = rb; }
+        else {
+            float* dst = kc + ((size_t)(h - H) * ctx + pos) * dh;
+            dst[j] = ra; dst[j + half] = rb;
+        }
+    } else {
+        const uint32_t i = e - (H + KVH) * half, kv = i / dh, l = i % dh;
+        vc[((size_t)kv * ctx + pos) * dh + l] = row[(size_t)(H + KVH) * dh + i];
+    }
+}
+
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+// D += A (16x8, row) * B (8x8, col), tf32 operands, fp32 accumulate.
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Causal GQA attention of a token batch against the fp32 caches. grid (token blocks, KVH), 256 threads = 8 warps.
+// Row r of a CTA = token t0 + r / REP, query head g * REP + r % REP; BT = 64 / REP tokens per CTA, keys in tiles of 32.
+// Both products run on the tensor cores as m16n8k8 tf32 MMAs with fp32 accumulation: q (pre-scaled), k, v and the
+// probabilities are rounded once to tf32 (10 mantissa bits, the precision the projections' fp16 operands have, with
+// fp32's range: scores of 128-wide heads overflow fp16); scores, softmax statistics and the output stay fp32.
+//   scores: warp w -> rows [16 (w / 2), +16) x keys [16 (w % 2), +16) of the tile (2 n-tiles, DH / 8 k-steps)
+//   output: warp w -> rows [16 (w / 2), +16) x dims [DH/2 (w % 2), + DH/2)     (DH / 16 n-tiles, 4 k-steps per tile)
+// Shared-memory strides are chosen so that the 32 lanes of a fragment load (8 rows x 4 columns) hit 32 banks.
+template <int DH>
+__global__ void __launch_bounds__(256) prefill_attn_kernel(const float* __restrict__ qkv, uint32_t ld, const float* __restrict__ kc,
+                                                           const float* __restrict__ vc, float* __restrict__ out, uint32_t QD,
+                                                           uint32_t T, uint32_t pos0, uint32_t ctx, uint32_t REP, float scale) {
+    constexpr int QS = DH + 4;                                  // Q and K rows: stride 4 (mod 32)
+    constexpr int VS = DH + 8;                                  // V rows: stride 8 (mod 32)
+    constexpr int D4 = DH / 4;
+    constexpr int NT = DH / 16;                                 // output n-tiles per warp
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                                             // [64][QS] tf32 bit patterns
+    float* Ks = Qs + 64 * QS;                                   // [32][QS]
+    float* Vs = Ks + 32 * QS;                                   // [32][VS]
+    float* Ss = Vs + 32 * VS;                                   // [64][33] scores, then probabilities (fp32)
+    float* mrow = Ss + 64 * 33;                                 // running max, sum, rescale factor per row
+    float* lrow = mrow + 64;
+    float* arow = lrow + 64;
+    const uint32_t BT = 64u / REP, nrows = BT * REP, g = blockIdx.y, t0 = blockIdx.x * BT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int fg = lane >> 2, ft = lane & 3;                    // fragment coordinates of this lane
+    const int rb = warp >> 1, wh = warp & 1;
+    const uint32_t t_end = min(T, t0 + BT);                     // tokens [t0, t_end)
+    const uint32_t kmax = pos0 + t_end;                         // keys [0, kmax) are visible to the block's last token
+
+    for (int i = tid; i < 64 * D4; i += 256) {
+        const uint32_t r = i / D4, c = i % D4, t = t0 + r / REP;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < nrows && t < T) v = *reinterpret_cast<const float4*>(qkv + (size_t)t * ld + (size_t)(g * REP + r % REP) * DH + 4 * c);
+        uint4 q;
+        q.x = to_tf32(v.x * scale); q.y = to_tf32(v.y * scale); q.z = to_tf32(v.z * scale); q.w = to_tf32(v.w * scale);
+        *reinterpret_cast<uint4*>(Qs + r * QS + 4 * c) = q;
+    }
+    if (tid < 64) { mrow[tid] = -INFINITY; lrow[tid] = 0.f; arow[tid] = 1.f; }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+
+    const float* kbase = kc + (size_t)g * ctx * DH;
+    const float* vbase = vc + (size_t)g * ctx * DH;
+    const uint32_t* Qu = reinterpret_cast<const uint32_t*>(Qs);
+    const uint32_t* Ku = reinterpret_cast<const uint32_t*>(Ks);
+    const uint32_t* Vu = reinterpret_cast<const uint32_t*>(Vs);
+    for (uint32_t k0 = 0; k0 < kmax; k0 += 32) {
+        __syncthreads();                                        // the previous tile's K, V and P are no longer read
+        for (int i = tid; i < 32 * D4; i += 256) {
+            const uint32_t j = i / D4, c = i % D4, kk = k0 + j;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (kk < kmax) {
+                kv = *reinterpret_cast<const float4*>(kbase + (size_t)kk * DH + 4 * c);
+                vv = *reinterpret_cast<const float4*>(vbase + (size_t)kk * DH + 4 * c);
+            }
+            uint4 a, b;
+            a.x = to_tf32(kv.x); a.y = to_tf32(kv.y); a.z = to_tf32(kv.z); a.w = to_tf32(kv.w);
+            b.x = to_tf32(vv.x); b.y = to_tf32(vv.y); b.z = to_tf32(vv.z); b.w = to_tf32(vv.w);
+            *reinterpret_cast<uint4*>(Ks + j * QS + 4 * c) = a;
+            *reinterpret_cast<uint4*>(Vs + j * VS + 4 * c) = b;
+        }
+        __syncthreads();
+        // scores of rows [16 rb, +16) x keys [16 wh, +16)
+        float sc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[n][e] = 0.f;
+#pragma unroll 4
+        for (int ks = 0; ks < DH / 8; ++ks) {
+            uint32_t a[4];
+            a[0] = Qu[(16 * rb + fg) * QS + 8 * ks + ft];
+            a[1] = Qu[(16 * rb + fg + 8) * QS + 8 * ks + ft];
+            a[2] = Qu[(16 * rb + fg) * QS + 8 * ks + ft + 4];
+            a[3] = Qu[(16 * rb + fg + 8) * QS + 8 * ks + ft + 4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int key = 16 * wh + 8 * n + fg;
+                mma_tf32(sc[n], a, Ku[key * QS + 8 * ks + ft], Ku[key * QS + 8 * ks + ft + 4]);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int col = 16 * wh + 8 * n + 2 * ft;
+            Ss[(16 * rb + fg) * 33 + col] = sc[n][0];
+            Ss[(16 * rb + fg) * 33 + col + 1] = sc[n][1];
+            Ss[(16 * rb + fg + 8) * 33 + col] = sc[n][2];
+            Ss[(16 * rb + fg + 8) * 33 + col + 1] = sc[n][3];
+        }
+        __syncthreads();
+        // online softmax: warp w owns rows 8 w .. 8 w + 7, lane = key of the tile
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t r = 8 * warp + i, t = t0 + r / REP, kk = k0 + lane;
+            const bool ok = r < nrows && t < T && kk <= pos0 + t;
+            const float sv = ok ? Ss[r * 33 + lane] : -INFINITY;
+            const float m_old = mrow[r];
+            const float m_new = fmaxf(m_old, wmax(sv));
+            const float p = (ok && m_new > -INFINITY) ? expf(sv - m_new) : 0.f;
+            const float sum = wsum(p);
+            const float alpha = (m_old > -INFINITY) ? expf(m_old - m_new) : 1.f;   // nothing accumulated yet: nothing to rescale
+            Ss[r * 33 + lane] = p;
+            if (lane == 0) { mrow[r] = m_new; lrow[r] = lrow[r] * alpha + sum; arow[r] = alpha; }
+        }
+        __syncthreads();
+        // output of rows [16 rb, +16) x dims [DH/2 wh, +DH/2): rescale, then += P V
+        const float al0 = arow[16 * rb + fg], al1 = arow[16 * rb + fg + 8];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { acc[n][0] *= al0; acc[n][1] *= al0; acc[n][2] *= al1; acc[n][3] *= al1; }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a[4];
+            a[0] = to_tf32(Ss[(16 * rb + fg) * 33 + 8 * ks + ft]);
+            a[1] = to_tf32(Ss[(16 * rb + fg + 8) * 33 + 8 * ks + ft]);
+            a[2] = to_tf32(Ss[(16 * rb + fg) * 33 + 8 * ks + ft + 4]);
+            a[3] = to_tf32(Ss[(16 * rb + fg + 8) * 33 + 8 * ks + ft + 4]);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int dim = (DH / 2) * wh + 8 * n + fg;
+                mma_tf32(acc[n], a, Vu[(8 * ks + ft) * VS + dim], Vu[(8 * ks + ft + 4) * VS + dim]);
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const uint32_t r0 = 16 * rb + fg, r1 = r0 + 8;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint32_t row = half ? r1 : r0, t = t0 + row / REP;
+            if (row >= nrows || t >= T) continue;
+            const float inv = 1.0f / lrow[row];
+            float* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + (DH / 2) * wh + 2 * ft;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+        }
+    }
+}
+
+// rows [pos0, pos0 + T) of an fp32 cache [KVH][ctx][dh] into a lane K/V slot of the same shape (half or fp32)
+template <typename TO>
+__global__ void kv_rows_to_slot_kernel(const float* __restrict__ src, TO* __restrict__ dst, uint32_t KVH, uint32_t ctx, uint32_t dh,
+                                       uint32_t pos0, uint32_t T) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per = (size_t)T * dh;
+    if (i >= (size_t)KVH * per) return;
+    const size_t kv = i / per, off = ((size_t)kv * ctx + pos0) * dh + i % per;
+    if constexpr (sizeof(TO) == 2) dst[off] = __float2half_rn(src[off]); else dst[off] = src[off];
+}
+
+struct Layer {
+    const uint8_t *q, *k, *v, *o, *gate, *up, *down;            // device block streams
+    float *rms1 = nullptr, *rms2 = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr;
+    float *kc = nullptr, *vc = nullptr;                         // device caches
+    float *kc_host = nullptr, *vc_host = nullptr;               // the caller's arrays
+    bool pinned_k = false, pinned_v = false;
+    cudaEvent_t kv_ready = nullptr, kv_done = nullptr;
+};
+struct Stack {
+    int L = 0, D = 0, H = 0, KVH = 0, dh = 0, F = 0, ctx = 0, REP = 0, QD = 0, KVD = 0;
+    float theta = 0.f, eps = 0.f;
+    unsigned dtype = DT_Q4_0;
+    std::vector<Layer> layers;
+    float *x = nullptr, *h = nullptr, *qkv = nullptr, *ao = nullptr, *h2 = nullptr, *g = nullptr, *u = nullptr;
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    int cap_T = 0;
+    cudaStream_t copy = nullptr;
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+    ~Stack() {
+        State& s = state();
+        if (s.ready) cudaStreamSynchronize(s.stream);
+        if (copy) { cudaStreamSynchronize(copy); cudaStreamDestroy(copy); }
+        for (Layer& l : layers) {
+            for (float* p : {l.rms1, l.rms2, l.qb, l.kb, l.vb, l.kc, l.vc}) if (p) cudaFree(p);
+            if (l.pinned_k) cudaHostUnregister(l.kc_host);
+            if (l.pinned_v) cudaHostUnregister(l.vc_host);
+            if (l.kv_ready) cudaEventDestroy(l.kv_ready);
+            if (l.kv_done) cudaEventDestroy(l.kv_done);
+        }
+        free_scratch();
+        if (t0) cudaEventDestroy(t0);
+        if (t1) cudaEventDestroy(t1);
+        cudaGetLastError();
+    }
+    void free_scratch() {
+        for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u}) if (*p) { cudaFree(*p); *p = nullptr; }
+        if (ws) { cudaFree(ws); ws = nullptr; }
+        cap_T = 0;
+    }
+};
+
+// the prefill in flight between begin and end (one at a time, like the reference's single shared event)
+struct Live { Stack* c = nullptr; int n = 0; bool failed = false; } g_live;
+double g_gpu_ms = 0.0;
+
+float* dev_copy(const float* host, size_t n) {
+    float* d = nullptr;
+    if (cudaMalloc(&d, n * 4) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaMemcpy(d, host, n * 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); cudaFree(d); return nullptr; }
+    return d;
+}
+
+bool ensure_scratch(Stack& c, int T) {
+    if (T <= c.cap_T) return true;
+    State& s = state();
+    cudaStreamSynchronize(s.stream);
+    c.free_scratch();
+    auto mk = [&](size_t floats) { float* p = nullptr; if (cudaMalloc(&p, floats * 4) != cudaSuccess) { cudaGetLastError(); p = nullptr; } return p; };
+    const size_t t = (size_t)T;
+    c.x = mk(t * c.D); c.h = mk(t * c.D); c.h2 = mk(t * c.D); c.qkv = mk(t * (c.QD + 2 * c.KVD)); c.ao = mk(t * c.QD);
+    c.g = mk(t * c.F); c.u = mk(t * c.F);
+    size_t need = 0;
+    for (auto nk : {std::pair<int, int>{c.QD, c.D}, {c.KVD, c.D}, {c.D, c.QD}, {c.F, c.D}, {c.D, c.F}})
+        need = std::max(need, gemm_workspace_bytes((unsigned)T, (unsigned)nk.first, (unsigned)nk.second));
+    if (cudaMalloc(&c.ws, need) != cudaSuccess) { cudaGetLastError(); c.ws = nullptr; }
+    c.ws_bytes = need;
+    if (!(c.x && c.h && c.h2 && c.qkv && c.ao && c.g && c.u && c.ws)) { c.free_scratch(); return fail("llama stack: out of device memory for a %d-token batch", T); }
+    c.cap_T = T;
+    return true;
+}
+
+template <int DH> constexpr size_t attn_smem() { return (size_t)(64 * (DH + 4) + 32 * (DH + 4) + 32 * (DH + 8) + 64 * 33 + 3 * 64) * 4; }
+template <int DH>
+bool attn_ready() {
+    constexpr size_t smem = attn_smem<DH>();
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(prefill_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return fail("llama stack: cannot raise the attention kernel's shared memory limit");
+        attr = true;
+    }
+    return true;
+}
+
+bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
+    Layer& L = c.layers[(size_t)l];
+    const unsigned D = (unsigned)c.D, QD = (unsigned)c.QD, KVD = (unsigned)c.KVD, F = (unsigned)c.F, dh = (unsigned)c.dh;
+    const unsigned ld = QD + 2 * KVD, Tn = (unsigned)T;
+    const float scale = 1.0f / std::sqrt((float)dh);
+    auto gemm = [&](const float* A, const uint8_t* W, float* Cm, unsigned ldc, unsigned N, unsigned K) {
+        return launch_gemm(A, W, Cm, ldc, Tn, N, K, c.dtype, c.ws, c.ws_bytes, st);
+    };
+    // 1. norm, q / k / v into one [T][QD + 2 KVD] buffer
+    rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms1, c.h, D, c.eps); note_launch();
+    if (!gemm(c.h, L.q, c.qkv, ld, QD, D) || !gemm(c.h, L.k, c.qkv + QD, ld, KVD, D) || !gemm(c.h, L.v, c.qkv + QD + KVD, ld, KVD, D)) return false;
+    if (L.qb) {
+        bias_rows_kernel<<<(unsigned)(((size_t)T * QD + 255) / 256), 256, 0, st>>>(c.qkv, L.qb, QD, ld, Tn);
+        bias_rows_kernel<<<(unsigned)(((size_t)T * KVD + 255) / 256), 256, 0, st>>>(c.qkv + QD, L.kb, KVD, ld, Tn);
+        bias_rows_kernel<<<(unsigned)(((size_t)T * KVD + 255) / 256), 256, 0, st>>>(c.qkv + QD + KVD, L.vb, KVD, ld, Tn);
+        note_launch(3);
+    }
+    // 2. rope + K/V rows into the caches; the rows then travel to the caller's arrays on the copy stream
+    unsigned tbl_n = 0;
+    const float* tbl = lane_rope_table(dh, (unsigned)(pos0 + T), c.theta, &tbl_n);
+    if (!tbl) return false;
+    const size_t per_tok = (size_t)(c.H + c.KVH) * (dh / 2) + (size_t)c.KVH * dh;
+    rope_append_kernel<<<(unsigned)(((size_t)T * per_tok + 255) / 256), 256, 0, st>>>(c.qkv, ld, L.kc, L.vc, (unsigned)c.H, (unsigned)c.KVH, dh,
+                                                                                     (unsigned)c.ctx, (unsigned)pos0, Tn, (const float2*)tbl, tbl_n);
+    note_launch();
+    cudaEventRecord(L.kv_ready, st);
+    cudaStreamWaitEvent(c.copy, L.kv_ready, 0);
+    const size_t pitch = (size_t)c.ctx * dh * 4, width = (size_t)T * dh * 4, first = (size_t)pos0 * dh;
+    cudaMemcpy2DAsync(L.kc_host + first, pitch, L.kc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
+    cudaMemcpy2DAsync(L.vc_host + first, pitch, L.vc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
+    cudaEventRecord(L.kv_done, c.copy);
+    // 3. causal attention of the batch over [0, pos]
+    const unsigned BT = 64u / (unsigned)c.REP;
+    const dim3 grid((Tn + BT - 1) / BT, (unsigned)c.KVH);
+    if (dh == 128) {
+        if (!attn_ready<128>()) return false;
+        prefill_attn_kernel<128><<<grid, 256, attn_smem<128>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+    } else {
+        if (!attn_ready<64>()) return false;
+        prefill_attn_kernel<64><<<grid, 256, attn_smem<64>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+    }
+    note_launch();
+    // 4. o + residual, norm, gate / up, silu * up, down + residual
+    if (!gemm(c.ao, L.o, c.h2, D, D, QD)) return false;
+    if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
+    rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms2, c.h, D, c.eps); note_launch();
+    if (!gemm(c.h, L.gate, c.g, F, F, D) || !gemm(c.h, L.up, c.u, F, F, D)) return false;
+    if (!launch_silu_mul(c.g, c.u, Tn * F, st)) return false;
+    if (!gemm(c.g, L.down, c.h2, D, D, F)) return false;
+    if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
+    return check_launch("llama stack layer");
+}
+
+// Enqueue the whole batch: x up, rows [0, pos0) of the caches up, every layer.
+bool enqueue(Stack& c, const float* x, int T, int pos0) {
+    State& s = state();
+    if (T < 2 || pos0 < 0 || pos0 + T > c.ctx) return fail("llama stack: batch of %d tokens at position %d does not fit (T >= 2, context %d)", T, pos0, c.ctx);
+    if (!x) return fail("llama stack: null activations");
+    if ((size_t)T * (size_t)c.F > 0xffffffffull) return fail("llama stack: batch too long");
+    if (!ensure_scratch(c, T)) return false;
+    cudaEventRecord(c.t0, s.stream);
+    if (cudaMemcpyAsync(c.x, x, (size_t)T * c.D * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("llama stack: x upload");
+    if (pos0 > 0) {
+        // what unified memory would show the reference's GPU: the caller's earlier rows, whoever wrote them
+        const size_t pitch = (size_t)c.ctx * c.dh * 4, width = (size_t)pos0 * c.dh * 4;
+        for (Layer& L : c.layers) {
+            cudaMemcpy2DAsync(L.kc, pitch, L.kc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
+            cudaMemcpy2DAsync(L.vc, pitch, L.vc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
+        }
+        if (!check_launch("llama stack: cache upload")) return false;
+    }
+    for (int l = 0; l < c.L; ++l)
+        if (!encode_layer(c, l, T, pos0, s.stream)) return false;
+    cudaEventRecord(c.t1, s.stream);
+    return check_launch("llama stack");
+}
+
+// Bounded wait for an event (the reference's 30 s deadline, metal_llama.h:856-876).
+bool wait_event(cudaEvent_t ev, const char* what) {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30);
+    for (;;) {
+        const cudaError_t e = cudaEventQuery(ev);
+        if (e == cudaSuccess) return true;
+        if (e != cudaErrorNotReady) return fail("llama stack: %s: %s", what, cudaGetErrorString(e));
+        if (std::chrono::steady_clock::now() > deadline) return fail("llama stack: %s did not finish within 30 s", what);
+    }
+}
+
+void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
+    if (!d) { fail("llama stack: null description"); return nullptr; }
+    if (!ensure_init(-1)) return nullptr;
+    if (d->L <= 0 || d->D <= 0 || d->H <= 0 || d->KVH <= 0 || d->F <= 0 || d->ctx <= 0 || !d->layers || d->H % d->KVH || (d->dh & 1) ||
+        d->H / d->KVH > 64) { fail("llama stack: invalid dimensions"); return nullptr; }
+    if (d->dh != 64 && d->dh != 128) { fail("llama stack: head dimension %d (64 and 128 are built)", d->dh); return nullptr; }
+    if (d->D % 4 || (d->H * d->dh) % 4 || (d->KVH * d->dh) % 4) { fail("llama stack: row widths must be multiples of 4"); return nullptr; }
+    State& s = state();
+    auto c = std::make_unique<Stack>();
+    c->L = d->L; c->D = d->D; c->H = d->H; c->KVH = d->KVH; c->dh = d->dh; c->F = d->F; c->ctx = d->ctx;
+    c->REP = d->H / d->KVH; c->QD = d->H * d->dh; c->KVD = d->KVH * d->dh; c->theta = d->theta; c->eps = d->eps; c->dtype = dtype;
+    if (!weight_bytes(dtype, 1, (size_t)c->D) || !weight_bytes(dtype, 1, (size_t)c->F) || !weight_bytes(dtype, 1, (size_t)c->QD)) {
+        fail("llama stack: rows are not whole blocks of dtype %u", dtype); return nullptr;
+    }
+    if (cudaStreamCreateWithFlags(&c->copy, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreate(&c->t0) != cudaSuccess ||
+        cudaEventCreate(&c->t1) != cudaSuccess) { check_launch("llama stack: stream"); return nullptr; }
+    c->layers.resize((size_t)c->L);
+    const size_t cache_floats = (size_t)c->KVD * c->ctx;
+    for (int l = 0; l < c->L; ++l) {
+        const tm_llama_gpu_layer& src = d->layers[l];
+        Layer& L = c->layers[(size_t)l];
+        if (!src.q || !src.k || !src.v || !src.o || !src.gate || !src.up || !src.down || !src.rms1 || !src.rms2 || !src.kc || !src.vc) {
+            fail("llama stack: layer %d has a null pointer", l); return nullptr;
+        }
+        auto reg = [&](const void* p, int rows, int cols) -> const uint8_t* {
+            const size_t bytes = weight_bytes(dtype, (size_t)rows, (size_t)cols);
+            uint64_t woff = 0;
+            const int id = tm_cuda_tok_wbuf(p, bytes, d->map_base, d->map_size, d->map_base ? 1 : 0, &woff);
+            return id < 0 ? nullptr : lane_weight_ptr(id, woff, bytes);
+        };
+        L.q = reg(src.q, c->QD, c->D); L.k = reg(src.k, c->KVD, c->D); L.v = reg(src.v, c->KVD, c->D); L.o = reg(src.o, c->D, c->QD);
+        L.gate = reg(src.gate, c->F, c->D); L.up = reg(src.up, c->F, c->D); L.down = reg(src.down, c->D, c->F);
+        if (!(L.q && L.k && L.v && L.o && L.gate && L.up && L.down)) return nullptr;
+        L.rms1 = dev_copy(src.rms1, (size_t)c->D); L.rms2 = dev_copy(src.rms2, (size_t)c->D);
+        if (src.q_bias && src.k_bias && src.v_bias) {
+            L.qb = dev_copy(src.q_bias, (size_t)c->QD); L.kb = dev_copy(src.k_bias, (size_t)c->KVD); L.vb = dev_copy(src.v_bias, (size_t)c->KVD);
+            if (!(L.qb && L.kb && L.vb)) { fail("llama stack: out of device memory"); return nullptr; }
+        }
+        if (cudaMalloc(&L.kc, cache_floats * 4) != cudaSuccess || cudaMalloc(&L.vc, cache_floats * 4) != cudaSuccess || !L.rms1 || !L.rms2) {
+            cudaGetLastError(); fail("llama stack: out of device memory for the K/V caches"); return nullptr;
+        }
+        cudaMemsetAsync(L.kc, 0, cache_floats * 4, s.stream); cudaMemsetAsync(L.vc, 0, cache_floats * 4, s.stream);
+        L.kc_host = src.kc; L.vc_host = src.vc;
+        // page-locking the caller's arrays makes the row copies asynchronous; where it is refused they are staged
+        L.pinned_k = cudaHostRegister(L.kc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
+        L.pinned_v = cudaHostRegister(L.vc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
+        cudaGetLastError();
+        if (cudaEventCreateWithFlags(&L.kv_ready, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&L.kv_done, cudaEventDisableTiming) != cudaSuccess) { check_launch("llama stack: events"); return nullptr; }
+    }
+    if (!sync_stream(s.stream, "llama stack: create")) return nullptr;
+    return c.release();
+}
+
+}  // namespace
+}  // namespace tmc
+
+using namespace tmc;
+
+extern "C" {
+
+void* tm_cuda_llama_create(const tm_llama_gpu_desc* d) { return create(d, DT_Q4_0); }
+void* tm_cuda_llama_create_dt(const tm_llama_gpu_desc* d, unsigned dtype) {
+    if (!block_elems(dtype) || dtype == DT_F16) { fail("llama stack: dtype %u is not a block format", dtype); return nullptr; }
+    return create(d, dtype);
+}
+
+void tm_cuda_llama_destroy(void* h) {
+    Stack* c = static_cast<Stack*>(h);
+    if (g_live.c == c) g_live = Live{};
+    delete c;
+}
+
+int tm_cuda_llama_prefill_begin(void* h, const float* x, int T, int pos0) {
+    Stack* c = static_cast<Stack*>(h);
+    if (!c) { fail("llama stack: null handle"); return 0; }
+    if (g_live.n) (void)tm_cuda_llama_prefill_end();               // drain an unfinished one, best effort (metal_llama.h:971)
+    if (!enqueue(*c, x, T, pos0)) return 0;
+    g_live.c = c; g_live.n = c->L; g_live.failed = false;
+    return 1;
+}
+
+int tm_cuda_llama_prefill_wait_layer(int l) {
+    if (l < 0 || l >= g_live.n || !g_live.c) { fail("llama stack: no layer %d in flight", l); return 0; }
+    if (g_live.failed) return 0;
+    if (!wait_event(g_live.c->layers[(size_t)l].kv_done, "layer")) { g_live.failed = true; return 0; }
+    return 1;
+}
+
+int tm_cuda_llama_prefill_end(void) {
+    if (!g_live.c || !g_live.n) return 1;
+    bool ok = true;
+    for (int l = 0; l < g_live.n; ++l)
+        if (!tm_cuda_llama_prefill_wait_layer(l)) ok = false;
+    State& s = state();
+    ok = wait_event(g_live.c->t1, "batch") && ok;
+    ok = sync_stream(s.stream, "llama stack") && ok;
+    float ms = 0.f;
+    if (ok && cudaEventElapsedTime(&ms, g_live.c->t0, g_live.c->t1) == cudaSuccess) g_gpu_ms = ms; else cudaGetLastError();
+    g_live.n = 0;
+    return ok ? 1 : 0;
+}
+
+double tm_cuda_llama_prefill_gpu_ms(void) { return g_gpu_ms; }
+
+int tm_cuda_llama_prefill(void* h, float* x, int T, int pos0) {
+    Stack* c = static_cast<Stack*>(h);
+    if (!c) { fail("llama stack: null handle"); return 0; }
+    if (!tm_cuda_llama_prefill_begin(h, x, T, pos0)) return 0;
+    State& s = state();
+    const bool copied = cudaMemcpyAsync(x, c->x, (size_t)T * c->D * 4, cudaMemcpyDeviceToHost, s.stream) == cudaSuccess;
+    const bool ok = tm_cuda_llama_prefill_end() != 0;
+    if (!copied) { check_launch("llama stack: x download"); return 0; }
+    return ok ? 1 : 0;
+}
+
+int tm_cuda_llama_kv_to_slots(void* h, int l, int kcslot, int vcslot, int pos0, int T) {
+    Stack* c = static_cast<Stack*>(h);
+    if (!c || l < 0 || l >= c->L || pos0 < 0 || T <= 0 || pos0 + T > c->ctx) { fail("llama stack: bad K/V row range"); return 0; }
+    State& s = state();
+    const size_t elems = (size_t)c->KVD * c->ctx, es = s.kv_half ? 2 : 4;
+    uint8_t* kd = lane_slot_ptr(kcslot, elems * es, "llama_kv_to_slots");
+    uint8_t* vd = lane_slot_ptr(vcslot, elems * es, "llama_kv_to_slots");
+    if (!kd || !vd) return 0;
+    const Layer& L = c->layers[(size_t)l];
+    const unsigned blocks = (unsigned)(((size_t)c->KVH * T * c->dh + 255) / 256);
+    if (s.kv_half) {
+        kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.kc, (__half*)kd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);
+        kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.vc, (__half*)vd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);
+    } else {
+        kv_rows_to_slot_kernel<float><<<blocks, 256, 0, s.stream>>>(L.kc, (float*)kd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);
+        kv_rows_to_slot_kernel<float><<<blocks, 256, 0, s.stream>>>(L.vc, (float*)vd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);
+    }
+    note_launch(2);
+    return check_launch("llama_kv_to_slots") ? 1 : 0;
+}
+
+// the reference's names (tensormark/metal_shim.mm:153-160)
+void* tm_metal_llama_create(const tm_llama_gpu_desc* d) { return tm_cuda_llama_create(d); }
+int tm_metal_llama_prefill(void* h, float* x, int T, int pos0) { return tm_cuda_llama_prefill(h, x, T, pos0); }
+int tm_metal_llama_prefill_begin(void* h, const float* x, int T, int pos0) { return tm_cuda_llama_prefill_begin(h, x, T, pos0); }
+int tm_metal_llama_prefill_wait_layer(int l) { return tm_cuda_llama_prefill_wait_layer(l); }
+int tm_metal_llama_prefill_end(void) { return tm_cuda_llama_prefill_end(); }
+double tm_metal_llama_prefill_gpu_ms(void) { return tm_cuda_llama_prefill_gpu_ms(); }
+void tm_metal_llama_destroy(void* h) { tm_cuda_llama_destroy(h); }
+
+}  // extern "C"

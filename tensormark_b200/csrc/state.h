@@ -97,6 +97,11 @@ bool ensure_init(int device);
 bool harvest_status(const char* where);
 bool sync_stream(cudaStream_t st, const char* where);
 const uint8_t* cached_weights(const void* host, size_t bytes);
+// token_lane.cu, for the prefill layer stack: device address of a registered weight range (nullptr + latched error when
+// outside the handle), the shared (cos, sin) rope table grown to `need` positions, a slot's device address.
+const uint8_t* lane_weight_ptr(int wid, uint64_t woff, size_t bytes);
+const float* lane_rope_table(unsigned dh, unsigned need, float theta, unsigned* entries);
+uint8_t* lane_slot_ptr(int sid, size_t bytes, const char* who);
 SegTable one_segment(unsigned N);
 bool make_segments(SegTable& t, unsigned N, const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg);
 

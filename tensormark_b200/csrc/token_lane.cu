@@ -150,6 +150,15 @@ void gemv_common(int xslot, int wid, int yslot, size_t yoff, unsigned N, unsigne
 
 }  // namespace
 
+// What the prefill layer stack (llama_stack.cu) shares with the lane: the resident weights, the rope table, the slots.
+const uint8_t* lane_weight_ptr(int wid, uint64_t woff, size_t bytes) { return weight_ptr(wid, woff, bytes, "llama stack"); }
+const float* lane_rope_table(unsigned dh, unsigned need, float theta, unsigned* entries) {
+    if (!ensure_rope(dh, need, theta)) return nullptr;
+    if (entries) *entries = state().rope_cap * (dh / 2);
+    return state().rope_tbl;
+}
+uint8_t* lane_slot_ptr(int sid, size_t bytes, const char* who) { return slot_ptr(sid, bytes, who); }
+
 }  // namespace tmc
 
 using namespace tmc;

@@ -48,7 +48,7 @@ TMCHAIN_API void* tmchain_create(const int* cfg, float theta, float eps, const v
 }
 // Also drops the lane's weight registrations: they are keyed by the host addresses of this model's tensors.
 TMCHAIN_API void tmchain_destroy(void* p) {
-    delete static_cast<Holder*>(p);
+    delete static_cast<Holder*>(p);                        // the layer stack goes first: it points into the resident weights
     tm_cuda_release_weights();
 }
 TMCHAIN_API int tmchain_seen(void* p) { return static_cast<Holder*>(p)->m->seen; }
@@ -111,6 +111,17 @@ TMCHAIN_API int tmchain_feed(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_feed(toks, n); }
     catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
+
+// A prompt of n >= 2 tokens through the batched layer stack; returns the model's next token or -1.
+TMCHAIN_API int tmchain_prefill(void* p, const int* toks, int n) {
+    try { return static_cast<Holder*>(p)->m->gpu_prefill(toks, n); }
+    catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+TMCHAIN_API int tmchain_prefill_prepare(void* p) {
+    try { static_cast<Holder*>(p)->m->gpu_prefill_prepare(); return 1; }
+    catch (const std::exception& e) { g_err = e.what(); return 0; }
+}
+TMCHAIN_API double tmchain_prefill_gpu_ms(void* p) { return static_cast<Holder*>(p)->m->last_prefill_gpu_ms(); }
 
 // ---- .tmq containers (include/tmq_reader.h) ---------------------------------------------------------------
 // Open a container, make the named tensors resident under one weight handle with aligned offsets, and keep the

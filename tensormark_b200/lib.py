@@ -78,6 +78,15 @@ SIGNATURES = {
     "tm_cuda_tok_peek": (_u, [C.c_int, _u]),
     "tm_cuda_tok_gemv_fused": (None, [C.c_int, _sz, C.c_int, C.c_int, _sz, _vp, C.c_float, C.c_int, C.c_int, _sz, _u, _u, _u,
                                       C.POINTER(_u64), C.POINTER(_u), _u, C.c_int]),
+    "tm_cuda_llama_create": (_vp, [_vp]),
+    "tm_cuda_llama_create_dt": (_vp, [_vp, _u]),
+    "tm_cuda_llama_prefill": (C.c_int, [_vp, _vp, C.c_int, C.c_int]),
+    "tm_cuda_llama_prefill_begin": (C.c_int, [_vp, _vp, C.c_int, C.c_int]),
+    "tm_cuda_llama_prefill_wait_layer": (C.c_int, [C.c_int]),
+    "tm_cuda_llama_prefill_end": (C.c_int, []),
+    "tm_cuda_llama_prefill_gpu_ms": (C.c_double, []),
+    "tm_cuda_llama_destroy": (None, [_vp]),
+    "tm_cuda_llama_kv_to_slots": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tm_cuda_tok_qkv_post_at": (None, [C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_int]),
     "tm_cuda_tok_attn_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, _u, C.c_float, _u, C.c_int]),
     "tm_cuda_tok_attn_fused_at": (None, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_float, C.c_int]),

@@ -67,7 +67,7 @@ def chain_weight_bytes(cfg: dict) -> int:
 
 
 def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank: int = 0, world: int = 1, gather: str = "peer",
-                  dist=None, graph: bool = True, trace: bool = False) -> dict:
+                  dist=None, graph: bool = True, trace: bool = False, prefill: str = "feed") -> dict:
     """Feed `prompt_n` tokens, then time `steps` greedy tokens chosen on the GPU (CUDA events on the lane stream, max over
     ranks). world > 1: FFN and LM-head rows sharded over the ranks; the communicator (and, for gather == "peer", the peer
     arena) must exist already and `dist` is the initialised torch.distributed module (any backend). Returns the record
@@ -88,7 +88,13 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
     prompt = synth.make_tokens(prompt_n, cfg["V"], seed=5).astype(np.int32)
     stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
     t0 = time.perf_counter()
-    if not graph:
+    prefill_gpu_ms = None
+    if prefill == "stack" and world == 1 and prompt_n >= 2:
+        m.prefill_prepare()                                # one-time set-up (device caches, page-locked host arrays) is not prompt time
+        t0 = time.perf_counter()
+        nxt = m.prefill(prompt)                            # the batched layer stack (tensor-core GEMMs)
+        prefill_gpu_ms = m.prefill_gpu_ms()
+    elif not graph:
         last = None
         for t in prompt:
             last = m.forward(int(t))
@@ -96,6 +102,10 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
     else:
         nxt = m.feed(prompt)
     t_prompt = time.perf_counter() - t0
+    if graph:
+        # one untimed token: the chain's CUDA graph exists afterwards whichever way the prompt went in
+        one, _ = m.greedy(nxt, 1)
+        nxt = int(one[0])
     if dist is not None and world > 1:
         dist.barrier()
     if trace:                                               # drop the prompt's records: the log holds 8192 launches
@@ -131,6 +141,9 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
            "decode_tok_per_s": round(steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / steps, 4),
            "wall_tok_per_s": round(steps / wall, 1),
            "prompt_tok_per_s": round(prompt_n / t_prompt, 1),
+           "prompt_path": "layer stack" if prefill_gpu_ms is not None else "decode lane, token by token",
+           "prompt_gpu_ms": None if prefill_gpu_ms is None else round(prefill_gpu_ms, 3),
+           "prompt_tok_per_s_gpu": None if not prefill_gpu_ms else round(prompt_n / (prefill_gpu_ms * 1e-3), 1),
            "weight_bytes_per_token": wbytes,
            "weight_GBps": round(wbytes * steps / (dev_ms * 1e-3) / 1e9, 1),
            "kernels_encoded_per_chain_call": int(L.tm_cuda_launch_count()) - launches0,
@@ -160,7 +173,8 @@ def run_chain(args, L, torch, rank: int = 0, world: int = 1) -> None:
     t0 = time.perf_counter()
     w = synth.make_llama(cfg, seed=5)
     t_gen = time.perf_counter() - t0
-    rec = measure_chain(L, torch, cfg, w, args.prompt, args.steps, rank, world, args.gather, dist, not args.no_graph, args.trace)
+    rec = measure_chain(L, torch, cfg, w, args.prompt, args.steps, rank, world, args.gather, dist, not args.no_graph, args.trace,
+                        args.prefill)
     logits = rec.pop("logits")
     if args.dump_logits and rank == 0:
         np.save(args.dump_logits, logits)
@@ -185,6 +199,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--gather", choices=["nccl", "peer"], default="peer", help="--op chain on several GPUs: how shards are gathered")
     ap.add_argument("--no-graph", action="store_true", help="--op chain: one host call per op instead of the graph lane")
+    ap.add_argument("--prefill", choices=["feed", "stack"], default="feed",
+                    help="--op chain: the prompt token by token through the decode lane, or as one batch through the layer stack")
     ap.add_argument("--dump-logits", default="", help="--op chain: rank 0 saves the last step's logits to this .npy file")
     ap.add_argument("--trace", action="store_true", help="--op chain with TM_CUDA_TRACE=1: add the per-kernel timeline summary")
     ap.add_argument("--dtype", default="Q8_0", choices=sorted(NAMES))

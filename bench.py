@@ -298,7 +298,7 @@ def sharded_chain_record(L, lib, torch, dist, rank: int, world: int, prompt_n: i
     t0 = time.perf_counter()
     w = synth.make_llama(cfg, seed=5)
     build_s = time.perf_counter() - t0
-    one = run_case.measure_chain(L, torch, cfg, w, prompt_n, steps, 0, 1, "peer", None)
+    one = run_case.measure_chain(L, torch, cfg, w, prompt_n, steps, 0, 1, "peer", None, prefill="stack")
     ref_logits = one.pop("logits")
     one.pop("trace", None)
     bound_ms = run_case.chain_weight_bytes(cfg) / (measured_peak()[0] * 1e9) * 1e3
@@ -311,7 +311,7 @@ def sharded_chain_record(L, lib, torch, dist, rank: int, world: int, prompt_n: i
         one_ms = float(one_ms.item())
         chain.init_comm(L, rank, world)
         chain.init_peer(L, rank, world, chain.peer_arena_bytes(cfg))
-        sh = run_case.measure_chain(L, torch, cfg, w, prompt_n, steps, rank, world, "peer", dist)
+        sh = run_case.measure_chain(L, torch, cfg, w, prompt_n, steps, rank, world, "peer", dist, prefill="stack")
         got = sh.pop("logits")
         sh.pop("trace", None)
         scale = max(1.0, float(np.abs(ref_logits).max()))

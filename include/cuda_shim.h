@@ -17,7 +17,7 @@
  *     latches a sticky error that makes the next tok_end / tok_flush /
  *     tok_wait_pending return false. tm_cuda_last_error() names it.
  *   - dtype codes are the container's (tensormark/tmq.h:48-60):
- *     0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K, 6 Q6_K, 8 Q4_K.
+ *     0 Q8_0, 1 Q4_0, 3 F16, 4 Q4_1, 5 Q5_K, 6 Q6_K, 8 Q4_K, 9 GGUF-native Q4_0, 10 BF16.
  *   - Host-pointer entries are blocking and, like the reference's function-local
  *     caches, not thread-safe: one caller thread per process.
  *
@@ -44,6 +44,8 @@ extern "C" {
 #define TM_DT_Q5_K 5u
 #define TM_DT_Q6_K 6u
 #define TM_DT_Q4_K 8u
+#define TM_DT_GGUF_Q4_0 9u   /* GGUF's own Q4_0: split nibbles (tensormark/tmq.h:58, llama.h:4588-4597) */
+#define TM_DT_BF16 10u
 
 /* ---- library state ------------------------------------------------------- */
 /* Select the device for this process and create the lane stream. Called lazily
@@ -105,8 +107,12 @@ void tm_cuda_release_weights(void);
 /* ---- device-pointer kernels ---------------------------------------------- */
 /* Bytes of an N x K tensor of `dtype`; 0 when K is not whole blocks (tmq.h:124-133). */
 size_t tm_cuda_weight_bytes(unsigned dtype, size_t N, size_t K);
-/* y = W x. W must be 16-byte aligned. (metal.h:3457-3480 tok_gemv, 3647-3669 tok_gemv_kq) */
+/* y = W x. W must be 16-byte aligned. (metal.h:3457-3480 tok_gemv, 3647-3669 tok_gemv_kq; dtype 3 / 10: plain fp16 /
+ * bf16 rows, metal.h:575-613 f16_gemv_coop and 3693-3721 tok_gemv_h) */
 bool tm_cuda_gemv_q_dev(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype, void* stream);
+/* nblocks Q4_0 blocks in GGUF's split nibble order, rewritten in place in the container's interleaved order (what the
+ * reference's converter does on the host, convert_gguf.cpp:124-135): same scale, same codes, bit-identical weights. */
+bool tm_cuda_q4_0_from_gguf_dev(void* blocks, size_t nblocks, void* stream);
 /* Segmented GEMV: N total rows over nseg segments; segment s covers seg_rows[s]
  * rows whose blocks start seg_woff[s] bytes after W. One launch; every row is
  * computed exactly as the unsegmented kernel computes it. nseg <= 16.
@@ -191,6 +197,10 @@ void tm_cuda_tok_gemv_kq(int xslot, int wid, uint64_t woff, int yslot, size_t yo
                          unsigned dtype);
 void tm_cuda_tok_embed_q4(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D);  /* metal.h:3227-3240 */
 void tm_cuda_tok_embed_kq(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype);
+void tm_cuda_tok_gemv_h(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K);   /* F16 tensor; metal.h:3693-3721 */
+void tm_cuda_tok_embed_h(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D);           /* metal.h:3260-3271 */
+/* The same reorder for a registered weight range (blocking); afterwards the range is container Q4_0 (dtype 1). */
+bool tm_cuda_tok_wbuf_q4_from_gguf(int wid, uint64_t woff, size_t nblocks);
 void tm_cuda_tok_bias_qkv(int yslot, int biasslot, size_t bias_off, unsigned N);     /* metal.h:3672-3688 */
 void tm_cuda_tok_rmsnorm(int xslot, const void* w, int outslot, unsigned D, float eps);  /* metal.h:3722-3746 */
 void tm_cuda_tok_add(int a, int b, unsigned n);                                      /* metal.h:3747-3754 */
@@ -226,6 +236,8 @@ void tm_cuda_tok_attn_at(int qslot, int kcslot, int vcslot, int probslot, int ou
  * over [0, position] and the merge of its splits. qkvslot holds the token's un-rotated [q | k | v]; q is
  * not written back. probslot is scratch: (dh + 2) * H * 4 bytes per split, as many splits as fit up to
  * one CTA per SM. (metal.h:3950-4030, 4153-4222 in one dispatch.) */
+/* The merge of the splits uses one counter per K/V head that is shared by every call of this entry in the process:
+ * calls must not overlap on the GPU (the lane issues them on its one stream, which orders them). */
 void tm_cuda_tok_attn_fused_at(int qkvslot, int kcslot, int vcslot, int probslot, int outslot, unsigned H, unsigned KVH,
                                unsigned dh, unsigned ctx, float scale, float theta, int stateslot);
 void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot);

@@ -394,50 +394,35 @@ public:
         return (int)next;
     }
 
-    // A prompt of n >= 2 tokens through the batched layer stack (tensormark/llama.h:6305-6352: embed the rows on the
-    // host, tm_*_llama_prefill, final norm + LM head on the last row), then the stack's K/V rows into the decode lane's
-    // caches so that a chain continues from position seen + n. Returns the token the model chooses after the prompt.
-    // Single GPU (the stack does not shard).
+    // A prompt of n >= 3 tokens: the first n - 1 through the batched layer stack (tensormark/llama.h:6305-6352: embed
+    // the rows on the host, tm_*_llama_prefill), the stack's K/V rows into the decode lane's caches on the device, and
+    // the last token through the decode lane, which leaves its logits and the model's next token exactly as gpu_feed
+    // does. Returns that token. With a row-sharded model every rank runs the stack on the whole prompt (attention and
+    // its K/V caches are replicated); only the last token's FFN and LM head are sharded.
     int gpu_prefill(const int* toks, int n) {
-        if (n < 2) throw std::invalid_argument("llama: the layer stack takes batches of two or more tokens");
+        if (n < 3) throw std::invalid_argument("llama: the layer stack takes prompts of three or more tokens");
         if (seen + n > d_.ctx) throw std::invalid_argument("llama: prompt exceeds context");
         if (chain_n_) throw std::runtime_error("llama: chain already running");
-        if (d_.world > 1) throw std::invalid_argument("llama: the layer stack runs on one GPU");
         gpu_token_prologue();
         ensure_stack();
+        const int m = n - 1;
         const size_t D = (size_t)d_.D, row_bytes = tm_cuda_weight_bytes(d_.dt_embed, 1, D);
-        std::vector<float> x((size_t)n * D);
-        for (int i = 0; i < n; ++i) {
+        std::vector<float> x((size_t)m * D);
+        for (int i = 0; i < n; ++i)
             if (toks[i] < 0 || toks[i] >= d_.V) throw std::invalid_argument("llama: token id out of range");
+        for (int i = 0; i < m; ++i)
             tmq::dequantize_row(d_.dt_embed, (const uint8_t*)d_.embed + (size_t)toks[i] * row_bytes, x.data() + (size_t)i * D, D);
-        }
-        if (!tm_cuda_llama_prefill(stack_, x.data(), n, seen))
+        if (!tm_cuda_llama_prefill(stack_, x.data(), m, seen))
             throw std::runtime_error(std::string("cuda: layer stack prefill failed: ") + tm_cuda_last_error());
         for (int l = 0; l < d_.L; ++l)
-            if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, n))
+            if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, m))
                 throw std::runtime_error(std::string("cuda: K/V hand-over failed: ") + tm_cuda_last_error());
-        // last row -> final norm -> LM head -> greedy choice, on the lane
-        const unsigned cap = (unsigned)d_.ctx + 1;
-        std::vector<unsigned> t((size_t)cap, 0xFFFFFFFFu);
-        if (!tm_cuda_tok_reserve(SLOT_TOK, sizeof(unsigned) * (size_t)cap) ||
-            !tm_cuda_tok_upload(SLOT_TOK, 0, t.data(), sizeof(unsigned) * (size_t)cap) ||
-            !tm_cuda_tok_upload(SLOT_X, 0, x.data() + (size_t)(n - 1) * D, D * 4))
-            throw std::runtime_error("cuda: prompt result upload failed");
-        if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
-        tm_cuda_tok_rmsnorm(SLOT_X, d_.rmsf, SLOT_XF, (unsigned)d_.D, d_.eps);
-        tm_cuda_tok_gemv_kq(SLOT_XF, head_.id, head_.woff, SLOT_LOGITS, 0, (unsigned)d_.V, (unsigned)d_.D, d_.dt_head);
-        tm_cuda_tok_argmax(SLOT_LOGITS, SLOT_TOK, 0, (unsigned)d_.V);
-        if (!tm_cuda_tok_end(SLOT_LOGITS, logits_.data(), (unsigned)d_.V))
-            throw std::runtime_error(std::string("cuda: prompt head failed: ") + tm_cuda_last_error());
-        unsigned next = 0;
-        if (!tm_cuda_tok_download(SLOT_TOK, 0, &next, sizeof next)) throw std::runtime_error("cuda: token download failed");
-        seen += n;
-        return (int)next;
+        seen += m;
+        return gpu_feed(toks + m, 1);
     }
     double last_prefill_gpu_ms() const { return tm_cuda_llama_prefill_gpu_ms(); }
     // Creates the layer stack ahead of the first gpu_prefill (it is otherwise created by it).
     void gpu_prefill_prepare() {
-        if (d_.world > 1) throw std::invalid_argument("llama: the layer stack runs on one GPU");
         gpu_token_prologue();
         ensure_stack();
     }

@@ -66,19 +66,20 @@ static_assert(sizeof(BlockQ4_K) == 144 && alignof(BlockQ4_K) == 1);
 static_assert(sizeof(BlockQ5_K) == 176 && alignof(BlockQ5_K) == 1);
 static_assert(sizeof(BlockQ6_K) == 210 && alignof(BlockQ6_K) == 1);
 
-enum class Dtype : std::uint32_t { Q8_0 = 0, Q4_0 = 1, F32 = 2, F16 = 3, Q4_1 = 4, Q5_K = 5, Q6_K = 6, Q4_K = 8 };
+enum class Dtype : std::uint32_t { Q8_0 = 0, Q4_0 = 1, F32 = 2, F16 = 3, Q4_1 = 4, Q5_K = 5, Q6_K = 6, TQ2 = 7, Q4_K = 8, GGUF_Q4_0 = 9, BF16 = 10 };
 
 constexpr std::uint32_t block_elems(std::uint32_t dtype) {
     switch (dtype) {
-        case 0: case 1: case 4: return 32;
+        case 0: case 1: case 4: case 9: return 32;
         case 5: case 6: case 8: return 256;
-        case 2: case 3: return 1;
+        case 7: return 128;
+        case 2: case 3: case 10: return 1;
         default: return 0;
     }
 }
 constexpr std::size_t block_bytes(std::uint32_t dtype) {
     switch (dtype) {
-        case 0: return 34; case 1: return 18; case 2: return 4; case 3: return 2;
+        case 0: case 7: return 34; case 1: case 9: return 18; case 2: return 4; case 3: case 10: return 2;
         case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144;
         default: return 0;
     }
@@ -259,6 +260,43 @@ inline void dequantize_row_q6_K(const BlockQ6_K* in, float* x, std::size_t n) {
     }
 }
 
+// TQ2 (container dtype 7): 34-byte blocks of 128 ternary-coded weights, four 2-bit codes per byte, low bits first,
+// w = (code - 1) * d (tensormark/quant.h:452-456, 507-515).
+struct BlockTq2_34x128 {
+    std::uint16_t d_fp16;
+    std::uint8_t qs[32];
+} __attribute__((packed));
+static_assert(sizeof(BlockTq2_34x128) == 34 && alignof(BlockTq2_34x128) == 1);
+inline void dequantize_row_tq2_34x128(const BlockTq2_34x128* in, float* x, std::size_t n) {
+    detail::need_rows(in, x, n, 128);
+    for (std::size_t b = 0; b < n / 128; ++b, x += 128) {
+        const float d = fp16_to_fp32(in[b].d_fp16);
+        for (int j = 0; j < 128; ++j) x[j] = static_cast<float>(static_cast<int>((in[b].qs[j >> 2] >> (2 * (j & 3))) & 3u) - 1) * d;
+    }
+}
+
+// GGUF's own Q4_0 (container dtype 9): split nibbles, byte j = elements j | j + 16 (tensormark/llama.h:4588-4597).
+inline void dequantize_row_gguf_q4_0(const BlockQ4_0* in, float* x, std::size_t n) {
+    detail::need_rows(in, x, n, kBlock);
+    for (std::size_t b = 0; b < n / kBlock; ++b, x += kBlock) {
+        const float d = fp16_to_fp32(in[b].d_fp16);
+        for (int j = 0; j < 16; ++j) {
+            x[j] = d * static_cast<float>((in[b].qs[j] & 15) - 8);
+            x[j + 16] = d * static_cast<float>((in[b].qs[j] >> 4) - 8);
+        }
+    }
+}
+// A split-nibble block rewritten as the container's interleaved Q4_0 block: same scale, same 32 codes, so the weights
+// are bit-identical (what tensormark/convert_gguf.cpp:124-135 does when it converts a GGUF file). src may equal dst.
+inline void q4_split_to_interleaved(const BlockQ4_0* src, BlockQ4_0* dst, std::size_t nblocks) {
+    for (std::size_t b = 0; b < nblocks; ++b) {
+        std::uint8_t code[32];
+        for (int j = 0; j < 16; ++j) { code[j] = src[b].qs[j] & 15; code[j + 16] = static_cast<std::uint8_t>(src[b].qs[j] >> 4); }
+        dst[b].d_fp16 = src[b].d_fp16;
+        for (int j = 0; j < 16; ++j) dst[b].qs[j] = static_cast<std::uint8_t>(code[2 * j] | (code[2 * j + 1] << 4));
+    }
+}
+
 // Dequantize `n` weights of any block dtype served by the matmul path.
 inline void dequantize_row(std::uint32_t dtype, const void* in, float* x, std::size_t n) {
     switch (dtype) {
@@ -267,7 +305,9 @@ inline void dequantize_row(std::uint32_t dtype, const void* in, float* x, std::s
         case 4: dequantize_row_q4_1(static_cast<const BlockQ4_1*>(in), x, n); break;
         case 5: dequantize_row_q5_K(static_cast<const BlockQ5_K*>(in), x, n); break;
         case 6: dequantize_row_q6_K(static_cast<const BlockQ6_K*>(in), x, n); break;
+        case 7: dequantize_row_tq2_34x128(static_cast<const BlockTq2_34x128*>(in), x, n); break;
         case 8: dequantize_row_q4_K(static_cast<const BlockQ4_K*>(in), x, n); break;
+        case 9: dequantize_row_gguf_q4_0(static_cast<const BlockQ4_0*>(in), x, n); break;
         default: throw std::invalid_argument("dequantize_row: dtype is not a block format");
     }
 }

@@ -3,8 +3,10 @@
 // Mirror of the container half of the reference's tensormark/tmq.h: the dtype geometry (83-133), the
 // record type and THE index parser both of its readers share (136-238, same accept / reject rules) and
 // the mmap-backed reader `Mapped` (248-463) reduced to what the matmul path needs: open, the tensor
-// table, find. Wiring policy (mlock, TM_RESIDENT), the demand-paged reader and the GGUF-native reader
-// are outside this path.
+// table, find. A file that starts with "GGUF" is read natively (tmq.h:434-463): its index comes from
+// include/gguf_reader.h, GGUF types map to container dtypes (GGUF's Q4_0 to dtype 9, whose nibble order differs
+// from the container's Q4_0), and only the text model's tensors are kept (embedding, head, final norm, layers).
+// Wiring policy (mlock, TM_RESIDENT) and the demand-paged reader are outside this path.
 //
 // File format ("TMQ1"): u32 tensor count, then per tensor
 //   u32 name_len | name | u32 dtype | u32 ndims | ndims x u32 shape | u64 nblocks | nblocks blocks
@@ -15,6 +17,7 @@
 #pragma once
 
 #include "cuda_shim.h"
+#include "gguf_reader.h"
 #include "quant.h"
 
 #include <cstddef>
@@ -147,23 +150,41 @@ public:
         ::close(fd);
         if (p == MAP_FAILED) return false;
         const std::uint8_t* base = static_cast<const std::uint8_t*>(p);
-        std::vector<TmqRecord> recs;
-        const bool ok = parse_tmq_index(size, [&](void* dst, std::size_t n, std::size_t at) { std::memcpy(dst, base + at, n); return true; }, recs);
-        if (!ok) { ::munmap(p, size); return false; }
         std::map<std::string, TensorInfo> table;
-        for (TmqRecord& r : recs) {
-            TensorInfo t;
-            t.dtype = r.dtype; t.shape = std::move(r.shape); t.blocks = base + r.payload; t.nblocks = r.nblocks; t.bytes = r.length;
-            table[std::move(r.name)] = std::move(t);
+        std::string arch;
+        if (std::memcmp(base, "GGUF", 4) == 0) {
+            std::vector<tmgguf::Tensor> idx;
+            if (!tmgguf::parse_index(base, size, idx, arch)) { ::munmap(p, size); return false; }
+            for (tmgguf::Tensor& g : idx) {
+                // the text model only; a vision tower or an unknown tensor is never given an engine name (tmq.h:439-445)
+                const bool keep = g.name == "model.embed_tokens.weight" || g.name == "lm_head.weight" || g.name == "model.norm.weight" ||
+                                  g.name.rfind("model.layers.", 0) == 0;
+                if (!keep) continue;
+                TensorInfo t;
+                t.dtype = tmgguf::container_dtype(g.gguf_type);
+                if (t.dtype == UINT32_MAX) { ::munmap(p, size); return false; }
+                t.shape = std::move(g.shape); t.blocks = base + g.payload; t.nblocks = g.nblocks; t.bytes = g.bytes;
+                if (!table.emplace(std::move(g.name), std::move(t)).second) { ::munmap(p, size); return false; }
+            }
+        } else {
+            std::vector<TmqRecord> recs;
+            const bool ok = parse_tmq_index(size, [&](void* dst, std::size_t n, std::size_t at) { std::memcpy(dst, base + at, n); return true; }, recs);
+            if (!ok) { ::munmap(p, size); return false; }
+            for (TmqRecord& r : recs) {
+                TensorInfo t;
+                t.dtype = r.dtype; t.shape = std::move(r.shape); t.blocks = base + r.payload; t.nblocks = r.nblocks; t.bytes = r.length;
+                table[std::move(r.name)] = std::move(t);
+            }
         }
         close();
-        base_ = base; size_ = size; tensors_ = std::move(table);
+        base_ = base; size_ = size; tensors_ = std::move(table); architecture_ = std::move(arch);
         return true;
     }
     void close() {
         if (base_) ::munmap(const_cast<std::uint8_t*>(base_), size_);
-        base_ = nullptr; size_ = 0; tensors_.clear();
+        base_ = nullptr; size_ = 0; tensors_.clear(); architecture_.clear();
     }
+    const std::string& architecture() const { return architecture_; }      // general.architecture of a GGUF file, "" for .tmq
     const std::uint8_t* base() const { return base_; }
     std::size_t size() const { return size_; }
     const std::map<std::string, TensorInfo>& tensors() const { return tensors_; }
@@ -176,12 +197,17 @@ private:
     const std::uint8_t* base_ = nullptr;
     std::size_t size_ = 0;
     std::map<std::string, TensorInfo> tensors_;
+    std::string architecture_;
 };
 
 // Make the named tensors resident on the GPU as ONE weight handle with aligned offsets. Afterwards the lane's
 // tm_cuda_tok_wbuf(tensor.blocks, ...) (and so tmllama::CudaLlama, which registers by pointer) finds them there.
-// Throws std::invalid_argument for an unknown name, std::runtime_error when the upload fails.
-inline int upload_tensors(const Mapped& file, const std::vector<std::string>& names, std::vector<std::uint64_t>* offsets = nullptr) {
+// Tensors in GGUF's own Q4_0 (dtype 9) are reordered on the device into the container's Q4_0 (the converter's nibble
+// reorder, tensormark/convert_gguf.cpp:124-135, bit-identical weights): `dtypes`, when given, receives the dtype each
+// tensor has ON THE DEVICE (1 for those). Throws std::invalid_argument for an unknown name, std::runtime_error when
+// the upload fails.
+inline int upload_tensors(const Mapped& file, const std::vector<std::string>& names, std::vector<std::uint64_t>* offsets = nullptr,
+                          std::vector<std::uint32_t>* dtypes = nullptr) {
     std::vector<const void*> ptrs;
     std::vector<std::size_t> bytes;
     for (const std::string& nm : names) {
@@ -193,6 +219,17 @@ inline int upload_tensors(const Mapped& file, const std::vector<std::string>& na
     std::vector<std::uint64_t> woff(names.size());
     const int id = tm_cuda_tok_wbuf_pack(ptrs.data(), bytes.data(), static_cast<unsigned>(ptrs.size()), woff.data());
     if (id < 0) throw std::runtime_error(std::string("tmq: upload failed: ") + tm_cuda_last_error());
+    if (dtypes) dtypes->clear();
+    for (std::size_t i = 0; i < names.size(); ++i) {
+        const TensorInfo* t = file.find(names[i]);
+        std::uint32_t dt = t->dtype;
+        if (dt == static_cast<std::uint32_t>(Dtype::GGUF_Q4_0)) {
+            if (!tm_cuda_tok_wbuf_q4_from_gguf(id, woff[i], static_cast<std::size_t>(t->nblocks)))
+                throw std::runtime_error(std::string("tmq: Q4_0 reorder failed: ") + tm_cuda_last_error());
+            dt = static_cast<std::uint32_t>(Dtype::Q4_0);
+        }
+        if (dtypes) dtypes->push_back(dt);
+    }
     if (offsets) *offsets = std::move(woff);
     return id;
 }

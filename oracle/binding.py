@@ -35,6 +35,7 @@ class Oracle:
         lib.tmo_fp32_to_fp16.restype = C.c_uint16
         lib.tmo_fp32_to_fp16.argtypes = [C.c_float]
         lib.tmo_dequant.argtypes = [C.c_int, C.c_void_p, _c_f32p, C.c_size_t]
+        lib.tmo_q4_split_to_interleaved.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
         lib.tmo_gemv.argtypes = [C.c_int, C.c_void_p, _c_f32p, _c_f32p, C.c_int, C.c_int]
         lib.tmo_gemv_mt.argtypes = [C.c_int, C.c_void_p, _c_f32p, _c_f32p, C.c_int, C.c_int, C.c_int]
         lib.tmo_gemv_f64.argtypes = [C.c_int, C.c_void_p, _c_f32p, _c_f64p, _c_f64p, C.c_int, C.c_int]
@@ -56,6 +57,12 @@ class Oracle:
         out = np.empty(n, dtype=np.float32)
         if not self.lib.tmo_dequant(dtype, _ptr(blocks), _ptr(out, _c_f32p), n):
             raise ValueError("tmo_dequant rejected its arguments")
+        return out
+
+    def q4_split_to_interleaved(self, blocks: np.ndarray) -> np.ndarray:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        out = np.empty_like(blocks)
+        self.lib.tmo_q4_split_to_interleaved(_ptr(blocks), _ptr(out), blocks.size // 18)
         return out
 
     def fp16_to_fp32(self, h: int) -> float:
@@ -224,6 +231,7 @@ class Reference:
         lib.tmref_fp32_to_fp16.argtypes = [C.c_float]
         lib.tmref_quantize_q4_0.argtypes = [_c_f32p, C.c_void_p, C.c_size_t]
         lib.tmref_quantize_q8_0.argtypes = [_c_f32p, C.c_void_p, C.c_size_t]
+        lib.tmref_quantize_tq2.argtypes = [_c_f32p, C.c_void_p, C.c_size_t]
 
     def dequant(self, dtype: int, blocks: np.ndarray, n: int) -> np.ndarray:
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
@@ -234,9 +242,9 @@ class Reference:
 
     def quantize(self, dtype: int, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
-        bb = {0: 34, 1: 18}[dtype]
-        out = np.empty(x.size // 32 * bb, dtype=np.uint8)
-        fn = self.lib.tmref_quantize_q8_0 if dtype == 0 else self.lib.tmref_quantize_q4_0
+        bb, be = {0: (34, 32), 1: (18, 32), 7: (34, 128)}[dtype]
+        out = np.empty(x.size // be * bb, dtype=np.uint8)
+        fn = {0: self.lib.tmref_quantize_q8_0, 1: self.lib.tmref_quantize_q4_0, 7: self.lib.tmref_quantize_tq2}[dtype]
         fn(_ptr(x, _c_f32p), _ptr(out), x.size)
         return out
 

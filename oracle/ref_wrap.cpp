@@ -20,6 +20,7 @@ __attribute__((visibility("default"))) int tmref_dequant(int dtype, const void* 
             case 4: tmq::dequantize_row_q4_1(static_cast<const tmq::BlockQ4_1*>(blocks), out, n); return 1;
             case 5: tmq::dequantize_row_q5_K(static_cast<const tmq::BlockQ5_K*>(blocks), out, n); return 1;
             case 6: tmq::dequantize_row_q6_K(static_cast<const tmq::BlockQ6_K*>(blocks), out, n); return 1;
+            case 7: tmq::dequantize_row_tq2_34x128(static_cast<const tmq::BlockTq2_34x128*>(blocks), out, n); return 1;
             case 8: tmq::dequantize_row_q4_K(static_cast<const tmq::BlockQ4_K*>(blocks), out, n); return 1;
             default: return 0;
         }
@@ -29,6 +30,9 @@ __attribute__((visibility("default"))) float tmref_fp16_to_fp32(std::uint16_t h)
 __attribute__((visibility("default"))) std::uint16_t tmref_fp32_to_fp16(float f) { return tmq::fp32_to_fp16(f); }
 __attribute__((visibility("default"))) void tmref_quantize_q4_0(const float* x, void* out, std::size_t n) {
     tmq::quantize_row_q4_0(x, static_cast<tmq::BlockQ4_0*>(out), n);
+}
+__attribute__((visibility("default"))) void tmref_quantize_tq2(const float* x, void* out, std::size_t n) {
+    tmq::quantize_row_tq2_34x128(x, static_cast<tmq::BlockTq2_34x128*>(out), n);
 }
 __attribute__((visibility("default"))) void tmref_quantize_q8_0(const float* x, void* out, std::size_t n) {
     tmq::quantize_row_q8_0(x, static_cast<tmq::BlockQ8_0*>(out), n);

@@ -63,10 +63,10 @@ static uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); 
 
 /* ---- geometry (tensormark/tmq.h:83-115) ---------------------------------- */
 TMO_API int tmo_block_elems(int dtype) {
-    switch (dtype) { case 0: case 1: case 4: return 32; case 5: case 6: case 8: return 256; default: return 0; }
+    switch (dtype) { case 0: case 1: case 4: case 9: return 32; case 5: case 6: case 8: return 256; case 7: return 128; default: return 0; }
 }
 TMO_API int tmo_block_bytes(int dtype) {
-    switch (dtype) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
+    switch (dtype) { case 0: case 7: return 34; case 1: case 9: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
 }
 
 /* ---- dequantizers --------------------------------------------------------- */
@@ -167,6 +167,32 @@ static void deq_q6_k(const uint8_t* b, float* x) {
 }
 
 /* n weights (whole blocks) of `dtype`; returns 0 on a bad argument. */
+/* TQ2 (container dtype 7), quant.h:507-515 dequantize_ternary: 128 two-bit codes, four per byte, low bits first;
+ * x[j] = (float)(code - 1) * d. */
+static void deq_tq2(const uint8_t* b, float* x) {
+    float d = tmo_fp16_to_fp32(rd16(b));
+    for (int j = 0; j < 128; j++) x[j] = (float)((int)((b[2 + (j >> 2)] >> (2 * (j & 3))) & 3) - 1) * d;
+}
+/* GGUF's own Q4_0 (container dtype 9), llama.h:4588-4597: the Q4_0 block with split nibbles,
+ * x[j] = d * ((qs[j] & 15) - 8), x[j + 16] = d * ((qs[j] >> 4) - 8). */
+static void deq_gguf_q4_0(const uint8_t* b, float* x) {
+    float d = tmo_fp16_to_fp32(rd16(b));
+    for (int j = 0; j < 16; j++) {
+        x[j] = d * (float)((b[2 + j] & 15) - 8);
+        x[j + 16] = d * (float)((b[2 + j] >> 4) - 8);
+    }
+}
+/* The converter's nibble reorder (convert_gguf.cpp:124-135): a split-nibble block as the container's interleaved
+ * Q4_0 block with the same scale and the same 32 codes; dequantizing either gives the same bits. */
+TMO_API void tmo_q4_split_to_interleaved(const uint8_t* src, uint8_t* dst, size_t nblocks) {
+    for (size_t b = 0; b < nblocks; b++, src += 18, dst += 18) {
+        uint8_t code[32];
+        for (int j = 0; j < 16; j++) { code[j] = src[2 + j] & 15; code[j + 16] = src[2 + j] >> 4; }
+        dst[0] = src[0]; dst[1] = src[1];
+        for (int j = 0; j < 16; j++) dst[2 + j] = (uint8_t)(code[2 * j] | (code[2 * j + 1] << 4));
+    }
+}
+
 TMO_API int tmo_dequant(int dtype, const void* blocks, float* out, size_t n) {
     int be = tmo_block_elems(dtype), bb = tmo_block_bytes(dtype);
     if (!be || n % (size_t)be) return 0;
@@ -177,7 +203,9 @@ TMO_API int tmo_dequant(int dtype, const void* blocks, float* out, size_t n) {
             case 1: deq_q4_0(p, out); break;
             case 4: deq_q4_1(p, out); break;
             case 5: deq_q5_k(p, out); break;
+            case 7: deq_tq2(p, out); break;
             case 8: deq_q4_k(p, out); break;
+            case 9: deq_gguf_q4_0(p, out); break;
             default: deq_q6_k(p, out); break;
         }
     }

@@ -151,7 +151,8 @@ class Chain:
         return nxt
 
     def prefill(self, tokens) -> int:
-        """Run a prompt (two or more tokens) through the batched layer stack; returns the token chosen after it."""
+        """Run a prompt (three or more tokens) through the batched layer stack, its last token through the decode lane;
+        returns the token chosen after it."""
         t = np.ascontiguousarray(tokens, dtype=np.int32)
         nxt = self.L.tmchain_prefill(self.h, t.ctypes.data, t.size)
         self._check(nxt >= 0)

@@ -8,13 +8,17 @@
 namespace tmc {
 
 // dtype ids of the weight container (tensormark/tmq.h:48-60)
-enum : unsigned { DT_Q8_0 = 0, DT_Q4_0 = 1, DT_F16 = 3, DT_Q4_1 = 4, DT_Q5_K = 5, DT_Q6_K = 6, DT_Q4_K = 8 };
+// 9 is GGUF's own Q4_0 block: the same 18 bytes with SPLIT nibbles (byte j = elements j | j + 16, llama.h:4588-4597),
+// where the container's Q4_0 interleaves (byte j = elements 2j | 2j + 1). 3 and 10 are plain fp16 / bf16 rows, served by
+// gemv_f16.cu; they are not block formats (block_elems is 0 for them).
+// 7 is the ternary pack TQ2: 128 two-bit codes and one fp16 scale per 34-byte block, w = (code - 1) * d (quant.h:446-566).
+enum : unsigned { DT_Q8_0 = 0, DT_Q4_0 = 1, DT_F16 = 3, DT_Q4_1 = 4, DT_Q5_K = 5, DT_Q6_K = 6, DT_TQ2 = 7, DT_Q4_K = 8, DT_GGUF_Q4_0 = 9, DT_BF16 = 10 };
 
 inline __host__ __device__ unsigned block_elems(unsigned dt) {
-    return (dt == 0 || dt == 1 || dt == 4) ? 32u : (dt == 5 || dt == 6 || dt == 8) ? 256u : 0u;
+    return (dt == 0 || dt == 1 || dt == 4 || dt == 9) ? 32u : (dt == 5 || dt == 6 || dt == 8) ? 256u : dt == 7 ? 128u : 0u;
 }
 inline __host__ __device__ unsigned block_bytes(unsigned dt) {
-    switch (dt) { case 0: return 34; case 1: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
+    switch (dt) { case 0: case 7: return 34; case 1: case 9: return 18; case 4: return 20; case 5: return 176; case 6: return 210; case 8: return 144; default: return 0; }
 }
 inline size_t weight_bytes(unsigned dt, size_t n_out, size_t n_in) {
     const unsigned e = block_elems(dt);
@@ -90,6 +94,10 @@ bool launch_xprep(uint32_t* out, const float* x, const float* x2, unsigned x_op,
                   const Exchange* xchg, cudaStream_t st);
 bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigned K, unsigned dtype,
                  const SegTable& seg, cudaStream_t st, const GemvFuse* fuse = nullptr);
+// gemv_f16.cu: plain 16-bit rows (fp16 or bf16), and the GGUF -> container Q4_0 nibble reorder
+bool launch_gemv_half(const float* x, const void* W, float* y, unsigned N, unsigned K, bool bf16, cudaStream_t st);
+bool launch_embed_half(const unsigned* tok, unsigned idx, const void* W, float* x, unsigned D, bool bf16, cudaStream_t st);
+bool launch_q4_split_to_interleaved(uint8_t* blocks, size_t nblocks, cudaStream_t st);
 bool launch_dequant(const uint8_t* W, float* out, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);
 bool launch_dequant_half(const uint8_t* W, void* out_half, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);
 

@@ -187,7 +187,13 @@ size_t tm_cuda_weight_bytes(unsigned dtype, size_t N, size_t K) { return weight_
 // ---- device-pointer kernels ----------------------------------------------------
 bool tm_cuda_gemv_q_dev(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype, void* stream) {
     if (!ensure_init(-1)) return false;
+    if (dtype == DT_F16 || dtype == DT_BF16) return launch_gemv_half(x, W, y, N, K, dtype == DT_BF16, (cudaStream_t)stream);
     return launch_gemv(x, (const uint8_t*)W, y, N, K, dtype, one_segment(N), (cudaStream_t)stream);
+}
+
+bool tm_cuda_q4_0_from_gguf_dev(void* blocks, size_t nblocks, void* stream) {
+    if (!ensure_init(-1)) return false;
+    return launch_q4_split_to_interleaved((uint8_t*)blocks, nblocks, (cudaStream_t)stream);
 }
 
 bool tm_cuda_gemv_seg_dev(const float* x, const void* W, float* y, unsigned N, unsigned K, unsigned dtype,

@@ -53,6 +53,8 @@ bool launch(const uint8_t* W, void* out, unsigned N, unsigned K, unsigned dtype,
         case DT_Q4_1: dequant_rows<4, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         case DT_Q5_K: dequant_rows<5, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         case DT_Q4_K: dequant_rows<8, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
+        case DT_TQ2: dequant_rows<7, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
+        case DT_GGUF_Q4_0: dequant_rows<9, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
         default:      dequant_rows<6, HALF><<<grid, 256, 0, st>>>(W, out, N, K, row_bytes); break;
     }
     note_launch();

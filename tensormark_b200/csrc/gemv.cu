@@ -531,6 +531,39 @@ template <> __device__ float generic_row<1>(const uint8_t* r, const float* x, ui
     }
     return acc;
 }
+template <> __device__ float generic_row<9>(const uint8_t* r, const float* x, uint32_t K, int lane) {
+    float acc = 0.f;
+    for (uint32_t b = lane; b < K / 32; b += 32) {
+        const uint8_t* q = r + (size_t)b * 18;
+        float s = 0.f;
+        for (int j = 0; j < 16; ++j)
+            s += (float)((int)(q[2 + j] & 15) - 8) * x[b * 32 + j] + (float)((int)(q[2 + j] >> 4) - 8) * x[b * 32 + 16 + j];
+        acc += s * ldh(q);
+    }
+    return acc;
+}
+// TQ2: the reference's code-counting dot (quant.h:520-531): with lo / hi the two bits of a code,
+// sum w x = d * (sum_{lo} x + 2 sum_{hi} x - sum x) per 128-block; one block per lane iteration.
+template <> __device__ float generic_row<7>(const uint8_t* r, const float* x, uint32_t K, int lane) {
+    float acc = 0.f;
+    for (uint32_t b = lane; b < K / 128; b += 32) {
+        const uint8_t* q = r + (size_t)b * 34;
+        float lo = 0.f, hi = 0.f, all = 0.f;
+        for (int j = 0; j < 32; ++j) {
+            const uint32_t byte = q[2 + j];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float xv = x[b * 128 + 4 * j + t];
+                const uint32_t c = (byte >> (2 * t)) & 3u;
+                all += xv;
+                if (c & 1u) lo += xv;
+                if (c & 2u) hi += xv;
+            }
+        }
+        acc += ldh(q) * (lo + 2.f * hi - all);
+    }
+    return acc;
+}
 template <> __device__ float generic_row<0>(const uint8_t* r, const float* x, uint32_t K, int lane) {
     float acc = 0.f;
     for (uint32_t b = lane; b < K / 32; b += 32) {
@@ -726,6 +759,8 @@ unsigned cluster_sms(unsigned cluster, unsigned sms) {
     return cached[cluster];
 }
 
+template <int DT> bool launch_generic_only(GemvParams p, cudaStream_t st);
+
 template <int DT>
 bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
     using L = Lane<DT>;
@@ -801,6 +836,11 @@ bool launch_dt(GemvParams p, bool aligned, cudaStream_t st) {
             }
         }
     }
+    return launch_generic_only<DT>(p, st);
+}
+
+template <int DT>
+bool launch_generic_only(GemvParams p, cudaStream_t st) {
     p.xq = nullptr;                                         // the plain kernel reads the fp32 x
     const unsigned rows_per_cta = 8;
     const size_t xsmem = p.x_op ? (size_t)p.K * 4 : 0;
@@ -824,6 +864,7 @@ bool launch_any(const GemvParams& p, unsigned dtype, bool aligned, cudaStream_t 
         case DT_Q4_1: return launch_dt<4>(p, aligned, st);
         case DT_Q5_K: return launch_dt<5>(p, aligned, st);
         case DT_Q4_K: return launch_dt<8>(p, aligned, st);
+        case DT_GGUF_Q4_0: return launch_dt<9>(p, aligned, st);
         default: return launch_dt<6>(p, aligned, st);
     }
 }
@@ -861,6 +902,10 @@ bool launch_gemv(const float* x, const uint8_t* W, float* y, unsigned N, unsigne
     }
     bool aligned = ((uintptr_t)W % 16 == 0) && (p.row_bytes % 16 == 0);
     for (unsigned s = 0; s < seg.nseg; ++s) aligned = aligned && (seg.woff[s] % 16 == 0);
+    if (dtype == DT_TQ2) {                                  // ternary rows: the plain kernel (no streaming lane is built for them)
+        p.xq = nullptr;
+        return launch_generic_only<7>(p, st);
+    }
     return launch_any(p, dtype, aligned, st);
 }
 
@@ -872,6 +917,7 @@ size_t xq_bytes(unsigned K, unsigned dtype) {
         case DT_Q4_1: return sz(Lane<4>::STEP_W, Lane<4>::XW);
         case DT_Q5_K: return sz(Lane<5>::STEP_W, Lane<5>::XW);
         case DT_Q4_K: return sz(Lane<8>::STEP_W, Lane<8>::XW);
+        case DT_GGUF_Q4_0: return sz(Lane<9>::STEP_W, Lane<9>::XW);
         case DT_Q6_K: return sz(Lane<6>::STEP_W, Lane<6>::XW);
         default: return 0;
     }
@@ -909,6 +955,7 @@ bool launch_xprep(uint32_t* out, const float* x, const float* x2, unsigned x_op,
         case DT_Q4_1: return launch_xprep_dt<4>(out, x, x2, x_op, eps, K, xc, st);
         case DT_Q5_K: return launch_xprep_dt<5>(out, x, x2, x_op, eps, K, xc, st);
         case DT_Q4_K: return launch_xprep_dt<8>(out, x, x2, x_op, eps, K, xc, st);
+        case DT_GGUF_Q4_0: return launch_xprep_dt<9>(out, x, x2, x_op, eps, K, xc, st);
         default: return launch_xprep_dt<6>(out, x, x2, x_op, eps, K, xc, st);
     }
 }

@@ -327,6 +327,21 @@ template <> struct Lane<1> {
     }
 };
 
+// ---- GGUF Q4_0 (dtype 9): the Q4_0 block with split nibbles, byte j = elements j (low) | j + 16 (high)
+// (tensormark/llama.h:4588-4597). Same lane bytes, same dot: only the x images differ. The image that meets the
+// low nibbles holds element j under byte j, the one that meets the high nibbles element j + 16.
+template <> struct Lane<9> : Lane<1> {
+    static TM_HD uint32_t plane_byte(uint32_t e, int t) {
+        const uint32_t b = e >> 5, i = e & 31u;
+        return (b >> 1) * (XW * 4u) + 4u * (18u * (uint32_t)t + 9u * (i >> 4)) + ((b & 1u) ? 20u : 2u) + (i & 15u);
+    }
+    static TM_HD void store_quad(uint32_t* units, uint32_t e0, int t, uint32_t packed) {
+        uint8_t* p = reinterpret_cast<uint8_t*>(units) + plane_byte(e0, t);      // four consecutive bytes of one image, 2 mod 4
+        *reinterpret_cast<uint16_t*>(p) = (uint16_t)packed;
+        *reinterpret_cast<uint16_t*>(p + 2) = (uint16_t)(packed >> 16);
+    }
+};
+
 // ---- Q4_1: 20-byte blocks [d:2][m:2][qs:16], byte j = elements j (low) | j+16 (high), w = n*d + m
 // Lane bytes: 40 = 10 words. x unit: per block b and plane t a "low" 4-word image at
 // [8P b + 8t, +4) and a "high" image at [8P b + 8t + 4, +4); [16 P] = sA, [16 P + 1] = sB,

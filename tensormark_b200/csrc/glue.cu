@@ -474,10 +474,13 @@ bool launch_advance(int* state, cudaStream_t st) {
 }
 
 AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t probs_bytes) {
+    return plan_attention_sms((unsigned)device_sm_count(), H, KVH, dh, ctx, allow, probs_bytes);
+}
+AttnPlan plan_attention_sms(unsigned sms, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t probs_bytes) {
     AttnPlan pl{};
     // Enough (kv head, split) CTAs to cover the machine; every split at least 32
     // positions; the partials must fit the caller's probs buffer.
-    unsigned nsplit = cdiv((unsigned)device_sm_count(), KVH);
+    unsigned nsplit = cdiv(sms, KVH);
     nsplit = nsplit < cdiv(allow, 32u) ? nsplit : cdiv(allow, 32u);
     const size_t per_split = (size_t)H * (dh + 2) * sizeof(float);
     const unsigned fit = (unsigned)(probs_bytes / per_split);

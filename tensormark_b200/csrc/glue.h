@@ -35,6 +35,8 @@ struct AttnPlan {
 };
 // scratch_bytes: size of the buffer that will receive partials and stats.
 AttnPlan plan_attention(unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t scratch_bytes);
+// The same rule for a caller that names the SM count itself (a scratch_bytes of 1 << 40 means: no limit from the buffer).
+AttnPlan plan_attention_sms(unsigned sms, unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, size_t scratch_bytes);
 bool launch_attention(const float* q, const void* kc, const void* vc, bool half_cache, float* scratch, float* out,
                       unsigned H, unsigned KVH, unsigned dh, unsigned ctx, unsigned allow, float scale, unsigned REP,
                       const AttnPlan& pl, cudaStream_t st, const int* state = nullptr);

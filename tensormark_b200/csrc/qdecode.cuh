@@ -2,7 +2,7 @@
 //
 // decode_weight<DT>(row, k) returns weight k of a row exactly as the reference's
 // scalar dequantizers produce it (tensormark/quant.h:194-200 Q8_0, 397-408 Q4_0,
-// 267-277 Q4_1, 282-301 Q4_K, 304-330 Q5_K, 338-365 Q6_K): the same fp32 operations in the
+// 267-277 Q4_1, 282-301 Q4_K, 304-330 Q5_K, 338-365 Q6_K; llama.h:4588-4597 GGUF Q4_0): the same fp32 operations in the
 // same order, each rounded separately (__fmul_rn/__fadd_rn/__fsub_rn keep the
 // compiler from contracting them into FMAs), and the same half->float rule for
 // every encoding including subnormals and NaN payloads (quant.h:58-70).
@@ -34,6 +34,18 @@ template <> __device__ __forceinline__ float decode_weight<1>(const uint8_t* row
     const uint32_t e = k & 31, byte = b[2 + (e >> 1)];
     const int n = (int)((e & 1) ? (byte >> 4) : (byte & 15u)) - 8;
     return __fmul_rn(__int2float_rn(n), rd_half(b));
+}
+template <> __device__ __forceinline__ float decode_weight<9>(const uint8_t* row, uint32_t k) {   // GGUF Q4_0, llama.h:4588-4597
+    const uint8_t* b = row + (size_t)(k >> 5) * 18;
+    const uint32_t e = k & 31, byte = b[2 + (e & 15)];
+    const int n = (int)((e & 16) ? (byte >> 4) : (byte & 15u)) - 8;
+    return __fmul_rn(rd_half(b), __int2float_rn(n));
+}
+template <> __device__ __forceinline__ float decode_weight<7>(const uint8_t* row, uint32_t k) {   // TQ2, quant.h:507-515
+    const uint8_t* b = row + (size_t)(k >> 7) * 34;
+    const uint32_t e = k & 127;
+    const int code = (int)((b[2 + (e >> 2)] >> (2 * (e & 3))) & 3u) - 1;
+    return __fmul_rn(__int2float_rn(code), rd_half(b));
 }
 template <> __device__ __forceinline__ float decode_weight<4>(const uint8_t* row, uint32_t k) {
     const uint8_t* b = row + (size_t)(k >> 5) * 20;
@@ -85,7 +97,9 @@ __device__ __forceinline__ float decode_weight_dt(unsigned dt, const uint8_t* ro
         case 1: return decode_weight<1>(row, k);
         case 4: return decode_weight<4>(row, k);
         case 5: return decode_weight<5>(row, k);
+        case 7: return decode_weight<7>(row, k);
         case 8: return decode_weight<8>(row, k);
+        case 9: return decode_weight<9>(row, k);
         default: return decode_weight<6>(row, k);
     }
 }

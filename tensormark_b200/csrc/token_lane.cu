@@ -370,6 +370,38 @@ void tm_cuda_tok_embed_kq(int tokslot, unsigned idx, int wid, uint64_t woff, int
 void tm_cuda_tok_embed_q4(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D) {
     tm_cuda_tok_embed_kq(tokslot, idx, wid, woff, xslot, D, DT_Q4_0);
 }
+// F16 tensors (tensormark/metal.h:3693-3721 tok_gemv_h, 3260-3271 tok_embed_h). woff is a byte offset into the handle.
+void tm_cuda_tok_gemv_h(int xslot, int wid, uint64_t woff, int yslot, size_t yoff, unsigned N, unsigned K) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    if (yoff % 4 || woff % 2) { latch("tok_gemv_h: misaligned offset"); return; }
+    const float* x = (const float*)slot_ptr(xslot, (size_t)K * 4, "tok_gemv_h");
+    uint8_t* y = slot_ptr(yslot, yoff + (size_t)N * 4, "tok_gemv_h");
+    const uint8_t* W = weight_ptr(wid, woff, (size_t)N * K * 2, "tok_gemv_h");
+    if (!x || !y || !W) return;
+    if (!launch_gemv_half(x, W, (float*)(y + yoff), N, K, false, s.stream)) s.sticky = true;
+}
+void tm_cuda_tok_embed_h(int tokslot, unsigned idx, int wid, uint64_t woff, int xslot, unsigned D) {
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    const unsigned* tok = (const unsigned*)slot_ptr(tokslot, sizeof(unsigned) * ((size_t)idx + 1), "tok_embed_h");
+    float* x = (float*)slot_ptr(xslot, (size_t)D * 4, "tok_embed_h");
+    const uint8_t* W = weight_ptr(wid, woff, 0, "tok_embed_h");
+    if (!tok || !x || !W) return;
+    if (woff % 2) { latch("tok_embed_h: misaligned offset"); return; }
+    if (!launch_embed_half(tok, idx, W, x, D, false, s.stream)) s.sticky = true;
+}
+// The Q4_0 blocks of a registered range arrived in GGUF's split nibble order: rewrite them in place in the container's
+// order, after which every Q4_0 kernel serves them (tensormark/convert_gguf.cpp:124-135, done on the device).
+bool tm_cuda_tok_wbuf_q4_from_gguf(int wid, uint64_t woff, size_t nblocks) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    if (s.encoding) return fail("tok_wbuf_q4_from_gguf: not while a token is encoded");
+    const uint8_t* W = weight_ptr(wid, woff, nblocks * 18, "tok_wbuf_q4_from_gguf");
+    if (!W) { s.sticky = false; return false; }
+    if (!launch_q4_split_to_interleaved(const_cast<uint8_t*>(W), nblocks, s.stream)) return false;
+    return sync_stream(s.stream, "tok_wbuf_q4_from_gguf");
+}
 void tm_cuda_tok_bias_qkv(int yslot, int biasslot, size_t bias_off, unsigned N) {
     if (!ensure_init(-1)) return;
     State& s = state();
@@ -854,6 +886,8 @@ void tm_metal_tok_gemv_seg_dt(int x, int w, int y, size_t yo, unsigned N, unsign
 void tm_metal_tok_gemv_kq(int x, int w, uint64_t wo, int y, size_t yo, unsigned N, unsigned K, unsigned dt) { tm_cuda_tok_gemv_kq(x, w, wo, y, yo, N, K, dt); }
 void tm_metal_tok_embed_q4(int t, unsigned i, int w, uint64_t wo, int x, unsigned D) { tm_cuda_tok_embed_q4(t, i, w, wo, x, D); }
 void tm_metal_tok_embed_kq(int t, unsigned i, int w, uint64_t wo, int x, unsigned D, unsigned dt) { tm_cuda_tok_embed_kq(t, i, w, wo, x, D, dt); }
+void tm_metal_tok_gemv_h(int x, int w, uint64_t wo, int y, size_t yo, unsigned N, unsigned K) { tm_cuda_tok_gemv_h(x, w, wo, y, yo, N, K); }
+void tm_metal_tok_embed_h(int t, unsigned i, int w, uint64_t wo, int x, unsigned D) { tm_cuda_tok_embed_h(t, i, w, wo, x, D); }
 void tm_metal_tok_bias_qkv(int y, int b, size_t bo, unsigned N) { tm_cuda_tok_bias_qkv(y, b, bo, N); }
 void tm_metal_tok_rmsnorm(int x, const void* w, int o, unsigned D, float eps) { tm_cuda_tok_rmsnorm(x, w, o, D, eps); }
 void tm_metal_tok_add(int a, int b, unsigned n) { tm_cuda_tok_add(a, b, n); }

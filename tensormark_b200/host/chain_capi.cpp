@@ -112,7 +112,7 @@ TMCHAIN_API int tmchain_feed(void* p, const int* toks, int n) {
     catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 
-// A prompt of n >= 2 tokens through the batched layer stack; returns the model's next token or -1.
+// A prompt of n >= 3 tokens through the batched layer stack (last token through the decode lane); returns the model's next token or -1.
 TMCHAIN_API int tmchain_prefill(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_prefill(toks, n); }
     catch (const std::exception& e) { g_err = e.what(); return -1; }
@@ -135,10 +135,11 @@ TMCHAIN_API int tmq_upload(const char* path, const char* const* names, int n, un
         if (!m->open(path)) { g_err = std::string("tmq: cannot open or parse ") + path; return -1; }
         std::vector<std::string> nm(names, names + n);
         std::vector<std::uint64_t> off;
-        const int id = tmmq::upload_tensors(*m, nm, &off);
+        std::vector<std::uint32_t> dts;                    // the dtype each tensor has on the device (GGUF Q4_0 becomes Q4_0)
+        const int id = tmmq::upload_tensors(*m, nm, &off, &dts);
         for (int i = 0; i < n; ++i) {
             const tmmq::TensorInfo* t = m->find(nm[(size_t)i]);
-            woff[i] = off[(size_t)i]; dtype[i] = t->dtype; nblocks[i] = t->nblocks;
+            woff[i] = off[(size_t)i]; dtype[i] = dts[(size_t)i]; nblocks[i] = t->nblocks;
         }
         keep.push_back(std::move(m));
         return id;

@@ -65,6 +65,10 @@ SIGNATURES = {
     "tm_cuda_tok_gemv_kq": (None, [C.c_int, C.c_int, _u64, C.c_int, _sz, _u, _u, _u]),
     "tm_cuda_tok_embed_q4": (None, [C.c_int, _u, C.c_int, _u64, C.c_int, _u]),
     "tm_cuda_tok_embed_kq": (None, [C.c_int, _u, C.c_int, _u64, C.c_int, _u, _u]),
+    "tm_cuda_tok_gemv_h": (None, [C.c_int, C.c_int, _u64, C.c_int, _sz, _u, _u]),
+    "tm_cuda_tok_embed_h": (None, [C.c_int, _u, C.c_int, _u64, C.c_int, _u]),
+    "tm_cuda_tok_wbuf_q4_from_gguf": (C.c_bool, [C.c_int, _u64, _sz]),
+    "tm_cuda_q4_0_from_gguf_dev": (C.c_bool, [_vp, _sz, _vp]),
     "tm_cuda_tok_bias_qkv": (None, [C.c_int, C.c_int, _sz, _u]),
     "tm_cuda_tok_rmsnorm": (None, [C.c_int, _vp, C.c_int, _u, C.c_float]),
     "tm_cuda_tok_add": (None, [C.c_int, C.c_int, _u]),

@@ -89,7 +89,7 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
     stream = torch.cuda.ExternalStream(L.tm_cuda_tok_stream())
     t0 = time.perf_counter()
     prefill_gpu_ms = None
-    if prefill == "stack" and world == 1 and prompt_n >= 2:
+    if prefill == "stack" and prompt_n >= 3:
         m.prefill_prepare()                                # one-time set-up (device caches, page-locked host arrays) is not prompt time
         t0 = time.perf_counter()
         nxt = m.prefill(prompt)                            # the batched layer stack (tensor-core GEMMs)

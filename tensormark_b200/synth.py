@@ -12,10 +12,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_0, F16, Q4_1, Q5_K, Q6_K, Q4_K = 0, 1, 3, 4, 5, 6, 8
-DTYPE_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_K: "Q5_K", Q6_K: "Q6_K", Q4_K: "Q4_K"}
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_1: 32, Q5_K: 256, Q6_K: 256, Q4_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_1: 20, Q5_K: 176, Q6_K: 210, Q4_K: 144}
+Q8_0, Q4_0, F16, Q4_1, Q5_K, Q6_K, TQ2, Q4_K, GGUF_Q4_0, BF16 = 0, 1, 3, 4, 5, 6, 7, 8, 9, 10
+DTYPE_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_1: "Q4_1", Q5_K: "Q5_K", Q6_K: "Q6_K", TQ2: "TQ2", Q4_K: "Q4_K", GGUF_Q4_0: "GGUF_Q4_0"}
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_1: 32, Q5_K: 256, Q6_K: 256, TQ2: 128, Q4_K: 256, GGUF_Q4_0: 32}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_1: 20, Q5_K: 176, Q6_K: 210, TQ2: 34, Q4_K: 144, GGUF_Q4_0: 18}
 
 
 def weight_bytes(dtype: int, n_out: int, n_in: int) -> int:
@@ -55,7 +55,7 @@ def make_weights(dtype: int, n_out: int, n_in: int, seed: int, stream: int = 1) 
     nb = n_out * (n_in // BLOCK_ELEMS[dtype])
     bb = BLOCK_BYTES[dtype]
     out = np.empty((nb, bb), dtype=np.uint8)
-    if dtype == Q4_0:
+    if dtype in (Q4_0, GGUF_Q4_0):               # the same bytes; the two formats differ in which element a nibble is
         out[:, 0:2] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.02)
         out[:, 2:18] = g.integers(0, 256, size=(nb, 16), dtype=np.uint8)
     elif dtype == Q8_0:
@@ -73,6 +73,9 @@ def make_weights(dtype: int, n_out: int, n_in: int, seed: int, stream: int = 1) 
         out[:, 0:2] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
         out[:, 2:4] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.001)
         out[:, 4:144] = g.integers(0, 256, size=(nb, 140), dtype=np.uint8)
+    elif dtype == TQ2:                            # d = half(|N(0,1)| * 0.02), 128 codes uniform in 0..3 (3 = +2 never comes out of the
+        out[:, 0:2] = _half_bytes(np.abs(g.standard_normal(nb)) * 0.02)      # reference's quantizer but must decode, quant.h:489-492)
+        out[:, 2:34] = g.integers(0, 256, size=(nb, 32), dtype=np.uint8)
     elif dtype == Q6_K:
         out[:, 0:192] = g.integers(0, 256, size=(nb, 192), dtype=np.uint8)
         out[:, 192:208] = g.integers(-32, 32, size=(nb, 16), dtype=np.int8).view(np.uint8)

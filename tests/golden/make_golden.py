@@ -29,7 +29,7 @@ def special_blocks(dtype: int, rng: np.random.Generator) -> np.ndarray:
     """One block per special scale encoding (zero, subnormal, max, inf, NaN ...) with random codes,
     plus all-min / all-max code blocks."""
     bb = synth.BLOCK_BYTES[dtype]
-    scale_off = {0: [0], 1: [0], 4: [0, 2], 5: [0, 2], 6: [208], 8: [0, 2]}[dtype]
+    scale_off = {0: [0], 1: [0], 4: [0, 2], 5: [0, 2], 6: [208], 7: [0], 8: [0, 2]}[dtype]
     out = []
     for h in SPECIAL_HALVES:
         for off in scale_off:
@@ -53,7 +53,10 @@ def main() -> None:
         raise SystemExit("oracle/_ref/libtm_ref.so is missing: run `make -C oracle` where the reference tree exists")
     out = {}
     rng = np.random.Generator(np.random.Philox(key=[2026, 7]))
-    for dt, name in synth.DTYPE_NAMES.items():
+    # the formats quant.h itself dequantizes, TQ2 last (so the earlier formats' vectors do not depend on it). GGUF's own
+    # Q4_0 (dtype 9) is decoded in llama.h, not quant.h: it is pinned by its relation to Q4_0 instead (tests/test_oracle.py).
+    for dt in (synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K, synth.TQ2):
+        name = synth.DTYPE_NAMES[dt]
         be = synth.BLOCK_ELEMS[dt]
         k = 512
         blocks = synth.make_weights(dt, 6, k, seed=100 + dt).reshape(-1, synth.BLOCK_BYTES[dt])
@@ -64,7 +67,7 @@ def main() -> None:
         out[f"{name}_dequant_bits"] = deq.view(np.uint32)
     # the reference's own quantizers on seeded floats: realistic scales, every code reachable
     x = (rng.standard_normal(32 * 64) * np.repeat(np.exp(rng.standard_normal(64) * 3.0), 32)).astype(np.float32)
-    for dt in (0, 1):
+    for dt in (0, 1, 7):
         q = ref.quantize(dt, x)
         out[f"{synth.DTYPE_NAMES[dt]}_quantized_from"] = x
         out[f"{synth.DTYPE_NAMES[dt]}_quantized_blocks"] = q

@@ -69,7 +69,7 @@ static void emul(const uint8_t* W, const float* x, float* y, unsigned N, unsigne
 extern "C" __attribute__((visibility("default")))
 int lane_emul_gemv(int dtype, const void* W, const float* x, float* y, unsigned N, unsigned K) {
     const unsigned be = (dtype == 5 || dtype == 6 || dtype == 8) ? 256 : 32;
-    const unsigned bb = dtype == 0 ? 34 : dtype == 1 ? 18 : dtype == 4 ? 20 : dtype == 5 ? 176 : dtype == 8 ? 144 : 210;
+    const unsigned bb = dtype == 0 ? 34 : (dtype == 1 || dtype == 9) ? 18 : dtype == 4 ? 20 : dtype == 5 ? 176 : dtype == 8 ? 144 : 210;
     if (K % be) return 0;
     const unsigned rb = K / be * bb;
     switch (dtype) {
@@ -79,6 +79,7 @@ int lane_emul_gemv(int dtype, const void* W, const float* x, float* y, unsigned 
         case 5: emul<5>((const uint8_t*)W, x, y, N, K, rb); return 1;
         case 6: emul<6>((const uint8_t*)W, x, y, N, K, rb); return 1;
         case 8: emul<8>((const uint8_t*)W, x, y, N, K, rb); return 1;
+        case 9: emul<9>((const uint8_t*)W, x, y, N, K, rb); return 1;
         default: return 0;
     }
 }

@@ -15,6 +15,7 @@ from tests.gpu_util import dev_bytes, dev_f32, gemv_dev, ptr, stream_ptr
 
 pytestmark = pytest.mark.gpu
 DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
+DEQUANT_DTYPES = DTYPES + [synth.TQ2]        # the ternary pack: bit-exact dequant and a plain (not streaming) GEMV
 TOL = 1e-3      # relative to sum_k |w_k x_k| per output, the bar the path is judged by
 
 
@@ -34,7 +35,7 @@ def _dequant_dev(cuda, torch, dt, blocks, n, k):
     return out.cpu().numpy()
 
 
-@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("dt", DEQUANT_DTYPES)
 def test_dequant_bit_exact_vs_golden(cuda, torch_mod, golden, dt):
     name = synth.DTYPE_NAMES[dt]
     blocks = golden[f"{name}_blocks"]

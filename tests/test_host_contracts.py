@@ -12,7 +12,7 @@ import pytest
 from tensormark_b200 import synth
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K, synth.TQ2]
 _f32p = C.POINTER(C.c_float)
 
 
@@ -92,6 +92,7 @@ def test_gemv_pool_rows(hc, orc, dt):
     (synth.Q5_K, [(4, 4096), (2, 14336), (3, 256), (2, 768)]),
     (synth.Q6_K, [(4, 4096), (2, 14336), (3, 2048), (2, 256), (2, 5632)]),
     (synth.Q4_K, [(4, 4096), (2, 14336), (3, 256), (2, 768)]),
+    (synth.GGUF_Q4_0, [(5, 2048), (3, 5632), (3, 96), (2, 32)]),
 ])
 def test_gemv_lane_maps_on_cpu(lanes, orc, dt, shapes):
     """The kernel's lane decomposition, replayed on the CPU, against the fp64 reference.
@@ -192,3 +193,87 @@ def test_tmq_reader_accepts_and_rejects(hc, tmp_path):
     assert count(bytes(wrong_blocks)) == -1
     assert count(b"TMQ1" + struct.pack("<I", 1000)) == -1
     assert count(b"TMQ1" + struct.pack("<I", 0)) == 0                 # an empty container is a valid one
+
+
+# ---- GGUF files read natively (include/gguf_reader.h through tmmq::Mapped) ------------------------------------
+def _gguf_bytes(tensors, arch="llama", alignment=None, extra_kv=(), version=3, dup_key=False) -> bytes:
+    """Serialize [(gguf name, gguf type, dims innermost first, payload)] as a GGUF v3 file."""
+    import struct
+
+    def s(t: str) -> bytes:
+        b = t.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    kv = [s("general.architecture") + struct.pack("<I", 8) + s(arch)]
+    if alignment is not None:
+        kv.append(s("general.alignment") + struct.pack("<I", 4) + struct.pack("<I", alignment))
+    kv.append(s("general.name") + struct.pack("<I", 8) + s("synthetic"))
+    kv.append(s("llama.block_count") + struct.pack("<I", 4) + struct.pack("<I", 1))
+    kv.append(s("tokenizer.scores") + struct.pack("<I", 9) + struct.pack("<IQ", 6, 3) + struct.pack("<3f", 1, 2, 3))     # array of f32
+    kv.append(s("tokenizer.tokens") + struct.pack("<I", 9) + struct.pack("<IQ", 8, 2) + s("a") + s("bc"))                # array of strings
+    kv += list(extra_kv)
+    if dup_key:
+        kv.append(kv[2])
+    align = alignment or 32
+    infos, blobs, rel = [], [], 0
+    for name, typ, dims, payload in tensors:
+        infos.append(s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, rel))
+        pad = (-len(payload)) % align
+        blobs.append(payload + b"\0" * pad)
+        rel += len(payload) + pad
+    head = b"GGUF" + struct.pack("<IQQ", version, len(tensors), len(kv)) + b"".join(kv) + b"".join(infos)
+    head += b"\0" * ((-len(head)) % align)
+    return head + b"".join(blobs)
+
+
+def test_gguf_index_is_read_natively(hc, tmp_path):
+    hc.hc_tmq_count.argtypes = [C.c_char_p]
+    hc.hc_tmq_tensor.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong),
+                                 C.POINTER(C.c_uint), C.POINTER(C.c_uint)]
+    q4 = synth.make_weights(synth.GGUF_Q4_0, 6, 64, seed=1).tobytes()      # 6 x 64, GGUF type 2
+    q6 = synth.make_weights(synth.Q6_K, 3, 512, seed=2).tobytes()           # GGUF type 14
+    q8 = synth.make_weights(synth.Q8_0, 4, 64, seed=3).tobytes()            # GGUF type 8
+    nrm = np.arange(64, dtype=np.float32).tobytes()                         # GGUF type 0
+    bf = np.arange(128, dtype=np.uint16).tobytes()                          # GGUF type 30
+    tensors = [("blk.0.attn_q.weight", 2, (64, 6), q4), ("output.weight", 14, (512, 3), q6), ("token_embd.weight", 8, (64, 4), q8),
+               ("output_norm.weight", 0, (64,), nrm), ("blk.0.ffn_down.weight", 30, (64, 2), bf),
+               ("v.patch_embd.weight", 0, (64,), nrm)]                      # a vision tensor: indexed, not kept
+    good = _gguf_bytes(tensors)
+
+    def count(data: bytes) -> int:
+        p = tmp_path / "m.gguf"
+        p.write_bytes(data)
+        return hc.hc_tmq_count(str(p).encode())
+
+    assert count(good) == 5
+    dt, nb, off, rank = C.c_uint(), C.c_ulonglong(), C.c_ulonglong(), C.c_uint()
+    dims = (C.c_uint * 4)()
+    path = str(tmp_path / "m.gguf").encode()
+    # names are the engine's; shapes outermost first; GGUF's Q4_0 is container dtype 9, not 1 (tmq.h:446-457)
+    assert hc.hc_tmq_tensor(path, b"model.layers.0.self_attn.q_proj.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims)
+    assert (dt.value, nb.value, rank.value, dims[0], dims[1]) == (9, 12, 2, 6, 64)
+    assert good[off.value: off.value + len(q4)] == q4
+    assert hc.hc_tmq_tensor(path, b"lm_head.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims)
+    assert (dt.value, nb.value, dims[0], dims[1]) == (6, 6, 3, 512) and good[off.value: off.value + len(q6)] == q6
+    assert hc.hc_tmq_tensor(path, b"model.embed_tokens.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims) and dt.value == 0
+    assert hc.hc_tmq_tensor(path, b"model.norm.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims) and dt.value == 2
+    assert hc.hc_tmq_tensor(path, b"model.layers.0.mlp.down_proj.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims) and dt.value == 10
+    assert not hc.hc_tmq_tensor(path, b"v.patch_embd.weight", C.byref(dt), C.byref(nb), C.byref(off), C.byref(rank), dims)
+    assert count(_gguf_bytes(tensors, alignment=64)) == 5
+    # refusals (tensormark/gguf_native.h:142-222): other versions, truncated payload, duplicate metadata key, duplicate
+    # tensor name, an alignment that is not a power of two, a type outside the engine's set, rows that are not whole
+    # blocks, a zero dimension, five dimensions, overlapping payloads
+    import struct
+    assert count(_gguf_bytes(tensors, version=2)) == -1
+    assert count(good[:-40]) == -1
+    assert count(_gguf_bytes(tensors, dup_key=True)) == -1
+    assert count(_gguf_bytes(tensors + [("output.weight", 0, (64,), nrm)])) == -1
+    assert count(_gguf_bytes(tensors, alignment=48)) == -1
+    assert count(_gguf_bytes([("blk.0.attn_q.weight", 6, (64, 6), q4)])) == -1          # Q5_0 is not carried
+    assert count(_gguf_bytes([("blk.0.attn_q.weight", 2, (48, 8), q4)])) == -1
+    assert count(_gguf_bytes([("blk.0.attn_q.weight", 0, (0,), b"")])) == -1
+    assert count(_gguf_bytes([("blk.0.attn_q.weight", 0, (2, 2, 2, 2, 4), nrm)])) == -1
+    over = bytearray(_gguf_bytes([("a.weight", 0, (64,), nrm), ("b.weight", 0, (64,), nrm)]))
+    i = over.rindex(struct.pack("<IQ", 0, 256))                                         # second tensor's (type, offset)
+    over[i: i + 12] = struct.pack("<IQ", 0, 128)
+    assert count(bytes(over)) == -1

@@ -7,7 +7,7 @@ import pytest
 from oracle import binding
 from tensormark_b200 import synth
 
-DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K]
+DTYPES = [synth.Q8_0, synth.Q4_0, synth.Q4_1, synth.Q5_K, synth.Q6_K, synth.Q4_K, synth.TQ2]
 
 
 @pytest.mark.parametrize("dt", DTYPES)
@@ -20,7 +20,7 @@ def test_dequant_matches_golden(orc, golden, dt):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("dt", [synth.Q8_0, synth.Q4_0])
+@pytest.mark.parametrize("dt", [synth.Q8_0, synth.Q4_0, synth.TQ2])
 def test_dequant_of_reference_quantized_rows(orc, golden, dt):
     name = synth.DTYPE_NAMES[dt]
     q = golden[f"{name}_quantized_blocks"]
@@ -29,8 +29,10 @@ def test_dequant_of_reference_quantized_rows(orc, golden, dt):
     assert np.array_equal(got, want)
     # round trip stays inside half a quantization step of the source (sanity on the fixture itself)
     x = golden[f"{name}_quantized_from"]
-    step = np.abs(x).reshape(-1, 32).max(axis=1) / (127.0 if dt == synth.Q8_0 else 8.0)
-    err = np.abs(got.view(np.float32) - x).reshape(-1, 32).max(axis=1)
+    be = synth.BLOCK_ELEMS[dt]
+    # ternary: d = max|x| and codes -1, 0, +1, so a value can be off by half of d (plus the fp16 rounding of d)
+    step = np.abs(x).reshape(-1, be).max(axis=1) / {synth.Q8_0: 127.0, synth.Q4_0: 8.0, synth.TQ2: 2.0}[dt]
+    err = np.abs(got.view(np.float32) - x).reshape(-1, be).max(axis=1)
     assert np.all(err <= step * 1.01 + 1e-12)
 
 
@@ -124,3 +126,21 @@ def test_glue_restatements(orc):
     g = rng.standard_normal(64).astype(np.float32); u = rng.standard_normal(64).astype(np.float32)
     assert np.allclose(orc.silu_mul(g, u), g / (1 + np.exp(-g.astype(np.float64))) * u, rtol=1e-5, atol=1e-6)
     assert orc.argmax(np.array([1, 5, 5, 2], np.float32)) == 1      # ties -> lowest index
+
+
+def test_gguf_q4_0_equals_repacked_q4_0(orc):
+    """Container dtype 9 (GGUF's split-nibble Q4_0, tensormark/llama.h:4588-4597) holds the same weights as the block the
+    converter's nibble reorder makes of it (tensormark/convert_gguf.cpp:124-135): two independent statements of the
+    layout, one checked against the other bit for bit, on random blocks and on the golden special-scale blocks."""
+    import numpy as np
+    from tensormark_b200 import synth
+    W = synth.make_weights(synth.GGUF_Q4_0, 64, 2048, seed=9)
+    a = orc.dequant(synth.GGUF_Q4_0, W, 64 * 2048)
+    b = orc.dequant(synth.Q4_0, orc.q4_split_to_interleaved(W), 64 * 2048)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # and it is NOT the interleaved reading of the same bytes
+    assert not np.array_equal(a, orc.dequant(synth.Q4_0, W, 64 * 2048))
+    # element j comes from the low nibble of byte j, element j + 16 from its high nibble
+    blk = np.zeros(18, np.uint8); blk[0:2] = np.array([1.0], np.float16).view(np.uint8); blk[2] = 0x3C
+    x = orc.dequant(synth.GGUF_Q4_0, blk, 32)
+    assert x[0] == 0xC - 8 and x[16] == 0x3 - 8 and x[1] == -8

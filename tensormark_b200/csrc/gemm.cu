@@ -23,13 +23,15 @@
 // C[token][row]; for a fixed token the 32 lanes of a warp write 32 consecutive rows,
 // one coalesced 128-byte store).
 //
-// Q4_0 weights never exist as an fp16 matrix in memory: eight producer warps read the 18-byte
-// blocks of their tile rows straight from global memory, turn the nibbles into (n - 8) * d with
-// two half2 instructions per pair (the exact product rounded once to fp16, the same value the
-// fp32 dequantizer rounded to fp16 gives) and store them into the stage in the 128-byte-swizzled
-// K-major layout the MMA descriptor expects, followed by a proxy fence and an arrive on the
-// stage's barrier. TMA then only carries the activations. Other formats take a pre-pass that
-// writes the fp16 weight matrix to the workspace, and both operands come by TMA.
+// Two forms. The default (gemm_f16_tn) takes both operands by TMA from an fp16 copy that one pre-pass
+// launch writes to the workspace (weights dequantized exactly and rounded once, activations rounded
+// once). The other (gemm_q4_tn, TM_GEMM_FUSED=1, Q4_0 only) never materialises the fp16 weights: eight
+// producer warps take the rows' 18-byte blocks from a bulk-copied raw ring, turn the nibbles into
+// (n - 8) * d with two half2 instructions per pair (the same value the fp32 dequantizer rounded to fp16
+// gives) and store them into the stage in the 128-byte-swizzled K-major layout the MMA descriptor
+// expects, followed by a proxy fence and an arrive on the stage's barrier; TMA then only carries the
+// activations. It is the slower of the two today (its producers wait on their barriers while the tensor
+// pipe idles), which is why the pre-pass form is the default.
 //
 // Operand precision: weights are dequantized exactly to fp32 and rounded once to
 // fp16; activations are rounded once to fp16. Each product then carries at most

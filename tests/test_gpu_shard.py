@@ -46,6 +46,9 @@ def test_sharded_chain_matches_single_gpu(torch_mod, tmp_path):
         assert two["n_gpus"] == 2 and two["tokens_equal_on_all_ranks"], gather
         assert two["last_logits_max_abs_diff_across_ranks"] == 0.0, gather     # every rank holds the same gathered logits
         got = np.load(path)
-        tol = 1e-4 * max(1.0, float(np.abs(ref).max()))
+        # The sharded lane computes SiLU*up in a kernel of its own (NCCL form) or stages other vectors than the one-GPU
+        # lane; a last-bit difference in an activation can move its fixed-point rounding by one step, so the two runs
+        # agree to the GEMV's own accuracy (a few 1e-5 of sum|w x| per dot), not bit for bit: 1e-3 of the largest logit.
+        tol = 1e-3 * max(1.0, float(np.abs(ref).max()))
         assert float(np.abs(got - ref).max()) <= tol, (gather, float(np.abs(got - ref).max()), tol)
         assert two["first_tokens"] == one["first_tokens"], gather

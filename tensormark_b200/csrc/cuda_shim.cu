@@ -236,6 +236,26 @@ bool tm_cuda_gemv_q(const float* x, const void* W, float* y, unsigned N, unsigne
     }
     if (!direct) dy = (float*)s.io_y.get((size_t)N * 4);
     if (!dy) return fail("gemv: out of device memory");
+    // x in page-locked host memory is not copied by the DMA engine (a dozen microseconds before the kernel can start):
+    // the staging kernel reads it over PCIe once, 4 K bytes, and leaves it in the form the GEMV's lanes consume; the GEMV
+    // then copies that image instead of staging x in every CTA. Pageable x takes the copy.
+    {
+        cudaPointerAttributes ax;
+        const size_t img = xq_bytes(K, dtype);
+        if (img && cudaPointerGetAttributes(&ax, x) == cudaSuccess && ax.type == cudaMemoryTypeHost && ax.devicePointer &&
+            (uintptr_t)ax.devicePointer % 16 == 0) {
+            uint32_t* xq = (uint32_t*)s.io_xq.get(img);
+            if (!xq) return fail("gemv: out of device memory");
+            const float* xm = (const float*)ax.devicePointer;
+            if (!launch_xprep(xq, xm, nullptr, 0, 0.f, K, dtype, nullptr, s.stream)) return false;
+            GemvFuse f{};
+            f.xq = xq;
+            if (!launch_gemv(xm, dW, dy, N, K, dtype, one_segment(N), s.stream, &f)) return false;
+            if (!direct && cudaMemcpyAsync(y, dy, (size_t)N * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("gemv: y download");
+            return sync_stream(s.stream, "gemv");
+        }
+        cudaGetLastError();
+    }
     if (cudaMemcpyAsync(dx, x, (size_t)K * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("gemv: x upload");
     if (!launch_gemv(dx, dW, dy, N, K, dtype, one_segment(N), s.stream)) return false;
     if (!direct && cudaMemcpyAsync(y, dy, (size_t)N * 4, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess) return check_launch("gemv: y download");

@@ -61,7 +61,7 @@ struct State {
 
     // per-tensor host-pointer entries
     std::map<std::pair<const void*, size_t>, uint8_t*> wcache;
-    Scratch io_x, io_y, io_big, io_a, gemm_ws;
+    Scratch io_x, io_y, io_big, io_a, io_xq, gemm_ws;
 
     // token lane
     std::vector<Slot> slots;

@@ -59,7 +59,10 @@ constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitNs = 2000000000ull;
-constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 256 + 1024;   // tiles + barriers + alignment slack
+constexpr int kMaxStages = 8;
+constexpr uint32_t kTileRegion = 225u * 1024u;      // operand ring: as many stages of 16 KB + bn x 128 B as fit (4 at bn = 256)
+constexpr size_t kSmemBytes = (size_t)kTileRegion + 256 + 1024;              // ring + barriers + alignment slack
+static_assert(kStages * STAGE_BYTES <= kTileRegion && kSmemBytes <= 227u * 1024u, "shared memory budget");
 
 // kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N=256, M=128
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -138,24 +141,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// tmA: weights as fp16 [n_rows][K], box 64 x 128.  tmB: activations as fp16 [m_tok][K], box 64 x 256.
+// tmA: weights as fp16 [n_rows][K], box 64 x 128.  tmB: activations as fp16 [m_tok][K], box 64 x bn.
+// bn = tokens per tile (UMMA N): a multiple of 16 up to BN = 256, chosen per call so that the tiles fill whole waves of
+// the persistent grid (pick_token_tile). A narrower tile makes a smaller stage, and the ring then holds more of them:
+// the bytes in flight per SM, which is what covers the L2 latency, stay the same. The TMEM stride stays 256 columns.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, int* status) {
+            float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + (size_t)kStages * STAGE_BYTES);
-    uint64_t* empty = full + kStages;
-    uint64_t* tfull = empty + kStages;
+    uint64_t* full = (uint64_t*)(smem + kTileRegion);
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tfull = empty + kMaxStages;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t num_kb = (K + BK - 1) / BK;
-    const uint32_t tiles_n = (n_rows + BM - 1) / BM, tiles_m = (m_tok + BN - 1) / BN, tiles = tiles_n * tiles_m;
+    const uint32_t tiles_n = (n_rows + BM - 1) / BM, tiles_m = (m_tok + bn - 1) / bn, tiles = tiles_n * tiles_m;
+    const uint32_t idesc = (1u << 4) | ((bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);      // kIdesc with N = bn
+    const uint32_t stage_bytes = A_BYTES + bn * (uint32_t)(BK * 2);                           // a multiple of 1024
+    const uint32_t stages = min((uint32_t)kMaxStages, kTileRegion / stage_bytes);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -176,12 +185,12 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
-                const int n0 = (int)(tile / tiles_m) * BM, m0 = (int)(tile % tiles_m) * BN;
+                const int n0 = (int)(tile / tiles_m) * BM, m0 = (int)((tile % tiles_m) * bn);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
-                    uint8_t* a = smem + (size_t)s * STAGE_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t* a = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full[s], stage_bytes);
                     tma_load_2d(a, &tmA, (int)(kb * BK), n0, &full[s]);
                     tma_load_2d(a + A_BYTES, &tmB, (int)(kb * BK), m0, &full[s]);
                 }
@@ -196,13 +205,13 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
                     if (!mbar_wait(&full[s], ph)) { dead = true; break; }
                     tc_fence_after();
-                    const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_f16(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(a + A_BYTES + k * UMMA_K * 2), kIdesc,
+                        umma_f16(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(a + A_BYTES + k * UMMA_K * 2), idesc,
                                  (kb | (uint32_t)k) ? 1u : 0u);
                     umma_commit(&empty[s]);            // the stage is free once these MMAs have read it
                 }
@@ -215,20 +224,20 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t tcount = 0;
         for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x, ++tcount) {
             const uint32_t buf = tcount & 1u;
-            const uint32_t n0 = (tile / tiles_m) * BM, m0 = (tile % tiles_m) * BN;
+            const uint32_t n0 = (tile / tiles_m) * BM, m0 = (tile % tiles_m) * bn;
             if (!mbar_wait(&tfull[buf], (tcount >> 1) & 1u)) { dead = true; break; }
             tc_fence_after();
             const uint32_t row = n0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((q * 32u) << 16);
-            for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 32) {
+            for (uint32_t c0 = 0; c0 < bn; c0 += 32) {
                 if (m0 + c0 >= m_tok) break;            // warp-uniform: whole column block past the last token
                 uint32_t v[32];
-                tmem_ld32(taddr + c0, v);
+                tmem_ld32(taddr + c0, v);               // a 16-column remainder reads 16 stale columns of the buffer: masked below
                 if (row < n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + c0 + j;
-                        if (m < m_tok) C[(size_t)m * ldc + row] = __uint_as_float(v[j]);
+                        if (c0 + j < bn && m < m_tok) C[(size_t)m * ldc + row] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -242,6 +251,167 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+
+// ---- the same GEMM on CTA pairs (tcgen05 cta_group::2) ----------------------------------------------------------
+// Two CTAs of a cluster share one 256 x bn tile: each loads its own 128 weight rows and HALF of the token rows
+// (16 KB + 16 KB per k-block at bn = 256 instead of 16 KB + 32 KB, so the ring holds 7 stages instead of 4); the MMA,
+// issued by the even CTA for both, reads the token rows out of both CTAs' shared memory, and each CTA's 128 x bn
+// accumulator lands in its own TMEM. Measured against the one-CTA kernel on the same GPU (2000 tokens, fp16 operands
+// resident in L2 or HBM alike): 3 % faster on the 32000 x 2048 head (14 waves of tiles), equal on 5632 x 2048, 3 %
+// slower on 2048 x 5632 (one wave) - operand delivery is not what bounds the one-CTA kernel, so halving it buys
+// little. The launcher takes this kernel where there are at least four waves of tiles.
+//
+// Barriers: the loads of both CTAs count on the EVEN CTA's full[s] (a TMA load may signal the pair's other CTA);
+// empty[s] and tfull[buf] are raised in both CTAs by one multicast commit; the epilogue warps of both CTAs arrive
+// on the even CTA's tempty[buf] (256 arrivals). Every wait is bounded like the single-CTA kernel's.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {      // shared::cta address -> shared::cluster address in CTA `rank`
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t z = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {        // arrives on `bar` at this offset in both CTAs
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+
+// tmA: box 64 x 128 of the fp16 weights. tmB: box 64 x bn/2 of the fp16 activations. bn: tokens per pair tile, a
+// multiple of 32 up to 256. Grid: an even number of CTAs, clusters of two.
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // the same offset in both CTAs
+    uint64_t* full = (uint64_t*)(smem + kTileRegion);
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tfull = empty + kMaxStages;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs and owns full[] and tempty[]
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const uint32_t half = bn >> 1;
+    const uint32_t num_kb = (K + BK - 1) / BK;
+    const uint32_t tiles_n = (n_rows + 2 * BM - 1) / (2 * BM), tiles_m = (m_tok + bn - 1) / bn, tiles = tiles_n * tiles_m;
+    const uint32_t idesc = (1u << 4) | ((bn >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);   // M = 256 over the pair, N = bn
+    const uint32_t stage_bytes = A_BYTES + half * (uint32_t)(BK * 2);                            // per CTA; a multiple of 1024
+    const uint32_t stages = min((uint32_t)kMaxStages, kTileRegion / stage_bytes);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 256); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();                                          // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool dead = false;
+    asm volatile("griddepcontrol.wait;" ::: "memory");           // the pre-pass has written the fp16 operands
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs) {
+                const int n0 = (int)((tile / tiles_m) * 2 * BM + rank * BM), m0 = (int)((tile % tiles_m) * bn + rank * half);
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
+                    uint8_t* a = smem + (size_t)s * stage_bytes;
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
+                    const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+                    tma_load_2d_pair(a, &tmA, (int)(kb * BK), n0, bar);           // rows or tokens past the end arrive as zeros
+                    tma_load_2d_pair(a + A_BYTES, &tmB, (int)(kb * BK), m0, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, tcount = 0;
+            for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs, ++tcount) {
+                const uint32_t buf = tcount & 1u;
+                if (!mbar_wait(&tempty[buf], ((tcount >> 1) & 1u) ^ 1u)) { dead = true; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                    if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_f16_pair(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(a + A_BYTES + k * UMMA_K * 2), idesc,
+                                      (kb | (uint32_t)k) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (dead) break;
+                umma_commit_pair(&tfull[buf]);
+            }
+        }
+    } else {
+        const uint32_t q = (uint32_t)warp & 3u;
+        uint32_t tcount = 0;
+        for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs, ++tcount) {
+            const uint32_t buf = tcount & 1u;
+            const uint32_t n0 = (tile / tiles_m) * 2 * BM + rank * BM, m0 = (tile % tiles_m) * bn;
+            if (!mbar_wait(&tfull[buf], (tcount >> 1) & 1u)) { dead = true; break; }
+            tc_fence_after();
+            const uint32_t row = n0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + ((q * 32u) << 16);
+            for (uint32_t c0 = 0; c0 < bn; c0 += 32) {
+                if (m0 + c0 >= m_tok) break;
+                uint32_t v[32];
+                tmem_ld32(taddr + c0, v);
+                if (row < n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t m = m0 + c0 + j;
+                        if (m < m_tok) C[(size_t)m * ldc + row] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[buf]), 0));
+        }
+    }
+    if (dead) *(volatile int*)status = 2;
+    tc_fence_before();
+    cluster_sync_all();                  // neither CTA leaves, or frees its TMEM, while the other may still signal or read it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -589,6 +759,45 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K, uint3
     return true;
 }
 
+// Tokens per tile. The persistent grid runs the tiles in waves of one per SM, and a call's time is (waves) x (time of
+// a tile), so a tile width that fills the last wave beats the widest one: 2000 tokens against 5632 rows are 352 tiles
+// of 256 tokens = 2.38 waves run as 3, but 440 tiles of 208 tokens = 2.97 waves. A tile's time is modelled as
+// 128 + bn (the kernel is bound by operand delivery: 128 weight rows + bn token rows per k-block). Widths below 64
+// are only taken when the whole batch is narrower.
+unsigned pick_token_tile(unsigned M, unsigned N, unsigned sms) {
+    static const int forced = [] { const char* e = std::getenv("TM_GEMM_BN"); return e && *e ? std::atoi(e) : 0; }();   // A/B knob
+    if (forced >= 16 && forced <= BN && forced % 16 == 0) return (unsigned)forced;
+    const unsigned rt = (N + BM - 1) / BM;
+    if (M <= 64) return (M + 15) / 16 * 16;
+    unsigned best = BN;
+    unsigned long long best_cost = ~0ull;
+    for (unsigned bn = BN; bn >= 64; bn -= 16) {
+        const unsigned long long tiles = (unsigned long long)rt * ((M + bn - 1) / bn), waves = (tiles + sms - 1) / sms;
+        const unsigned long long cost = waves * (128 + bn);
+        if (cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+// The same for the CTA-pair kernel: 256 weight rows x bn tokens per pair of SMs, bn a multiple of 32. Per k-block a
+// CTA takes 16 KB + bn x 64 B from L2 at 64 B per clock (256 + bn clocks) while the pair's MMAs run about 2.1 clocks
+// per token column; the slower of the two is the tile's time.
+unsigned pick_token_tile_pair(unsigned M, unsigned N, unsigned sms) {
+    static const int forced = [] { const char* e = std::getenv("TM_GEMM_BN"); return e && *e ? std::atoi(e) : 0; }();
+    if (forced >= 32 && forced <= BN && forced % 32 == 0) return (unsigned)forced;
+    const unsigned rt = (N + 2 * BM - 1) / (2 * BM), pairs = sms / 2 ? sms / 2 : 1;
+    if (M <= 64) return (M + 31) / 32 * 32;
+    unsigned best = BN;
+    unsigned long long best_cost = ~0ull;
+    for (unsigned bn = BN; bn >= 64; bn -= 32) {
+        const unsigned long long tiles = (unsigned long long)rt * ((M + bn - 1) / bn), waves = (tiles + pairs - 1) / pairs;
+        const unsigned long long l2 = 256 + bn, mma = (unsigned long long)bn * 21 / 10;
+        const unsigned long long cost = waves * (l2 > mma ? l2 : mma);
+        if (cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 }  // namespace
 
 size_t gemm_workspace_bytes(unsigned M, unsigned N, unsigned K) {
@@ -638,7 +847,39 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     }
 
     CUtensorMap tmA, tmB;
-    if (!make_map(&tmB, Ah, M, K, BN)) return false;
+    // Two SMs per tile (gemm_f16_tn_pair) where it measured faster: four or more waves of pair tiles. TM_GEMM_PAIR=0
+    // keeps one SM per tile everywhere, TM_GEMM_PAIR=1 pairs wherever there are 256 weight rows.
+    static const int pair_mode = [] { const char* e = std::getenv("TM_GEMM_PAIR"); return e && *e ? std::atoi(e) : -1; }();
+    const unsigned sms = (unsigned)device_sm_count();
+    const unsigned bn2 = pick_token_tile_pair(M, N, sms);
+    const unsigned long long pair_tiles = (unsigned long long)((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
+    const bool paired = !fused && N >= 2 * BM && sms >= 2 && (pair_mode == 1 || (pair_mode < 0 && pair_tiles >= 4ull * (sms / 2)));
+    if (paired) {
+        if (!make_map(&tmB, Ah, M, K, bn2 / 2) || !make_map(&tmA, Wh, N, K, BM)) return false;
+        static bool attr2 = false;
+        if (!attr2) {
+            if (cudaFuncSetAttribute(gemm_f16_tn_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+                return check_launch("gemm: shared memory attribute");
+            attr2 = true;
+        }
+        const unsigned tiles2 = ((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
+        const unsigned pairs = sms / 2 < tiles2 ? sms / 2 : tiles2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+        cudaLaunchAttribute at[2];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        at[1].id = cudaLaunchAttributeClusterDimension;
+        at[1].val.clusterDim.x = 2; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 2;
+        if (cudaLaunchKernelEx(&cfg, gemm_f16_tn_pair, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn2,
+                               device_status_word()) != cudaSuccess)
+            return check_launch("gemm_f16_tn_pair");
+        note_launch();
+        return check_launch("gemm_f16_tn_pair");
+    }
+    const unsigned bn = fused ? (unsigned)BN : pick_token_tile(M, N, sms);
+    if (!make_map(&tmB, Ah, M, K, bn)) return false;
     if (fused) {
         static bool attr4 = false;
         if (!attr4) {
@@ -660,7 +901,7 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
             return check_launch("gemm: shared memory attribute");
         attr = true;
     }
-    const unsigned tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
+    const unsigned tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     unsigned grid = (unsigned)device_sm_count();
     if (grid > tiles) grid = tiles;
     cudaLaunchConfig_t cfg = {};
@@ -669,7 +910,8 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, device_status_word()) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn,
+                           device_status_word()) != cudaSuccess)
         return check_launch("gemm_f16_tn");
     note_launch();
     return check_launch("gemm_f16_tn");

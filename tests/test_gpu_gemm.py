@@ -39,9 +39,12 @@ def _check_samples(orc, dt, W, A, Cm, n, k, ns=4096, seed=0):
 
 @pytest.mark.parametrize("dt,m,n,k", [
     (synth.Q4_0, 64, 256, 512),        # one tile, short K
+    (synth.Q4_0, 40, 256, 512),        # a 48-token tile: the last 32-column read of the accumulator is half stale
+    (synth.Q4_0, 7, 128, 64),          # the narrowest tile, one k-block
     (synth.Q4_0, 300, 384, 2048),      # ragged token tile
     (synth.Q4_0, 257, 130, 96),        # ragged in both, K not a multiple of 64
     (synth.Q6_K, 100, 256, 1024),
+    (synth.Q4_0, 500, 640, 320),       # two and a half pairs of row tiles, five k-blocks
     (synth.Q8_0, 50, 128, 256),
     (synth.Q4_1, 50, 128, 256),
     (synth.Q5_K, 50, 128, 512),
@@ -99,5 +102,21 @@ def test_q4_kernel_with_in_kernel_dequant(torch_mod):
     env = dict(os.environ, TM_GEMM_FUSED="1")
     sel = "test_small_shapes_full_check or (test_config4_prefill_shapes_sampled and not 32000)"
     r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_gemm.py", "-q", "-x", "-k", sel],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("pair,bn", [(0, 16), (0, 80), (0, 144), (0, 208), (0, 256), (1, 32), (1, 96), (1, 160), (1, 224)])
+def test_token_tile_widths(torch_mod, pair, bn):
+    """The token tile is chosen per call (tiles that fill whole waves of the persistent grid); TM_GEMM_BN pins it, at
+    first use, so that every class of width (multiples of 32 and 16-column remainders, one and many token tiles) meets
+    the full-check shapes - on the kernel with one SM per tile (TM_GEMM_PAIR=0) and on the CTA-pair kernel, which is
+    the default wherever there are 256 weight rows."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TM_GEMM_BN=str(bn), TM_GEMM_PAIR=str(pair))
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_gemm.py", "-q", "-x", "-k", "test_small_shapes_full_check"],
                        cwd=root, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

@@ -56,7 +56,8 @@ constexpr int BK = 64;               // fp16 per tile row: 128 bytes, one swizzl
 constexpr int kStages = 4;
 constexpr int UMMA_K = 16;
 constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;          // the Q4_0 in-kernel form: producer, MMA issuer, four epilogue warps (+ its dequantizing warps)
+constexpr int kThreadsTma = 224;       // the two TMA-fed kernels: one more warp, so that each operand has its own issuing thread
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitNs = 2000000000ull;
 constexpr int kMaxStages = 8;
@@ -86,6 +87,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// One probe, never suspends the thread (try_wait costs ~200 clocks even on a completed phase, test_wait ~80).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -93,6 +104,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Bounded wait; false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_test(bar, parity)) return true;
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
@@ -123,6 +135,36 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The four MMAs of one 64-wide k-block (operand tiles at shared addresses a and b, K advancing 32 bytes per MMA inside
+// the swizzle atom) and, issued BEFORE them, a probe of the barrier the next k-block will need; the probe's answer is
+// only read after the MMAs are out, so its latency hides behind them. The issuing thread is the kernel's narrowest
+// point: a probe, four MMAs and a commit have to fit into the 512 clocks the tensor pipe needs for N = 256.
+__device__ __forceinline__ uint64_t umma_desc_at(uint32_t lo, uint32_t k) {       // lo = umma_desc's low word for the tile's start
+    constexpr uint32_t hi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | (uint64_t)(lo + 2u * k);                        // 32 bytes = 2 units of 16
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ bool umma_kblock(uint32_t tmem_d, uint32_t a, uint32_t b, uint32_t idesc, uint32_t acc_first,
+                                            uint64_t* next_bar, uint32_t next_parity) {
+    const uint32_t la = umma_desc_lo(a), lb = umma_desc_lo(b);
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t"
+        "setp.ne.b32 q, %12, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%13], %14;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %10, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %4, %5, %10, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %6, %7, %10, t;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %8, %9, %10, t;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tmem_d), "l"(umma_desc_at(la, 0)), "l"(umma_desc_at(lb, 0)), "l"(umma_desc_at(la, 1)), "l"(umma_desc_at(lb, 1)),
+          "l"(umma_desc_at(la, 2)), "l"(umma_desc_at(lb, 2)), "l"(umma_desc_at(la, 3)), "l"(umma_desc_at(lb, 3)),
+          "r"(idesc), "r"(0), "r"(acc_first), "r"(smem_u32(next_bar)), "r"(next_parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -145,7 +187,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 // bn = tokens per tile (UMMA N): a multiple of 16 up to BN = 256, chosen per call so that the tiles fill whole waves of
 // the persistent grid (pick_token_tile). A narrower tile makes a smaller stage, and the ring then holds more of them:
 // the bytes in flight per SM, which is what covers the L2 latency, stay the same. The TMEM stride stays 256 columns.
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsTma, 1)
 gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -181,39 +223,47 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // writes the fp16 operands; nothing below may start before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
+        // One issuing thread per operand, in warps of different SM sub-partitions: a thread's bulk-tensor copies go out
+        // about 230-320 ns apart whatever their size (measured: 4 KB to 32 KB boxes, 2 to 16 in flight, 1 to 148 CTAs),
+        // so one thread issuing both operands of a k-block is slower than the four MMAs that consume them; two threads
+        // issue side by side. Warp 0 announces the stage's bytes and loads the weight rows, warp 6 the token rows
+        // (its bytes may land on the barrier before the announcement: the phase still needs warp 0's arrival).
         if (lane == 0) {
-            uint32_t it = 0;
+            const bool weights = warp == 0;
+            uint32_t s = 0, ph = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
                 const int n0 = (int)(tile / tiles_m) * BM, m0 = (int)((tile % tiles_m) * bn);
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ph ^= (++s == stages), s = s == stages ? 0 : s) {
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
                     uint8_t* a = smem + (size_t)s * stage_bytes;
-                    mbar_expect_tx(&full[s], stage_bytes);
-                    tma_load_2d(a, &tmA, (int)(kb * BK), n0, &full[s]);
-                    tma_load_2d(a + A_BYTES, &tmB, (int)(kb * BK), m0, &full[s]);
+                    if (weights) {
+                        mbar_expect_tx(&full[s], stage_bytes);
+                        tma_load_2d(a, &tmA, (int)(kb * BK), n0, &full[s]);
+                    } else {
+                        tma_load_2d(a + A_BYTES, &tmB, (int)(kb * BK), m0, &full[s]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            uint32_t s = 0, ph = 0, tcount = 0;
+            bool ready = false;                                  // what the probe issued with the previous k-block said
             for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x, ++tcount) {
                 const uint32_t buf = tcount & 1u;
                 if (!mbar_wait(&tempty[buf], ((tcount >> 1) & 1u) ^ 1u)) { dead = true; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
-                    if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ready && !mbar_wait(&full[s], ph)) { dead = true; break; }
                     tc_fence_after();
-                    const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_f16(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(a + A_BYTES + k * UMMA_K * 2), idesc,
-                                 (kb | (uint32_t)k) ? 1u : 0u);
+                    const uint32_t a = smem_u32(smem) + s * stage_bytes;
+                    uint32_t s1 = s + 1, ph1 = ph;
+                    if (s1 == stages) { s1 = 0; ph1 ^= 1u; }
+                    ready = umma_kblock(d_tmem, a, a + A_BYTES, idesc, kb ? 1u : 0u, &full[s1], ph1);
                     umma_commit(&empty[s]);            // the stage is free once these MMAs have read it
+                    s = s1; ph = ph1;
                 }
                 if (dead) break;
                 umma_commit(&tfull[buf]);              // accumulator complete
@@ -256,13 +306,16 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 
 // ---- the same GEMM on CTA pairs (tcgen05 cta_group::2) ----------------------------------------------------------
-// Two CTAs of a cluster share one 256 x bn tile: each loads its own 128 weight rows and HALF of the token rows
-// (16 KB + 16 KB per k-block at bn = 256 instead of 16 KB + 32 KB, so the ring holds 7 stages instead of 4); the MMA,
-// issued by the even CTA for both, reads the token rows out of both CTAs' shared memory, and each CTA's 128 x bn
-// accumulator lands in its own TMEM. Measured against the one-CTA kernel on the same GPU (2000 tokens, fp16 operands
-// resident in L2 or HBM alike): 3 % faster on the 32000 x 2048 head (14 waves of tiles), equal on 5632 x 2048, 3 %
-// slower on 2048 x 5632 (one wave) - operand delivery is not what bounds the one-CTA kernel, so halving it buys
-// little. The launcher takes this kernel where there are at least four waves of tiles.
+// Two CTAs of a cluster share one 256 x bn tile: each loads its own 128 weight rows and HALF of the token rows; the
+// MMA, issued by the even CTA for both, reads the token rows out of both CTAs' shared memory, and each CTA's 128 x bn
+// accumulator lands in its own TMEM. Two things are gained. Operand delivery: 16 KB + bn x 64 B per CTA and 64 columns
+// of K instead of 16 KB + bn x 128 B (at bn = 256 the one-CTA kernel asks L2 for 94 bytes per clock and SM, about what
+// one SM gets; its MMA thread then waits for operands a fifth of the time). Issue rate: one issued MMA drives both
+// SMs' tensor pipes, and a stage here is two swizzle atoms of K (128 columns), so the issuing thread spends one
+// barrier probe and one commit per EIGHT MMAs.
+// Same-GPU A/B against the one-CTA kernel, 2000 tokens: 6 % faster on the 32000 x 2048 head (14 waves of tiles),
+// 1-2 % slower on 5632 x 2048 and 2048 x 5632 (three waves, one wave); the launcher takes this kernel from four waves
+// of pair tiles.
 //
 // Barriers: the loads of both CTAs count on the EVEN CTA's full[s] (a TMA load may signal the pair's other CTA);
 // empty[s] and tfull[buf] are raised in both CTAs by one multicast commit; the epilogue warps of both CTAs arrive
@@ -288,13 +341,34 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
 }
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    const uint32_t z = 0;
+// Two swizzle atoms (128 columns of K) in one go: eight MMAs behind one probe and before one commit. `a` and `b` are
+// the first atoms, the second ones lie a_step / b_step bytes further.
+__device__ __forceinline__ bool umma_kblock2_pair(uint32_t tmem_d, uint32_t a, uint32_t b, uint32_t a_step, uint32_t b_step, uint32_t idesc,
+                                                  uint32_t acc_first, uint64_t* next_bar, uint32_t next_parity) {
+    const uint32_t la = umma_desc_lo(a), lb = umma_desc_lo(b), la1 = la + (a_step >> 4), lb1 = lb + (b_step >> 4);
+    uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+        "{\n\t.reg .pred p, q, t;\n\t"
+        "setp.ne.b32 q, %20, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%21], %22;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, q;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %4, %5, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %6, %7, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %8, %9, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %10, %11, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %12, %13, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %14, %15, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %16, %17, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tmem_d), "l"(umma_desc_at(la, 0)), "l"(umma_desc_at(lb, 0)), "l"(umma_desc_at(la, 1)), "l"(umma_desc_at(lb, 1)),
+          "l"(umma_desc_at(la, 2)), "l"(umma_desc_at(lb, 2)), "l"(umma_desc_at(la, 3)), "l"(umma_desc_at(lb, 3)),
+          "l"(umma_desc_at(la1, 0)), "l"(umma_desc_at(lb1, 0)), "l"(umma_desc_at(la1, 1)), "l"(umma_desc_at(lb1, 1)),
+          "l"(umma_desc_at(la1, 2)), "l"(umma_desc_at(lb1, 2)), "l"(umma_desc_at(la1, 3)), "l"(umma_desc_at(lb1, 3)),
+          "r"(idesc), "r"(0), "r"(acc_first), "r"(smem_u32(next_bar)), "r"(next_parity)
+        : "memory");
+    return ok != 0;
 }
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {        // arrives on `bar` at this offset in both CTAs
     const uint16_t both = 3;
@@ -303,8 +377,9 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {        // arri
 }
 
 // tmA: box 64 x 128 of the fp16 weights. tmB: box 64 x bn/2 of the fp16 activations. bn: tokens per pair tile, a
-// multiple of 32 up to 256. Grid: an even number of CTAs, clusters of two.
-__global__ void __launch_bounds__(kThreads, 1)
+// multiple of 32 up to 256. Grid: an even number of CTAs, clusters of two. A stage per CTA: two weight atoms (2 x 16 KB),
+// then two token atoms (2 x bn/2 x 128 B); three stages at bn = 256.
+__global__ void __launch_bounds__(kThreadsTma, 1)
 gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -319,10 +394,11 @@ gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs and owns full[] and tempty[]
     const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const uint32_t half = bn >> 1;
-    const uint32_t num_kb = (K + BK - 1) / BK;
+    const uint32_t num_kb = (K + 2 * BK - 1) / (2 * BK);         // a stage is TWO swizzle atoms of K: half as many probes and commits per MMA
     const uint32_t tiles_n = (n_rows + 2 * BM - 1) / (2 * BM), tiles_m = (m_tok + bn - 1) / bn, tiles = tiles_n * tiles_m;
     const uint32_t idesc = (1u << 4) | ((bn >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);   // M = 256 over the pair, N = bn
-    const uint32_t stage_bytes = A_BYTES + half * (uint32_t)(BK * 2);                            // per CTA; a multiple of 1024
+    const uint32_t atom_b = half * (uint32_t)(BK * 2);                                           // one atom of this CTA's token rows
+    const uint32_t stage_bytes = 2 * (A_BYTES + atom_b);                                         // per CTA; a multiple of 1024
     const uint32_t stages = min((uint32_t)kMaxStages, kTileRegion / stage_bytes);
 
     if (threadIdx.x == 0) {
@@ -341,40 +417,46 @@ gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool dead = false;
     asm volatile("griddepcontrol.wait;" ::: "memory");           // the pre-pass has written the fp16 operands
 
-    if (warp == 0) {
-        if (lane == 0) {
-            uint32_t it = 0;
+    if (warp == 0 || warp == 6) {
+        if (lane == 0) {                                                 // one issuing thread per operand, as in gemm_f16_tn
+            const bool weights = warp == 0;
+            uint32_t s = 0, ph = 0;
             for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs) {
                 const int n0 = (int)((tile / tiles_m) * 2 * BM + rank * BM), m0 = (int)((tile % tiles_m) * bn + rank * half);
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, ph ^= (++s == stages), s = s == stages ? 0 : s) {
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
                     uint8_t* a = smem + (size_t)s * stage_bytes;
-                    if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
                     const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
-                    tma_load_2d_pair(a, &tmA, (int)(kb * BK), n0, bar);           // rows or tokens past the end arrive as zeros
-                    tma_load_2d_pair(a + A_BYTES, &tmB, (int)(kb * BK), m0, bar);
+                    const int x = (int)(kb * 2 * BK);                            // rows, tokens or columns past the end arrive as zeros
+                    if (weights) {
+                        if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
+                        tma_load_2d_pair(a, &tmA, x, n0, bar);
+                        tma_load_2d_pair(a + A_BYTES, &tmA, x + BK, n0, bar);
+                    } else {
+                        tma_load_2d_pair(a + 2 * A_BYTES, &tmB, x, m0, bar);
+                        tma_load_2d_pair(a + 2 * A_BYTES + atom_b, &tmB, x + BK, m0, bar);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            uint32_t it = 0, tcount = 0;
+            uint32_t s = 0, ph = 0, tcount = 0;
+            bool ready = false;
             for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs, ++tcount) {
                 const uint32_t buf = tcount & 1u;
                 if (!mbar_wait(&tempty[buf], ((tcount >> 1) & 1u) ^ 1u)) { dead = true; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
-                    if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!ready && !mbar_wait(&full[s], ph)) { dead = true; break; }
                     tc_fence_after();
-                    const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_f16_pair(d_tmem, umma_desc(a + k * UMMA_K * 2), umma_desc(a + A_BYTES + k * UMMA_K * 2), idesc,
-                                      (kb | (uint32_t)k) ? 1u : 0u);
+                    const uint32_t a = smem_u32(smem) + s * stage_bytes;
+                    uint32_t s1 = s + 1, ph1 = ph;
+                    if (s1 == stages) { s1 = 0; ph1 ^= 1u; }
+                    ready = umma_kblock2_pair(d_tmem, a, a + 2 * A_BYTES, A_BYTES, atom_b, idesc, kb ? 1u : 0u, &full[s1], ph1);
                     umma_commit_pair(&empty[s]);
+                    s = s1; ph = ph1;
                 }
                 if (dead) break;
                 umma_commit_pair(&tfull[buf]);
@@ -865,7 +947,7 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
         const unsigned tiles2 = ((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
         const unsigned pairs = sms / 2 < tiles2 ? sms / 2 : tiles2;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
         cudaLaunchAttribute at[2];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
@@ -905,7 +987,7 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     unsigned grid = (unsigned)device_sm_count();
     if (grid > tiles) grid = tiles;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;

@@ -81,8 +81,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// One probe that never suspends the thread: a third of try_wait's latency when the phase is already complete.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: false when the time limit ran out (the caller records it and leaves).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
+    if (mbar_test(bar, parity)) return true;
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
@@ -426,11 +437,12 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     if (csize > 1) cluster_arrive();                        // this CTA is done with its peers' shared memory
     const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - myc * L::STEP_W);
     const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
+    bool landed = false;                                    // the probe of this item's stage, made while the previous item was summed
     for (uint32_t t = 0; t < items; ++t) {
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = 0.f;
-        if (!mbar_wait(&mybar[slot], phase)) { dead = true; break; }
+        if (!landed && !mbar_wait(&mybar[slot], phase)) { dead = true; break; }
         const uint8_t* st = mystage + (size_t)slot * R * ROWCAP;
         const uint32_t rows = min((uint32_t)R, cta_hi - row0);
         if (L::LANE_UNITS == 2 ? valid > 0 : true) {
@@ -445,6 +457,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         __syncwarp();                                       // every lane is done with this stage
         if (issued < items) issue(slot);
         if (++slot == S) { slot = 0; phase ^= 1u; }
+        landed = t + 1 < items && mbar_test(&mybar[slot], phase);
         // Sum over lanes. The butterfly order (xor 16, 8, 4, 2, 1) is the same for every R, so a
         // row's bits do not depend on how rows were grouped; with R > 1 the first stages also
         // fold the R rows onto disjoint lanes to save shuffles.

@@ -734,8 +734,30 @@ __global__ void f32_to_f16_rows(const float* __restrict__ src, __half* __restric
     o[1] = __floats2half2_rn(v.z, v.w);
 }
 
+// Items per thread of the pre-pass kernels: a block covers 256 x kPrepItems consecutive items, each thread taking
+// every 256th, all loads requested before the first is used (with one item per thread the launches were 9632 and
+// 36000 short blocks that spent more time being scheduled than working).
+constexpr int kPrepItems = 4;
+
+__device__ __forceinline__ void round_activations(const float* __restrict__ A, __half* __restrict__ Ah, size_t n4, size_t first) {
+    float4 v[kPrepItems];
+#pragma unroll
+    for (int j = 0; j < kPrepItems; ++j) {
+        const size_t i = first + (size_t)j * 256;
+        if (i < n4) v[j] = __ldg(reinterpret_cast<const float4*>(A) + i);
+    }
+#pragma unroll
+    for (int j = 0; j < kPrepItems; ++j) {
+        const size_t i = first + (size_t)j * 256;
+        if (i < n4) {
+            const __half2 lo = __floats2half2_rn(v[j].x, v[j].y), hi = __floats2half2_rn(v[j].z, v[j].w);
+            reinterpret_cast<uint2*>(Ah)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+    }
+}
+
 // Both operand conversions of the Q4_0 pre-pass form in one launch. Blocks [0, blocks_w) turn weights into fp16:
-// one thread per 32-bit word of codes = eight consecutive weights = one 16-byte store, consecutive threads consecutive
+// one item per 32-bit word of codes = eight consecutive weights = one 16-byte store, consecutive threads consecutive
 // words, with the same two-instruction-per-pair arithmetic as the producer warps of gemm_q4_tn (the exact (n - 8) * d
 // rounded once to fp16). The remaining blocks round the activations.
 __global__ void __launch_bounds__(256) prepass_q4_f16(const uint8_t* __restrict__ W, uint32_t row_bytes, __half* __restrict__ Wh,
@@ -744,29 +766,37 @@ __global__ void __launch_bounds__(256) prepass_q4_f16(const uint8_t* __restrict_
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");        // the GEMM may set itself up meanwhile
     if (blockIdx.x < blocks_w) {
         const uint32_t wpr = K / 8;                                         // words per row
-        const uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x;
-        if (idx >= (uint64_t)N * wpr) return;
-        const uint32_t row = (uint32_t)(idx / wpr), j = (uint32_t)(idx % wpr), b = j >> 2, i = j & 3u;
-        const unsigned short* p = reinterpret_cast<const unsigned short*>(W + (size_t)row * row_bytes + (size_t)b * 18u);
-        const uint32_t dbits = __ldg(p), q = (uint32_t)__ldg(p + 1 + 2 * i) | ((uint32_t)__ldg(p + 2 + 2 * i) << 16);
-        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
-        const uint32_t lo = q & 0x0F0F0F0Fu, hi = (q >> 4) & 0x0F0F0F0Fu;
-        const uint32_t p01 = __byte_perm(lo, hi, 0x5140), p23 = __byte_perm(lo, hi, 0x7362);
-        uint4 o;
-        q4_quad(p01, d2, o.x, o.y);
-        q4_quad(p23, d2, o.z, o.w);
-        reinterpret_cast<uint4*>(Wh + (size_t)row * K)[j] = o;
+        const uint64_t total = (uint64_t)N * wpr, first = (uint64_t)blockIdx.x * (256 * kPrepItems) + threadIdx.x;
+        uint32_t dbits[kPrepItems], q[kPrepItems];
+#pragma unroll
+        for (int j = 0; j < kPrepItems; ++j) {
+            const uint64_t idx = first + (uint64_t)j * 256;
+            if (idx < total) {
+                const uint32_t row = (uint32_t)(idx / wpr), w = (uint32_t)(idx % wpr), blk = w >> 2, i = w & 3u;
+                const unsigned short* p = reinterpret_cast<const unsigned short*>(W + (size_t)row * row_bytes + (size_t)blk * 18u);
+                dbits[j] = __ldg(p);
+                q[j] = (uint32_t)__ldg(p + 1 + 2 * i) | ((uint32_t)__ldg(p + 2 + 2 * i) << 16);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kPrepItems; ++j) {
+            const uint64_t idx = first + (uint64_t)j * 256;
+            if (idx < total) {
+                const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits[j]));
+                const uint32_t lo = q[j] & 0x0F0F0F0Fu, hi = (q[j] >> 4) & 0x0F0F0F0Fu;
+                const uint32_t p01 = __byte_perm(lo, hi, 0x5140), p23 = __byte_perm(lo, hi, 0x7362);
+                uint4 o;
+                q4_quad(p01, d2, o.x, o.y);
+                q4_quad(p23, d2, o.z, o.w);
+                reinterpret_cast<uint4*>(Wh)[idx] = o;                      // rows are K / 8 sixteen-byte words long: word idx of the whole matrix
+            }
+        }
     } else {
-        const size_t i = (size_t)(blockIdx.x - blocks_w) * 256 + threadIdx.x;
-        if (i >= n4) return;
-        const float4 v = reinterpret_cast<const float4*>(A)[i];
-        __half2* o = reinterpret_cast<__half2*>(Ah) + 2 * i;
-        o[0] = __floats2half2_rn(v.x, v.y);
-        o[1] = __floats2half2_rn(v.z, v.w);
+        round_activations(A, Ah, n4, (size_t)(blockIdx.x - blocks_w) * (256 * kPrepItems) + threadIdx.x);
     }
 }
 
-// The same for Q6_K: one thread per eight consecutive weights (they share the super-block scale, the sub-block scale,
+// The same for Q6_K: one item per eight consecutive weights (they share the super-block scale, the sub-block scale,
 // the nibble half and the high-bit pair position), d * sc and then * (q - 32) in fp32 (both products are exact, as in
 // tmq::dequantize_row_q6_k, tensormark/quant.h:338-365), rounded once to fp16, one 16-byte store.
 __global__ void __launch_bounds__(256) prepass_q6k_f16(const uint8_t* __restrict__ W, uint32_t row_bytes, __half* __restrict__ Wh,
@@ -775,39 +805,52 @@ __global__ void __launch_bounds__(256) prepass_q6k_f16(const uint8_t* __restrict
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (blockIdx.x < blocks_w) {
         const uint32_t gpr = K / 8;                                         // groups of eight per row
-        const uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x;
-        if (idx >= (uint64_t)N * gpr) return;
-        const uint32_t row = (uint32_t)(idx / gpr), t = (uint32_t)(idx % gpr), k = t * 8;
-        const uint32_t e = k & 255u, h = e >> 7, j = (e >> 5) & 3u, l0 = e & 31u;
-        const uint8_t* b = W + (size_t)row * row_bytes + (size_t)(k >> 8) * 210u;
-        const unsigned short* ql = reinterpret_cast<const unsigned short*>(b + 64 * h + 32 * (j & 1u) + l0);
-        const unsigned short* qh = reinterpret_cast<const unsigned short*>(b + 128 + 32 * h + l0);
-        const uint32_t dbits = __ldg(reinterpret_cast<const unsigned short*>(b + 208));
-        const int sc = (int)(int8_t)__ldg(b + 192 + 8 * h + 2 * j + (l0 >> 4));
-        const float ds = __fmul_rn(__half2float(__ushort_as_half((unsigned short)dbits)), __int2float_rn(sc));
-        uint32_t o[4];
+        const uint64_t total = (uint64_t)N * gpr, first = (uint64_t)blockIdx.x * (256 * kPrepItems) + threadIdx.x;
+        uint32_t qlw[kPrepItems][2], qhw[kPrepItems][2], jj[kPrepItems];
+        float ds[kPrepItems];
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-            const uint32_t qlw = (uint32_t)__ldg(ql + 2 * w) | ((uint32_t)__ldg(ql + 2 * w + 1) << 16);
-            const uint32_t qhw = (uint32_t)__ldg(qh + 2 * w) | ((uint32_t)__ldg(qh + 2 * w + 1) << 16);
-            const uint32_t nib = ((j & 2u) ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
-            const uint32_t code = nib | (((qhw >> (2 * j)) & 0x03030303u) << 4);          // four codes 0..63
-            const float w0 = __fmul_rn(ds, __int2float_rn((int)(code & 255u) - 32));
-            const float w1 = __fmul_rn(ds, __int2float_rn((int)((code >> 8) & 255u) - 32));
-            const float w2 = __fmul_rn(ds, __int2float_rn((int)((code >> 16) & 255u) - 32));
-            const float w3 = __fmul_rn(ds, __int2float_rn((int)(code >> 24) - 32));
-            const __half2 a = __floats2half2_rn(w0, w1), c = __floats2half2_rn(w2, w3);
-            o[2 * w] = *reinterpret_cast<const uint32_t*>(&a);
-            o[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&c);
+        for (int it = 0; it < kPrepItems; ++it) {
+            const uint64_t idx = first + (uint64_t)it * 256;
+            if (idx < total) {
+                const uint32_t row = (uint32_t)(idx / gpr), t = (uint32_t)(idx % gpr), k = t * 8;
+                const uint32_t e = k & 255u, h = e >> 7, j = (e >> 5) & 3u, l0 = e & 31u;
+                const uint8_t* b = W + (size_t)row * row_bytes + (size_t)(k >> 8) * 210u;
+                const unsigned short* ql = reinterpret_cast<const unsigned short*>(b + 64 * h + 32 * (j & 1u) + l0);
+                const unsigned short* qh = reinterpret_cast<const unsigned short*>(b + 128 + 32 * h + l0);
+                const uint32_t dbits = __ldg(reinterpret_cast<const unsigned short*>(b + 208));
+                const int sc = (int)(int8_t)__ldg(b + 192 + 8 * h + 2 * j + (l0 >> 4));
+                ds[it] = __fmul_rn(__half2float(__ushort_as_half((unsigned short)dbits)), __int2float_rn(sc));
+                jj[it] = j;
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    qlw[it][w] = (uint32_t)__ldg(ql + 2 * w) | ((uint32_t)__ldg(ql + 2 * w + 1) << 16);
+                    qhw[it][w] = (uint32_t)__ldg(qh + 2 * w) | ((uint32_t)__ldg(qh + 2 * w + 1) << 16);
+                }
+            }
         }
-        reinterpret_cast<uint4*>(Wh + (size_t)row * K)[t] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int it = 0; it < kPrepItems; ++it) {
+            const uint64_t idx = first + (uint64_t)it * 256;
+            if (idx < total) {
+                const uint32_t j = jj[it];
+                uint32_t o[4];
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const uint32_t nib = ((j & 2u) ? (qlw[it][w] >> 4) : qlw[it][w]) & 0x0F0F0F0Fu;
+                    const uint32_t code = nib | (((qhw[it][w] >> (2 * j)) & 0x03030303u) << 4);          // four codes 0..63
+                    const float w0 = __fmul_rn(ds[it], __int2float_rn((int)(code & 255u) - 32));
+                    const float w1 = __fmul_rn(ds[it], __int2float_rn((int)((code >> 8) & 255u) - 32));
+                    const float w2 = __fmul_rn(ds[it], __int2float_rn((int)((code >> 16) & 255u) - 32));
+                    const float w3 = __fmul_rn(ds[it], __int2float_rn((int)(code >> 24) - 32));
+                    const __half2 a = __floats2half2_rn(w0, w1), c = __floats2half2_rn(w2, w3);
+                    o[2 * w] = *reinterpret_cast<const uint32_t*>(&a);
+                    o[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&c);
+                }
+                reinterpret_cast<uint4*>(Wh)[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
     } else {
-        const size_t i = (size_t)(blockIdx.x - blocks_w) * 256 + threadIdx.x;
-        if (i >= n4) return;
-        const float4 v = reinterpret_cast<const float4*>(A)[i];
-        __half2* o = reinterpret_cast<__half2*>(Ah) + 2 * i;
-        o[0] = __floats2half2_rn(v.x, v.y);
-        o[1] = __floats2half2_rn(v.z, v.w);
+        round_activations(A, Ah, n4, (size_t)(blockIdx.x - blocks_w) * (256 * kPrepItems) + threadIdx.x);
     }
 }
 
@@ -912,12 +955,14 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
     const bool fused = allow_fused && dtype == DT_Q4_0 && K % 256 == 0 && (uintptr_t)W % 16 == 0 && row_bytes % 16 == 0;
     const size_t n4 = (size_t)M * K / 4;
     if (!fused && dtype == DT_Q4_0 && K % 8 == 0 && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
-        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + 255) / 256), blocks_a = (unsigned)((n4 + 255) / 256);
+        const unsigned per = 256 * kPrepItems;
+        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + per - 1) / per), blocks_a = (unsigned)((n4 + per - 1) / per);
         prepass_q4_f16<<<blocks_w + blocks_a, 256, 0, st>>>(W, row_bytes, Wh, N, K, A, Ah, n4, blocks_w);
         note_launch();
         if (!check_launch("prepass_q4_f16")) return false;
     } else if (dtype == DT_Q6_K && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
-        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + 255) / 256), blocks_a = (unsigned)((n4 + 255) / 256);
+        const unsigned per = 256 * kPrepItems;
+        const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + per - 1) / per), blocks_a = (unsigned)((n4 + per - 1) / per);
         prepass_q6k_f16<<<blocks_w + blocks_a, 256, 0, st>>>(W, row_bytes, Wh, N, K, A, Ah, n4, blocks_w);
         note_launch();
         if (!check_launch("prepass_q6k_f16")) return false;

@@ -17,6 +17,7 @@ second: sum over the sweep of (block payload + 4*in + 4*out) divided by device t
              from pinned host memory and y goes back to the host inside the timed
              region, one blocking call per GEMV. Weights are cached on the device on
              first use, which is the contract of the entry point being replaced.
+             At N > 1 every rank does this on its own GPU; the slowest rank's time counts.
   roofline   the GEMV kernel against the measured HBM copy bandwidth.
   cpu_baseline  the CPU restatement of the reference's dot path on the host cores.
 
@@ -31,6 +32,7 @@ outputs all-gathered with NCCL; total work is then fixed ("strong" scaling).
 from __future__ import annotations
 
 import argparse
+import datetime
 import ctypes as C
 import json
 import os
@@ -350,7 +352,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     L = lib.load()
     lib.check(L.tm_cuda_init(local_rank), "tm_cuda_init")
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a collective that one rank never joins ends the run after five minutes, not after NCCL's default of ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
 
     def vp(t):
         return C.c_void_p(t.data_ptr())
@@ -494,6 +497,39 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if not status_ok:
         raise RuntimeError("device status: " + lib.last_error())
 
+    # ---- e2e: host-pointer C ABI, pinned x, y back to the host
+    hx = {k: torch.from_numpy(synth.make_activations(k, 1)).pin_memory() for k in {m["k"] for m in mats}}
+    hy = {m["n"]: torch.empty(m["n"], dtype=torch.float32).pin_memory() for m in mats}
+    hW = [np.ascontiguousarray(m["host"][0]) for m in mats]
+
+    def e2e_step():
+        for m, W in zip(mats, hW):
+            ok = L.tm_cuda_gemv_q(C.c_void_p(hx[m["k"]].data_ptr()), C.c_void_p(W.ctypes.data),
+                                  C.c_void_p(hy[m["n"]].data_ptr()), m["n"], m["k"], m["dt"])
+            lib.check(ok, "tm_cuda_gemv_q")
+
+    # Every rank drives its own GPU through the host-pointer entry (independent replicas, as in the device-resident
+    # sweep); the time is the slowest rank's wall clock between two barriers.
+    for _ in range(max(3, args.warmup)):
+        e2e_step()
+    barrier()
+    lb = L.tm_cuda_launch_count()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    es = time.perf_counter() - t0
+    e2e_launches = int(L.tm_cuda_launch_count() - lb)
+    if world > 1:
+        t = torch.tensor([es], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        es = float(t.item())
+    e2e = {"value": world * total * args.steps / es / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": world * sum(4 * m["k"] for m in mats), "d2h_bytes_per_step": world * sum(4 * m["n"] for m in mats),
+           "ms_per_step": es / args.steps * 1e3, "gpu_launches": e2e_launches * world,
+           "note": "blocking tm_cuda_gemv_q per GEMV on every rank's own GPU; weights cached on the device by (pointer, bytes) "
+                   "as the replaced entry does; slowest rank's wall clock"}
+    L.tm_cuda_release_weights()
+
     line = None
     if rank == 0:
         # ---- per-shape device numbers (each GEMV alone, rotating its copies; N=1 only)
@@ -523,36 +559,6 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                       "note": "24 launches per CUDA graph over 3 weight copies; a matrix whose 3 copies fit the "
                                               "126 MB L2 is served from L2, not HBM"})
                     del g
-
-        # ---- e2e: host-pointer C ABI, pinned x, y back to the host
-        hx = {k: torch.from_numpy(synth.make_activations(k, 1)).pin_memory() for k in {m["k"] for m in mats}}
-        hy = {m["n"]: torch.empty(m["n"], dtype=torch.float32).pin_memory() for m in mats}
-        hW = [np.ascontiguousarray(m["host"][0]) for m in mats]
-
-        def e2e_step():
-            for m, W in zip(mats, hW):
-                ok = L.tm_cuda_gemv_q(C.c_void_p(hx[m["k"]].data_ptr()), C.c_void_p(W.ctypes.data),
-                                      C.c_void_p(hy[m["n"]].data_ptr()), m["n"], m["k"], m["dt"])
-                lib.check(ok, "tm_cuda_gemv_q")
-
-        e2e = None
-        if world == 1:
-            for _ in range(max(3, args.warmup)):
-                e2e_step()
-            lb = L.tm_cuda_launch_count()
-            t0 = time.perf_counter()
-            for _ in range(args.steps):
-                e2e_step()
-            es = time.perf_counter() - t0
-            e2e_launches = int(L.tm_cuda_launch_count() - lb)
-            e2e = {"value": total * args.steps / es / 1e9, "unit": "GB/s",
-                   "h2d_bytes_per_step": sum(4 * m["k"] for m in mats), "d2h_bytes_per_step": sum(4 * m["n"] for m in mats),
-                   "ms_per_step": es / args.steps * 1e3, "gpu_launches": e2e_launches,
-                   "note": "blocking tm_cuda_gemv_q per GEMV; weights cached on the device by (pointer, bytes) as the replaced entry does"}
-            L.tm_cuda_release_weights()
-        else:
-            e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                   "note": "the host-pointer entry is single-GPU; measured at N=1 only"}
 
         # ---- CPU baseline (bounded sample, N=1 only)
         cpu = None

@@ -291,6 +291,9 @@ bool tm_cuda_peer_open(int rank, int world, const void* handles);
 /* Rehearsal on ONE GPU (tests): every peer arena is this GPU's own arena, so pushes land locally and the other
  * ranks' counters never advance; a kernel that waits for them runs into the wait limit. */
 bool tm_cuda_peer_open_loopback(int rank, int world);
+/* Rehearsals: advance rank `rank`'s counter of `site` in this rank's arena by `count` (stream-ordered), as that
+ * rank's pushes would. */
+bool tm_cuda_peer_bump(int site, int rank, unsigned count);
 int tm_cuda_peer_world(void);
 int tm_cuda_peer_rank(void);
 bool tm_cuda_peer_unmap(void);                                   /* then a barrier between the ranks, then: */
@@ -304,6 +307,13 @@ void tm_cuda_tok_gemv_xchg(int xslot, size_t xoff, int x_op, int x2slot, size_t 
                            const uint64_t* seg_woff, const unsigned* seg_rows, unsigned nseg, int accumulate,
                            int wait_site, int push_site, int stateslot);
 void tm_cuda_tok_argmax_xchg(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site);
+/* The choice of a row-sharded LM head WITHOUT gathering the logits: this rank reduces rows [lo, lo + n_local) of the
+ * n_total-entry vector in xslot (greedy when inv_temp <= 0, else Gumbel-max with the unsharded choice's noise per
+ * global row), stores its (value, index) key into entry `rank` of the key table in keyslot (a shared slot of
+ * 8 x world bytes) here and on every peer, signals `site` once, waits for the other ranks' keys and writes the
+ * winner (largest value, lowest index on ties: the unsharded rule) to tokslot. Every rank chooses the same token. */
+void tm_cuda_tok_choose_shard(int xslot, unsigned lo, unsigned n_local, unsigned n_total, int tokslot, unsigned max_tokens,
+                              float inv_temp, unsigned seed, int stateslot, int keyslot, int site);
 
 /* Device address of a slot (NULL when unreserved); for resident callers and tests. */
 void* tm_cuda_tok_slot_ptr(int slot);

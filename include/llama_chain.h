@@ -28,6 +28,7 @@
 #include "quant.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -71,7 +72,7 @@ public:
     enum {
         SLOT_X = 0, SLOT_H = 1, SLOT_QKV = 2, SLOT_AO = 3, SLOT_H2 = 4, SLOT_H2S = 5, SLOT_GU = 6, SLOT_DN = 7,
         SLOT_XF = 8, SLOT_LOGITS = 9, SLOT_PROBS = 10, SLOT_TOK = 11, SLOT_BIAS = 12, SLOT_STATE = 13, SLOT_ACT = 14,
-        SLOT_KC = 100, SLOT_VC = 200
+        SLOT_KEYS = 15, SLOT_KC = 100, SLOT_VC = 200
     };
 
     explicit CudaLlama(const CudaLlamaDesc& d) : d_(d), layers_(d.layers, d.layers + d.L) {
@@ -140,7 +141,7 @@ public:
         if (probs_bytes < want) probs_bytes = want;
         if (d_.world > 1 && d_.peer_gather &&
             !(tm_cuda_tok_reserve_shared(SLOT_X, D4) && tm_cuda_tok_reserve_shared(SLOT_GU, (size_t)2 * d_.F * 4) &&
-              tm_cuda_tok_reserve_shared(SLOT_LOGITS, (size_t)d_.V * 4)))
+              tm_cuda_tok_reserve_shared(SLOT_LOGITS, (size_t)d_.V * 4) && tm_cuda_tok_reserve_shared(SLOT_KEYS, 8 * (size_t)d_.world)))
             throw std::runtime_error(std::string("cuda: shared slot reservation failed: ") + tm_cuda_last_error());
         bool ok = tm_cuda_tok_reserve(SLOT_X, D4) && tm_cuda_tok_reserve(SLOT_H, D4) && tm_cuda_tok_reserve(SLOT_H2, D4) &&
                   tm_cuda_tok_reserve(SLOT_H2S, D4) && tm_cuda_tok_reserve(SLOT_DN, D4) && tm_cuda_tok_reserve(SLOT_XF, D4) &&
@@ -309,11 +310,27 @@ public:
                                   2 * l, 2 * l + 1, SLOT_STATE);
         }
         const size_t hd_yoff[1] = {rk * Vs * 4};
-        tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, hd_yoff, Vs, Dn, d_.dt_head, &head_.woff, &Vs, 1, 0,
-                              2 * d_.L - 1, 2 * d_.L, SLOT_STATE);
-        if (inv_temp_ > 0.f) tm_cuda_tok_sample_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, inv_temp_, seed_, SLOT_STATE, 2 * d_.L);
-        else tm_cuda_tok_argmax_xchg(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE, 2 * d_.L);
+        if (gather_logits_) {
+            tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, hd_yoff, Vs, Dn, d_.dt_head, &head_.woff, &Vs, 1, 0,
+                                  2 * d_.L - 1, 2 * d_.L, SLOT_STATE);
+            if (inv_temp_ > 0.f) tm_cuda_tok_sample_at(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, inv_temp_, seed_, SLOT_STATE, 2 * d_.L);
+            else tm_cuda_tok_argmax_xchg(SLOT_LOGITS, SLOT_TOK, Vn, max_tokens, SLOT_STATE, 2 * d_.L);
+        } else {
+            // The logits stay where they are computed: every rank chooses over its own rows and only the g (value, index)
+            // keys are exchanged (tie rule of the unsharded choice, tensormark/metal.h:2335: the lowest index wins).
+            tm_cuda_tok_gemv_xchg(SLOT_X, 0, 1, 0, 0, d_.rmsf, d_.eps, head_.id, SLOT_LOGITS, hd_yoff, Vs, Dn, d_.dt_head, &head_.woff, &Vs, 1, 0,
+                                  2 * d_.L - 1, -1, SLOT_STATE);
+            tm_cuda_tok_choose_shard(SLOT_LOGITS, (unsigned)(rk * Vs), Vs, Vn, SLOT_TOK, max_tokens, inv_temp_ > 0.f ? inv_temp_ : 0.f, seed_, SLOT_STATE,
+                                     SLOT_KEYS, 2 * d_.L);
+        }
         tm_cuda_tok_advance(SLOT_STATE);
+    }
+
+    // Rows of the logits vector that the graph chain leaves valid on this rank: all of them, except for a row-sharded
+    // model whose ranks exchange only their choices (then this rank's rows of the head).
+    void chain_logit_rows(int& lo, int& hi) const {
+        lo = 0; hi = d_.V;
+        if (d_.world > 1 && d_.peer_gather && !gather_logits_) { lo = d_.rank * (d_.V / d_.world); hi = lo + d_.V / d_.world; }
     }
 
     // One forward at position `seen`: logits of that token (tensormark/llama.h:5931-5980).
@@ -521,6 +538,10 @@ private:
     std::vector<tm_llama_gpu_layer> stack_layers_;
     std::vector<std::vector<float>> host_kc_, host_vc_;
     float inv_temp_ = 0.f, sg_inv_temp_ = 0.f;                 // > 0 only while a sampled chain is being encoded
+    // Peer-gather chain: true = the LM head's rows are gathered on every rank before the choice (every rank then holds
+    // all logits of the last step), false = only the ranks' (value, index) keys travel. TM_CUDA_GATHER_LOGITS=1 selects
+    // the former for callers that read the chain's logits.
+    bool gather_logits_ = [] { const char* e = std::getenv("TM_CUDA_GATHER_LOGITS"); return e && *e == '1'; }();
     unsigned seed_ = 0, sg_seed_ = 0;
 };
 

@@ -34,6 +34,8 @@ def load() -> C.CDLL:
                                  C.POINTER(C.c_ulonglong)]
         L.tmchain_chain_end.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         L.tmchain_logits.argtypes = [C.c_void_p, C.c_void_p]
+        L.tmchain_logit_rows.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.tmchain_logit_rows.restype = None
         L.tmchain_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.tmchain_prefill_prepare.argtypes = [C.c_void_p]
         L.tmchain_prefill_gpu_ms.argtypes = [C.c_void_p]
@@ -186,6 +188,13 @@ class Chain:
         out = np.empty(self.cfg["V"], np.float32)
         self.L.tmchain_logits(self.h, out.ctypes.data)
         return out
+
+    def logit_rows(self) -> tuple[int, int]:
+        """Rows of logits() that a finished chain left valid on this rank: all of them, or this rank's rows of the head
+        when the ranks of a row-sharded model exchange only their choices."""
+        lo, hi = C.c_int(0), C.c_int(0)
+        self.L.tmchain_logit_rows(self.h, C.byref(lo), C.byref(hi))
+        return lo.value, hi.value
 
     def close(self):
         if self.h:

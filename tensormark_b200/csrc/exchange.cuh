@@ -35,24 +35,28 @@ __device__ __forceinline__ bool wait_counter(const unsigned* ctr, unsigned want,
 // Consumer side of the exchange: one thread waits for every other rank's counter, the CTA follows. The first
 // wait that runs out writes status 2 and raises the abort word here and on every peer; while it is up no wait
 // is attempted at all (the data read afterwards is incomplete, which the status word tells the host).
-__device__ __forceinline__ void exchange_wait(const Exchange& xc, int* status) {
-    if (!xc.nwait) return;
-    if (threadIdx.x == 0) {
-        bool ok = !(xc.abort_local && peek_word(xc.abort_local));
-        if (ok) {
-            const unsigned want = (unsigned)(*(volatile const int*)xc.epoch + 1) * xc.wait_ctas;
-            for (uint32_t q = 0; q < xc.nwait && ok; ++q)
-                if (q != xc.self) ok = wait_counter(xc.wait_ctrs + q, want, xc.limit_ns, xc.abort_local);
-        }
-        if (!ok) {
-            *(volatile int*)status = 2;
-            if (xc.abort_local) {
-                *(volatile int*)xc.abort_local = 1;
-                for (uint32_t q = 0; q < xc.npeers; ++q) *(volatile int*)xc.abort_peer[q] = 1;
-                __threadfence_system();
-            }
+// The wait itself, for ONE thread; false when it gave up (status and abort words are then set).
+__device__ __forceinline__ bool exchange_wait_thread(const Exchange& xc, int* status) {
+    if (!xc.nwait) return true;
+    bool ok = !(xc.abort_local && peek_word(xc.abort_local));
+    if (ok) {
+        const unsigned want = (unsigned)(*(volatile const int*)xc.epoch + 1) * xc.wait_ctas;
+        for (uint32_t q = 0; q < xc.nwait && ok; ++q)
+            if (q != xc.self) ok = wait_counter(xc.wait_ctrs + q, want, xc.limit_ns, xc.abort_local);
+    }
+    if (!ok) {
+        *(volatile int*)status = 2;
+        if (xc.abort_local) {
+            *(volatile int*)xc.abort_local = 1;
+            for (uint32_t q = 0; q < xc.npeers; ++q) *(volatile int*)xc.abort_peer[q] = 1;
+            __threadfence_system();
         }
     }
+    return ok;
+}
+__device__ __forceinline__ void exchange_wait(const Exchange& xc, int* status) {
+    if (!xc.nwait) return;
+    if (threadIdx.x == 0) (void)exchange_wait_thread(xc, status);
     __syncthreads();
 }
 // Producer side, end of a CTA: every row this CTA computed has been stored here and on the peers by the

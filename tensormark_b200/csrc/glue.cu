@@ -210,6 +210,74 @@ __global__ void __launch_bounds__(256) choose_kernel(const float* x, uint32_t* o
     }
 }
 
+// The same choice for a row-sharded LM head without gathering the logits: every rank reduces ITS rows [lo, lo + n) of
+// x to one key (global row index inside, so the Gumbel noise and the tie rule are those of the unsharded choice), the
+// CTA that finishes last stores the key into slot `self` of a small key table here and on every peer, counts itself
+// on the site, waits (bounded) for the other ranks' counts and takes the largest of the g keys: g x 8 bytes cross
+// NVLink per token instead of the whole vocabulary's logits. A forced (prompt) entry still publishes and counts, so
+// that the site's counters keep step with the token epoch, and only leaves the token alone.
+template <bool SAMPLE>
+__global__ void __launch_bounds__(256) choose_shard_kernel(const float* x, uint32_t* out, uint32_t lo, uint32_t n,
+                                                            uint32_t idx, float inv_temp, uint32_t seed,
+                                                            unsigned long long* scratch /* [0]=key, [1]=done */,
+                                                            const int* st, unsigned long long* keys, const Exchange xc, int* status) {
+    pdl_enter();
+    __shared__ unsigned long long best_s[8];
+    bool forced = false;
+    if (st) {
+        idx = (uint32_t)st[1] + 1u;
+        forced = idx < (uint32_t)st[2];
+    }
+    unsigned long long best = pack_key(-CUDART_INF_F, 0);
+    const uint32_t base = hash32(seed * 0x9e3779b9u + idx * 0x85ebca6bu + 0x1234567u);
+    for (uint32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < n; j += gridDim.x * blockDim.x) {
+        const uint32_t i = lo + j;
+        float v = __ldcg(x + i);
+        if (SAMPLE && inv_temp > 0.f) {
+            const uint32_t h = hash32(base ^ (i * 0x27d4eb2fu + 0x165667b1u));
+            const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+            v = v * inv_temp - logf(-logf(u));
+        }
+        if (v > -CUDART_INF_F) {
+            const unsigned long long k = pack_key(v, i);
+            best = k > best ? k : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
+        best = t > best ? t : best;
+    }
+    if ((threadIdx.x & 31) == 0) best_s[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = best_s[w] > best ? best_s[w] : best;
+        atomicMax(&scratch[0], best);
+        __threadfence();
+        const unsigned long long done = atomicAdd(&scratch[1], 1ull);
+        if (done == gridDim.x - 1) {
+            unsigned long long k = atomicExch(&scratch[0], 0ull);
+            scratch[1] = 0ull;
+            *(volatile unsigned long long*)(keys + xc.self) = k;
+            for (uint32_t q = 0; q < xc.npush; ++q) *(volatile unsigned long long*)(reinterpret_cast<unsigned long long*>(xc.peer_y[q]) + xc.self) = k;
+            __threadfence_system();                             // the keys before the counts
+            for (uint32_t q = 0; q < xc.npush; ++q)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(xc.peer_ctr[q]) : "memory");
+            if (exchange_wait_thread(xc, status)) {
+                for (uint32_t r = 0; r < xc.nwait; ++r) {
+                    if (r == xc.self) continue;
+                    const unsigned long long kr = *(volatile const unsigned long long*)(keys + r);
+                    k = kr > k ? kr : k;
+                }
+            }
+            if (!forced) {
+                out[idx] = 0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull);
+                __threadfence_system();
+            }
+        }
+    }
+}
+
 // ---- GQA split-K decode attention -------------------------------------------------
 // grid (KVH, nsplit), 4 warps. A CTA serves the REP query heads that share one KV
 // head over positions [split*chunk, min(allow, (split+1)*chunk)). Each warp walks
@@ -457,6 +525,20 @@ bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, floa
     else launch_pdl(choose_kernel<false>, dim3(grid), dim3(256), st, x, out, n, idx, 0.f, 0u, scratch, state, xc, device_status_word());
     note_launch();
     return check_launch("argmax");
+}
+
+bool launch_choose_shard(const float* x, unsigned* out, unsigned lo, unsigned n, float inv_temp, unsigned seed, bool sample,
+                         unsigned long long* scratch, unsigned long long* keys, cudaStream_t st, const int* state, const Exchange& xc) {
+    if (!x || !out || !keys || !state || n == 0) return fail("choose_shard: bad arguments");
+    if (!xc.nwait || !xc.wait_ctrs || xc.wait_ctas != 1 || !xc.epoch || xc.npush + 1 != xc.nwait)
+        return fail("choose_shard: incomplete peer exchange description");
+    unsigned grid = cdiv(n, 256 * 4);
+    const unsigned sms = (unsigned)device_sm_count();
+    if (grid > sms) grid = sms;
+    if (sample) launch_pdl(choose_shard_kernel<true>, dim3(grid), dim3(256), st, x, out, lo, n, 0u, inv_temp, seed, scratch, state, keys, xc, device_status_word());
+    else launch_pdl(choose_shard_kernel<false>, dim3(grid), dim3(256), st, x, out, lo, n, 0u, 0.f, 0u, scratch, state, keys, xc, device_status_word());
+    note_launch();
+    return check_launch("choose_shard");
 }
 
 bool launch_qkv_post(float* qkv, void* kc, void* vc, bool half_cache, unsigned H, unsigned KVH, unsigned dh, unsigned ctx,

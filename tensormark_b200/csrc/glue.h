@@ -25,6 +25,8 @@ bool launch_half_to_f32(const void* src, float* dst, size_t n, cudaStream_t st);
 bool launch_embed_row(const unsigned* tok, unsigned idx, const uint8_t* W, float* x, unsigned D, unsigned dtype, cudaStream_t st,
                       const int* state = nullptr);
 // scratch: two zero-initialised 64-bit words owned by the caller, re-armed by the kernel
+bool launch_choose_shard(const float* x, unsigned* out, unsigned lo, unsigned n, float inv_temp, unsigned seed, bool sample,
+                         unsigned long long* scratch, unsigned long long* keys, cudaStream_t st, const int* state, const Exchange& xc);
 bool launch_choose(const float* x, unsigned* out, unsigned n, unsigned idx, float inv_temp, unsigned seed, bool sample,
                    unsigned long long* scratch, cudaStream_t st, const int* state = nullptr, const Exchange* xchg = nullptr);
 

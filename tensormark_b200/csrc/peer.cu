@@ -71,6 +71,19 @@ bool tm_cuda_peer_open_loopback(int rank, int world) {
     return true;
 }
 
+// Rehearsals (tests, tools): advance rank `rank`'s counter of `site` in THIS arena by `count`, in stream order, as
+// that rank's pushes would; with the loopback arena this is how a test plays the part of the other ranks.
+__global__ void peer_bump_kernel(unsigned* ctr, unsigned count) { atomicAdd_system(ctr, count); }
+bool tm_cuda_peer_bump(int site, int rank, unsigned count) {
+    if (!ensure_init(-1)) return false;
+    State& s = state();
+    PeerState& ps = s.peer;
+    if (!ps.open) return fail("peer: the arena is not open");
+    if (site < 0 || site >= kMaxSites || rank < 0 || rank >= ps.world) return fail("peer: site %d / rank %d out of range", site, rank);
+    peer_bump_kernel<<<1, 1, 0, s.stream>>>((unsigned*)ps.arena + (size_t)site * kMaxRanks + rank, count);
+    return check_launch("peer_bump");
+}
+
 int tm_cuda_peer_world(void) { return state().peer.open ? state().peer.world : 1; }
 int tm_cuda_peer_rank(void) { return state().peer.open ? state().peer.rank : 0; }
 

@@ -785,6 +785,29 @@ void tm_cuda_tok_argmax_at(int xslot, int tokslot, unsigned n, unsigned max_toke
 void tm_cuda_tok_argmax_xchg(int xslot, int tokslot, unsigned n, unsigned max_tokens, int stateslot, int wait_site) {
     argmax_at_impl("tok_argmax_xchg", xslot, tokslot, n, max_tokens, stateslot, wait_site);
 }
+void tm_cuda_tok_choose_shard(int xslot, unsigned lo, unsigned n_local, unsigned n_total, int tokslot, unsigned max_tokens,
+                              float inv_temp, unsigned seed, int stateslot, int keyslot, int site) {
+    const char* who = "tok_choose_shard";
+    if (!ensure_init(-1)) return;
+    State& s = state();
+    PeerState& ps = s.peer;
+    if (!ps.open) { latch("%s: the peer arena is not open", who); return; }
+    if (site < 0 || site >= kMaxSites) { latch("%s: exchange site out of range", who); return; }
+    if (n_local == 0 || (uint64_t)lo + n_local > n_total) { latch("%s: rows [%u, %u) are not inside %u", who, lo, lo + n_local, n_total); return; }
+    const float* x = (const float*)slot_ptr(xslot, (size_t)n_total * 4, who);
+    unsigned* t = (unsigned*)slot_ptr(tokslot, sizeof(unsigned) * (size_t)max_tokens, who);
+    const int* st = state_ptr(stateslot, who);
+    unsigned long long* keys = (unsigned long long*)slot_ptr(keyslot, sizeof(unsigned long long) * (size_t)ps.world, who);
+    unsigned long long* sc = choose_scratch();
+    if (!x || !t || !st || !keys || !sc) return;
+    if ((uintptr_t)keys % 8) { latch("%s: the key table must be 8-byte aligned", who); return; }
+    unsigned& ctas = ps.site_ctas[site];
+    if (ctas && ctas != 1) { latch("%s: site %d was pushed to by %u CTAs before; a key exchange counts once per rank", who, site, ctas); return; }
+    ctas = 1;
+    Exchange xc;
+    if (!make_exchange(xc, site, site, stateslot, (const uint8_t*)keys, who)) return;
+    if (!launch_choose_shard(x, t, lo, n_local, inv_temp, seed, inv_temp > 0.f, sc, keys, s.stream, st, xc)) s.sticky = true;
+}
 void tm_cuda_tok_embed_at(int tokslot, int wid, uint64_t woff, int xslot, unsigned D, unsigned dtype, unsigned max_tokens,
                           int stateslot) {
     if (!ensure_init(-1)) return;

@@ -106,6 +106,9 @@ TMCHAIN_API int tmchain_logits(void* p, float* out) {
     std::memcpy(out, l.data(), l.size() * sizeof(float));
     return (int)l.size();
 }
+// Rows [lo, hi) of that vector that a finished graph chain left valid on this rank (all, unless the ranks of a
+// row-sharded model exchanged only their choices).
+TMCHAIN_API void tmchain_logit_rows(void* p, int* lo, int* hi) { static_cast<Holder*>(p)->m->chain_logit_rows(*lo, *hi); }
 // Feed a prompt token by token through the graph lane; returns the model's next token or -1.
 TMCHAIN_API int tmchain_feed(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_feed(toks, n); }

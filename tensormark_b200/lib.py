@@ -24,6 +24,7 @@ SIGNATURES = {
     "tm_cuda_sm_count": (C.c_int, []),
     "tm_cuda_set_wait_limit_ms": (C.c_uint, [C.c_uint]),
     "tm_cuda_peer_open_loopback": (C.c_bool, [C.c_int, C.c_int]),
+    "tm_cuda_peer_bump": (C.c_bool, [C.c_int, C.c_int, _u]),
     "tm_cuda_q4_gemv": (C.c_bool, [_vp, _vp, _vp, _u, _u]),
     "tm_cuda_sgemm_q4": (C.c_bool, [_vp, _vp, _vp, _u, _u, _u]),
     "tm_cuda_q4_prefill": (C.c_bool, [_vp, C.POINTER(_vp), C.POINTER(_u), _u, _vp, _u, _u]),
@@ -120,6 +121,7 @@ SIGNATURES = {
     "tm_cuda_tok_gemv_xchg": (None, [C.c_int, _sz, C.c_int, C.c_int, _sz, _vp, C.c_float, C.c_int, C.c_int, C.POINTER(_sz), _u, _u, _u,
                                      C.POINTER(_u64), C.POINTER(_u), _u, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tm_cuda_tok_argmax_xchg": (None, [C.c_int, C.c_int, _u, _u, C.c_int, C.c_int]),
+    "tm_cuda_tok_choose_shard": (None, [C.c_int, _u, _u, _u, C.c_int, _u, C.c_float, _u, C.c_int, C.c_int, C.c_int]),
     "tm_cuda_trace_read": (C.c_size_t, [_vp, C.c_size_t]),
     "tm_cuda_tok_slot_ptr": (_vp, [C.c_int]),
     "tm_cuda_tok_stream": (_vp, []),

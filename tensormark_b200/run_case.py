@@ -124,19 +124,30 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
     # the last step's logits are compared across the ranks (and, by the caller, with the one-GPU run).
     logits = m.logits()
     logits_diff_ranks = 0.0
+    row_lo, row_hi = m.logit_rows()
+    choice = "all logits gathered on every rank, then the choice"
     if dist is not None and world > 1:
         dev_ms = float(reduce(torch.tensor([dev_ms], dtype=torch.float64), dist.ReduceOp.MAX).item())
         mine = torch.tensor([int(x) for x in toks], dtype=torch.int64)
         same = bool((reduce(mine.clone(), dist.ReduceOp.MIN) == reduce(mine.clone(), dist.ReduceOp.MAX)).all())
-        llo = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MIN)
-        lhi = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MAX)
-        logits_diff_ranks = float((lhi - llo).max())
+        if (row_lo, row_hi) != (0, cfg["V"]):
+            # Only the ranks' (value, index) keys travelled: every rank holds its own rows of the last logits. They are
+            # put together here, after the timed region, so that the whole vector can be compared with the one-GPU run.
+            choice = "each rank chooses over its rows of the head; only the ranks' (value, index) keys are exchanged"
+            whole = torch.zeros(cfg["V"], dtype=torch.float32)
+            whole[row_lo:row_hi] = torch.from_numpy(logits[row_lo:row_hi].copy())
+            logits = reduce(whole, dist.ReduceOp.SUM).numpy()
+        else:
+            llo = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MIN)
+            lhi = reduce(torch.from_numpy(logits.copy()), dist.ReduceOp.MAX)
+            logits_diff_ranks = float((lhi - llo).max())
     tr = summarize_trace(L, 5 * cfg["L"] + 1) if trace and rank == 0 else None
     wbytes = chain_weight_bytes(cfg)
     rec = {"n_gpus": world,
            "sharding": "none" if world == 1 else "FFN and LM-head rows over ranks, " +
            ("rows stored into the peers' buffers by the GEMVs, flags" if gather == "peer" else "NCCL all-gather after each"),
            "tokens_equal_on_all_ranks": same,
+           "lm_head_choice": choice if world > 1 else "one GPU",
            "lane": "CUDA graph per token" if graph else "host call per op",
            "decode_tok_per_s": round(steps / (dev_ms * 1e-3), 1), "ms_per_token": round(dev_ms / steps, 4),
            "wall_tok_per_s": round(steps / wall, 1),

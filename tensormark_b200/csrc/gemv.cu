@@ -278,6 +278,9 @@ __global__ void __launch_bounds__(512) xprep_kernel(uint32_t* out, const float* 
     __shared__ float red[16];
     // The GEMV that follows may become resident and prefetch its weights at once; it waits for this grid itself.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (x_op == 1u)                                        // norm weights: static, and out of L2 since the last token
+        for (uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) * 32u; i < K; i += gridDim.x * blockDim.x * 32u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(x2 + i) : "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     exchange_wait(xc, status);
     if (gridDim.x == 1) { stage_vector<CDT>(out, x, x2, x_op, eps, K, red); return; }
@@ -352,6 +355,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     };
     for (uint32_t s = 0; s < S && issued < items; ++s) issue(s);
 
+    // RMSNorm weights are read once per token, 4 GB of streamed blocks apart: by then they have left L2, and their DRAM
+    // latency (1.1-1.5 us, measured as the difference of the x phase with and without these loads) would sit between
+    // the dependency wait and the first row. They do not depend on the preceding kernel: ask for them now.
+    if (p.x_op == 1u && !p.xq) {
+        for (uint32_t i = threadIdx.x * 32u; i < p.K; i += blockDim.x * 32u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x2 + i) : "memory");
+    }
     // Everything above touches only weights. x may be written by the preceding
     // kernel in the stream: wait for it here, and let the next kernel start its own
     // weight prefetch.

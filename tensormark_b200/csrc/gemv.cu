@@ -362,6 +362,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         for (uint32_t i = threadIdx.x * 32u; i < p.K; i += blockDim.x * 32u)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x2 + i) : "memory");
     }
+    // x itself may still be written by the preceding kernel, but L2 is where its writes land: asking for the lines now
+    // costs nothing when they are there and saves the DRAM round trip after the wait when they are not (an activation
+    // vector that was last touched a few hundred MB of weights ago).
+    if (!p.xq) {
+        for (uint32_t i = threadIdx.x * 32u; i < p.K; i += blockDim.x * 32u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x + i) : "memory");
+    }
     // Everything above touches only weights. x may be written by the preceding
     // kernel in the stream: wait for it here, and let the next kernel start its own
     // weight prefetch.

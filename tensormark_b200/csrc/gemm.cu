@@ -57,7 +57,8 @@ constexpr int kStages = 4;
 constexpr int UMMA_K = 16;
 constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int kThreads = 192;          // the Q4_0 in-kernel form: producer, MMA issuer, four epilogue warps (+ its dequantizing warps)
-constexpr int kThreadsTma = 224;       // the two TMA-fed kernels: one more warp, so that each operand has its own issuing thread
+constexpr int kProducers = 3;          // TMA-issuing warps of the two TMA-fed kernels (warps 0, 6, 7), taking stages in turn
+constexpr int kThreadsTma = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitNs = 2000000000ull;
 constexpr int kMaxStages = 8;
@@ -223,28 +224,25 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // writes the fp16 operands; nothing below may start before that kernel has finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp == 0 || warp == 6) {
-        // One issuing thread per operand, in warps of different SM sub-partitions: a thread's bulk-tensor copies go out
-        // about 230-320 ns apart whatever their size (measured: 4 KB to 32 KB boxes, 2 to 16 in flight, 1 to 148 CTAs),
-        // so one thread issuing both operands of a k-block is slower than the four MMAs that consume them; two threads
-        // issue side by side. Warp 0 announces the stage's bytes and loads the weight rows, warp 6 the token rows
-        // (its bytes may land on the barrier before the announcement: the phase still needs warp 0's arrival).
-        if (lane == 0) {
-            const bool weights = warp == 0;
-            uint32_t s = 0, ph = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
-                const int n0 = (int)(tile / tiles_m) * BM, m0 = (int)((tile % tiles_m) * bn);
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ph ^= (++s == stages), s = s == stages ? 0 : s) {
-                    if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
-                    uint8_t* a = smem + (size_t)s * stage_bytes;
-                    if (weights) {
-                        mbar_expect_tx(&full[s], stage_bytes);
-                        tma_load_2d(a, &tmA, (int)(kb * BK), n0, &full[s]);
-                    } else {
-                        tma_load_2d(a + A_BYTES, &tmB, (int)(kb * BK), m0, &full[s]);
-                    }
-                }
-            }
+    if (warp == 0 || warp >= 6) {
+        // Producers. A warp's bulk-tensor copy instruction takes about 300 ns to issue whatever its size and ~25 ns more
+        // per active lane (measured: one lane x 4..32 KB boxes, 2..16 stages in flight: 300-320 ns per request; 3 lanes
+        // x 16 KB: 358 ns per instruction), so ONE issuing thread per operand fed a stage every ~570 clocks - longer
+        // than the stage's four MMAs run. Here a stage's two boxes go out in ONE instruction (lane 0 the weight rows,
+        // lane 1 the token rows) and kProducers warps take the stages in turn.
+        const uint32_t prod = warp == 0 ? 0u : (uint32_t)warp - 5u;
+        const uint32_t my_tiles = tiles > blockIdx.x ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+        const uint32_t total = my_tiles * num_kb;
+        for (uint32_t it = prod; it < total; it += kProducers) {
+            const uint32_t s = it % stages, ph = (it / stages) & 1u;
+            const uint32_t t = it / num_kb, kb = it - t * num_kb, tile = blockIdx.x + t * gridDim.x;
+            const int n0 = (int)(tile / tiles_m) * BM, m0 = (int)((tile % tiles_m) * bn);
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) { dead = true; break; }
+            uint8_t* a = smem + (size_t)s * stage_bytes;
+            if (lane == 0) mbar_expect_tx(&full[s], stage_bytes);
+            __syncwarp();
+            if (lane < 2)
+                tma_load_2d(lane == 0 ? a : a + A_BYTES, lane == 0 ? &tmA : &tmB, (int)(kb * BK), lane == 0 ? n0 : m0, &full[s]);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -341,17 +339,18 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
 }
-// Two swizzle atoms (128 columns of K) in one go: eight MMAs behind one probe and before one commit. `a` and `b` are
-// the first atoms, the second ones lie a_step / b_step bytes further.
-__device__ __forceinline__ bool umma_kblock2_pair(uint32_t tmem_d, uint32_t a, uint32_t b, uint32_t a_step, uint32_t b_step, uint32_t idesc,
-                                                  uint32_t acc_first, uint64_t* next_bar, uint32_t next_parity) {
-    const uint32_t la = umma_desc_lo(a), lb = umma_desc_lo(b), la1 = la + (a_step >> 4), lb1 = lb + (b_step >> 4);
+// The MMAs of TWO consecutive stages (eight MMAs) behind probes of the two stages after them: per 64 columns of K the
+// issuing thread spends half a probe and four MMA issues. Bit 0 of the result: bar0's phase is complete, bit 1: bar1's.
+__device__ __forceinline__ uint32_t umma_kblock2_pair(uint32_t tmem_d, uint32_t a0, uint32_t b0, uint32_t a1, uint32_t b1, uint32_t idesc,
+                                                      uint32_t acc_first, uint64_t* bar0, uint32_t parity0, uint64_t* bar1, uint32_t parity1) {
+    const uint32_t la = umma_desc_lo(a0), lb = umma_desc_lo(b0), la1 = umma_desc_lo(a1), lb1 = umma_desc_lo(b1);
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p, q, t;\n\t"
+        "{\n\t.reg .pred p0, p1, q, t;\n\t.reg .u32 r0, r1;\n\t"
         "setp.ne.b32 q, %20, 0;\n\t"
         "setp.eq.b32 t, 0, 0;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%21], %22;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p0, [%21], %22;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p1, [%23], %24;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, q;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %4, %5, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %6, %7, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
@@ -360,15 +359,39 @@ __device__ __forceinline__ bool umma_kblock2_pair(uint32_t tmem_d, uint32_t a, u
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %12, %13, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %14, %15, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%1], %16, %17, %18, {%19, %19, %19, %19, %19, %19, %19, %19}, t;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
+        "selp.u32 r0, 1, 0, p0;\n\t"
+        "selp.u32 r1, 2, 0, p1;\n\t"
+        "or.b32 %0, r0, r1;\n\t}"
         : "=r"(ok)
         : "r"(tmem_d), "l"(umma_desc_at(la, 0)), "l"(umma_desc_at(lb, 0)), "l"(umma_desc_at(la, 1)), "l"(umma_desc_at(lb, 1)),
           "l"(umma_desc_at(la, 2)), "l"(umma_desc_at(lb, 2)), "l"(umma_desc_at(la, 3)), "l"(umma_desc_at(lb, 3)),
           "l"(umma_desc_at(la1, 0)), "l"(umma_desc_at(lb1, 0)), "l"(umma_desc_at(la1, 1)), "l"(umma_desc_at(lb1, 1)),
           "l"(umma_desc_at(la1, 2)), "l"(umma_desc_at(lb1, 2)), "l"(umma_desc_at(la1, 3)), "l"(umma_desc_at(lb1, 3)),
+          "r"(idesc), "r"(0), "r"(acc_first), "r"(smem_u32(bar0)), "r"(parity0), "r"(smem_u32(bar1)), "r"(parity1)
+        : "memory");
+    return ok;
+}
+// One stage (a tile's odd last k-block), one probe.
+__device__ __forceinline__ uint32_t umma_kblock_pair(uint32_t tmem_d, uint32_t a, uint32_t b, uint32_t idesc, uint32_t acc_first,
+                                                     uint64_t* next_bar, uint32_t next_parity) {
+    const uint32_t la = umma_desc_lo(a), lb = umma_desc_lo(b);
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q, t;\n\t"
+        "setp.ne.b32 q, %12, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%13], %14;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %10, {%11, %11, %11, %11, %11, %11, %11, %11}, q;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %4, %5, %10, {%11, %11, %11, %11, %11, %11, %11, %11}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %6, %7, %10, {%11, %11, %11, %11, %11, %11, %11, %11}, t;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%1], %8, %9, %10, {%11, %11, %11, %11, %11, %11, %11, %11}, t;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tmem_d), "l"(umma_desc_at(la, 0)), "l"(umma_desc_at(lb, 0)), "l"(umma_desc_at(la, 1)), "l"(umma_desc_at(lb, 1)),
+          "l"(umma_desc_at(la, 2)), "l"(umma_desc_at(lb, 2)), "l"(umma_desc_at(la, 3)), "l"(umma_desc_at(lb, 3)),
           "r"(idesc), "r"(0), "r"(acc_first), "r"(smem_u32(next_bar)), "r"(next_parity)
         : "memory");
-    return ok != 0;
+    return ok;
 }
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {        // arrives on `bar` at this offset in both CTAs
     const uint16_t both = 3;
@@ -394,11 +417,10 @@ gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs and owns full[] and tempty[]
     const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const uint32_t half = bn >> 1;
-    const uint32_t num_kb = (K + 2 * BK - 1) / (2 * BK);         // a stage is TWO swizzle atoms of K: half as many probes and commits per MMA
+    const uint32_t num_kb = (K + BK - 1) / BK;
     const uint32_t tiles_n = (n_rows + 2 * BM - 1) / (2 * BM), tiles_m = (m_tok + bn - 1) / bn, tiles = tiles_n * tiles_m;
     const uint32_t idesc = (1u << 4) | ((bn >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);   // M = 256 over the pair, N = bn
-    const uint32_t atom_b = half * (uint32_t)(BK * 2);                                           // one atom of this CTA's token rows
-    const uint32_t stage_bytes = 2 * (A_BYTES + atom_b);                                         // per CTA; a multiple of 1024
+    const uint32_t stage_bytes = A_BYTES + half * (uint32_t)(BK * 2);                            // per CTA; a multiple of 1024
     const uint32_t stages = min((uint32_t)kMaxStages, kTileRegion / stage_bytes);
 
     if (threadIdx.x == 0) {
@@ -417,46 +439,54 @@ gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool dead = false;
     asm volatile("griddepcontrol.wait;" ::: "memory");           // the pre-pass has written the fp16 operands
 
-    if (warp == 0 || warp == 6) {
-        if (lane == 0) {                                                 // one issuing thread per operand, as in gemm_f16_tn
-            const bool weights = warp == 0;
-            uint32_t s = 0, ph = 0;
-            for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs) {
-                const int n0 = (int)((tile / tiles_m) * 2 * BM + rank * BM), m0 = (int)((tile % tiles_m) * bn + rank * half);
-                for (uint32_t kb = 0; kb < num_kb; ++kb, ph ^= (++s == stages), s = s == stages ? 0 : s) {
-                    if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
-                    uint8_t* a = smem + (size_t)s * stage_bytes;
-                    const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
-                    const int x = (int)(kb * 2 * BK);                            // rows, tokens or columns past the end arrive as zeros
-                    if (weights) {
-                        if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
-                        tma_load_2d_pair(a, &tmA, x, n0, bar);
-                        tma_load_2d_pair(a + A_BYTES, &tmA, x + BK, n0, bar);
-                    } else {
-                        tma_load_2d_pair(a + 2 * A_BYTES, &tmB, x, m0, bar);
-                        tma_load_2d_pair(a + 2 * A_BYTES + atom_b, &tmB, x + BK, m0, bar);
-                    }
-                }
-            }
+    if (warp == 0 || warp >= 6) {
+        // Producers, as in gemm_f16_tn: a stage's two boxes go out in one instruction, kProducers warps take the stages in turn.
+        const uint32_t prod = warp == 0 ? 0u : (uint32_t)warp - 5u;
+        const uint32_t my_tiles = tiles > pair ? (tiles - pair + npairs - 1) / npairs : 0u;
+        const uint32_t total = my_tiles * num_kb;
+        for (uint32_t it = prod; it < total; it += kProducers) {
+            const uint32_t s = it % stages, ph = (it / stages) & 1u;
+            const uint32_t t = it / num_kb, kb = it - t * num_kb, tile = pair + t * npairs;
+            const int n0 = (int)((tile / tiles_m) * 2 * BM + rank * BM), m0 = (int)((tile % tiles_m) * bn + rank * half);
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) { dead = true; break; }
+            uint8_t* a = smem + (size_t)s * stage_bytes;
+            const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+            if (lane == 0 && rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
+            __syncwarp();
+            if (lane < 2)                                                // rows or tokens past the end arrive as zeros
+                tma_load_2d_pair(lane == 0 ? a : a + A_BYTES, lane == 0 ? &tmA : &tmB, (int)(kb * BK), lane == 0 ? n0 : m0, bar);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            uint32_t s = 0, ph = 0, tcount = 0;
-            bool ready = false;
+            uint32_t s = 0, ph = 0, tcount = 0, ready = 0;      // ready: bit 0 / 1 = stage s / the one after it was complete when last probed
+            auto next = [&](uint32_t& st, uint32_t& p) { if (++st == stages) { st = 0; p ^= 1u; } };
             for (uint32_t tile = pair; tile < tiles && !dead; tile += npairs, ++tcount) {
                 const uint32_t buf = tcount & 1u;
                 if (!mbar_wait(&tempty[buf], ((tcount >> 1) & 1u) ^ 1u)) { dead = true; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!ready && !mbar_wait(&full[s], ph)) { dead = true; break; }
+                for (uint32_t kb = 0; kb < num_kb; kb += 2) {
+                    const bool two = kb + 1 < num_kb;
+                    uint32_t s1 = s, ph1 = ph;
+                    next(s1, ph1);
+                    if (!(ready & 1u) && !mbar_wait(&full[s], ph)) { dead = true; break; }
+                    if (two && !(ready & 2u) && !mbar_wait(&full[s1], ph1)) { dead = true; break; }
                     tc_fence_after();
-                    const uint32_t a = smem_u32(smem) + s * stage_bytes;
-                    uint32_t s1 = s + 1, ph1 = ph;
-                    if (s1 == stages) { s1 = 0; ph1 ^= 1u; }
-                    ready = umma_kblock2_pair(d_tmem, a, a + 2 * A_BYTES, A_BYTES, atom_b, idesc, kb ? 1u : 0u, &full[s1], ph1);
-                    umma_commit_pair(&empty[s]);
-                    s = s1; ph = ph1;
+                    const uint32_t a0 = smem_u32(smem) + s * stage_bytes, a1 = smem_u32(smem) + s1 * stage_bytes;
+                    if (two) {
+                        uint32_t s2 = s1, ph2 = ph1;
+                        next(s2, ph2);
+                        uint32_t s3 = s2, ph3 = ph2;
+                        next(s3, ph3);
+                        ready = umma_kblock2_pair(d_tmem, a0, a0 + A_BYTES, a1, a1 + A_BYTES, idesc, kb ? 1u : 0u, &full[s2], ph2, &full[s3], ph3);
+                        umma_commit_pair(&empty[s]);
+                        umma_commit_pair(&empty[s1]);
+                        s = s2; ph = ph2;
+                    } else {
+                        ready = umma_kblock_pair(d_tmem, a0, a0 + A_BYTES, idesc, kb ? 1u : 0u, &full[s1], ph1);
+                        umma_commit_pair(&empty[s]);
+                        s = s1; ph = ph1;
+                    }
                 }
                 if (dead) break;
                 umma_commit_pair(&tfull[buf]);

@@ -18,14 +18,15 @@
 // brought in by TMA; tcgen05.mma (kind::f16, fp32 accumulate) is issued by a single
 // thread and completion is tracked with tcgen05.commit on mbarriers.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA
-// issuer, warps 2..5 = epilogue (tcgen05.ld -> fp32 stores, transposing back to
-// C[token][row]; for a fixed token the 32 lanes of a warp write 32 consecutive rows,
-// one coalesced 128-byte store).
+// Warp roles of the TMA-fed kernels (256 threads): warps 0, 6, 7 = TMA producers taking the stages in
+// turn, warp 1 = TMEM allocator + MMA issuer, warps 2..5 = epilogue (tcgen05.ld -> fp32 stores,
+// transposing back to C[token][row]; for a fixed token the 32 lanes of a warp write 32 consecutive
+// rows, one coalesced 128-byte store). The in-kernel dequantizing form keeps one TMA producer and adds
+// eight converting warps.
 //
-// Two forms. The default (gemm_f16_tn) takes both operands by TMA from an fp16 copy that one pre-pass
-// launch writes to the workspace (weights dequantized exactly and rounded once, activations rounded
-// once). The other (gemm_q4_tn, TM_GEMM_FUSED=1, Q4_0 only) never materialises the fp16 weights: eight
+// Two forms. The default (gemm_f16_tn, and gemm_f16_tn_pair on CTA pairs for calls of many tiles) takes both
+// operands by TMA from an fp16 copy that one pre-pass launch writes to the workspace (weights dequantized
+// exactly and rounded once, activations rounded once). The other (gemm_q4_tn, TM_GEMM_FUSED=1, Q4_0 only) never materialises the fp16 weights: eight
 // producer warps take the rows' 18-byte blocks from a bulk-copied raw ring, turn the nibbles into
 // (n - 8) * d with two half2 instructions per pair (the same value the fp32 dequantizer rounded to fp16
 // gives) and store them into the stage in the 128-byte-swizzled K-major layout the MMA descriptor

@@ -956,6 +956,108 @@ unsigned pick_token_tile_pair(unsigned M, unsigned N, unsigned sms) {
 
 }  // namespace
 
+// The TMA-fed kernels over fp16 operands that are in place (or being written by the launch just before this one):
+// weights Wh [N][K], activations Ah [M][K].
+static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, cudaStream_t st) {
+    CUtensorMap tmA, tmB;
+    // Two SMs per tile (gemm_f16_tn_pair) where it measured faster: four or more waves of pair tiles. TM_GEMM_PAIR=0
+    // keeps one SM per tile everywhere, TM_GEMM_PAIR=1 pairs wherever there are 256 weight rows.
+    static const int pair_mode = [] { const char* e = std::getenv("TM_GEMM_PAIR"); return e && *e ? std::atoi(e) : -1; }();
+    const unsigned sms = (unsigned)device_sm_count();
+    const unsigned bn2 = pick_token_tile_pair(M, N, sms);
+    const unsigned long long pair_tiles = (unsigned long long)((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
+    const bool paired = N >= 2 * BM && sms >= 2 && (pair_mode == 1 || (pair_mode < 0 && pair_tiles >= 4ull * (sms / 2)));
+    if (paired) {
+        if (!make_map(&tmB, Ah, M, K, bn2 / 2) || !make_map(&tmA, Wh, N, K, BM)) return false;
+        static bool attr2 = false;
+        if (!attr2) {
+            if (cudaFuncSetAttribute(gemm_f16_tn_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+                return check_launch("gemm: shared memory attribute");
+            attr2 = true;
+        }
+        const unsigned tiles2 = ((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
+        const unsigned pairs = sms / 2 < tiles2 ? sms / 2 : tiles2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+        cudaLaunchAttribute at[2];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        at[1].id = cudaLaunchAttributeClusterDimension;
+        at[1].val.clusterDim.x = 2; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 2;
+        if (cudaLaunchKernelEx(&cfg, gemm_f16_tn_pair, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn2,
+                               device_status_word()) != cudaSuccess)
+            return check_launch("gemm_f16_tn_pair");
+        note_launch();
+        return check_launch("gemm_f16_tn_pair");
+    }
+    const unsigned bn = pick_token_tile(M, N, sms);
+    if (!make_map(&tmB, Ah, M, K, bn) || !make_map(&tmA, Wh, N, K, BM)) return false;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(gemm_f16_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+            return check_launch("gemm: shared memory attribute");
+        attr = true;
+    }
+    const unsigned tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    unsigned grid = sms;
+    if (grid > tiles) grid = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn,
+                           device_status_word()) != cudaSuccess)
+        return check_launch("gemm_f16_tn");
+    note_launch();
+    return check_launch("gemm_f16_tn");
+}
+
+// fp16 copy of a block-quantized tensor: the weight half of launch_gemm's pre-pass, for callers that keep it (the prefill
+// layer stack converts its static weights once instead of once per call).
+bool launch_weights_f16(const uint8_t* W, void* Wh_out, unsigned N, unsigned K, unsigned dtype, cudaStream_t st) {
+    const unsigned be = block_elems(dtype);
+    if (!be || dtype == DT_F16) return fail("gemm: dtype %u is not a block format", dtype);
+    if (!W || !Wh_out || (uintptr_t)Wh_out % 16) return fail("gemm: bad pointer for the fp16 weights");
+    if (N == 0) return true;
+    if (K == 0 || K % be || K % 8) return fail("gemm: K=%u is not a multiple of %u and of 8", K, be);
+    __half* Wh = (__half*)Wh_out;
+    const uint32_t row_bytes = (K / be) * block_bytes(dtype);
+    const unsigned per = 256 * kPrepItems;
+    const unsigned blocks_w = (unsigned)(((uint64_t)N * (K / 8) + per - 1) / per);
+    if (dtype == DT_Q4_0 && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
+        prepass_q4_f16<<<blocks_w, 256, 0, st>>>(W, row_bytes, Wh, N, K, nullptr, nullptr, 0, blocks_w);
+    } else if (dtype == DT_Q6_K && (uintptr_t)W % 2 == 0 && row_bytes % 2 == 0) {
+        prepass_q6k_f16<<<blocks_w, 256, 0, st>>>(W, row_bytes, Wh, N, K, nullptr, nullptr, 0, blocks_w);
+    } else {
+        return launch_dequant_half(W, Wh, N, K, dtype, st);
+    }
+    note_launch();
+    return check_launch("weights_f16");
+}
+
+size_t gemm_f16w_workspace_bytes(unsigned M, unsigned K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
+
+// The GEMM against weights that are already fp16 (launch_weights_f16): only the activations are rounded per call.
+bool launch_gemm_f16w(const float* A, const void* Wh, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K,
+                      void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (!A || !Wh || !C) return fail("gemm: null pointer");
+    if (M == 0 || N == 0) return true;
+    if (ldc < N) return fail("gemm: ldc=%u is smaller than N=%u", ldc, N);
+    if (K == 0 || K % 8) return fail("gemm: K must be a multiple of 8");
+    if ((uintptr_t)A % 16 || (uintptr_t)C % 4 || (uintptr_t)Wh % 16) return fail("gemm: A and the fp16 weights must be 16-byte aligned");
+    if (!workspace || (uintptr_t)workspace % 256 || workspace_bytes < gemm_f16w_workspace_bytes(M, K))
+        return fail("gemm: workspace of %zu bytes (256-byte aligned) required", gemm_f16w_workspace_bytes(M, K));
+    __half* Ah = (__half*)workspace;
+    const size_t n4 = (size_t)M * K / 4;
+    f32_to_f16_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(A, Ah, n4);
+    note_launch();
+    if (!check_launch("f32_to_f16_rows")) return false;
+    return launch_tiles((const __half*)Wh, Ah, C, ldc, M, N, K, st);
+}
+
 size_t gemm_workspace_bytes(unsigned M, unsigned N, unsigned K) {
     auto up = [](size_t b) { return (b + 255) / 256 * 256; };
     return up((size_t)N * K * 2) + up((size_t)M * K * 2);
@@ -1004,41 +1106,9 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
         if (!check_launch("f32_to_f16_rows")) return false;
     }
 
-    CUtensorMap tmA, tmB;
-    // Two SMs per tile (gemm_f16_tn_pair) where it measured faster: four or more waves of pair tiles. TM_GEMM_PAIR=0
-    // keeps one SM per tile everywhere, TM_GEMM_PAIR=1 pairs wherever there are 256 weight rows.
-    static const int pair_mode = [] { const char* e = std::getenv("TM_GEMM_PAIR"); return e && *e ? std::atoi(e) : -1; }();
-    const unsigned sms = (unsigned)device_sm_count();
-    const unsigned bn2 = pick_token_tile_pair(M, N, sms);
-    const unsigned long long pair_tiles = (unsigned long long)((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
-    const bool paired = !fused && N >= 2 * BM && sms >= 2 && (pair_mode == 1 || (pair_mode < 0 && pair_tiles >= 4ull * (sms / 2)));
-    if (paired) {
-        if (!make_map(&tmB, Ah, M, K, bn2 / 2) || !make_map(&tmA, Wh, N, K, BM)) return false;
-        static bool attr2 = false;
-        if (!attr2) {
-            if (cudaFuncSetAttribute(gemm_f16_tn_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
-                return check_launch("gemm: shared memory attribute");
-            attr2 = true;
-        }
-        const unsigned tiles2 = ((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
-        const unsigned pairs = sms / 2 < tiles2 ? sms / 2 : tiles2;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
-        cudaLaunchAttribute at[2];
-        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[0].val.programmaticStreamSerializationAllowed = 1;
-        at[1].id = cudaLaunchAttributeClusterDimension;
-        at[1].val.clusterDim.x = 2; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
-        cfg.attrs = at; cfg.numAttrs = 2;
-        if (cudaLaunchKernelEx(&cfg, gemm_f16_tn_pair, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn2,
-                               device_status_word()) != cudaSuccess)
-            return check_launch("gemm_f16_tn_pair");
-        note_launch();
-        return check_launch("gemm_f16_tn_pair");
-    }
-    const unsigned bn = fused ? (unsigned)BN : pick_token_tile(M, N, sms);
-    if (!make_map(&tmB, Ah, M, K, bn)) return false;
     if (fused) {
+        CUtensorMap tmB;
+        if (!make_map(&tmB, Ah, M, K, BN)) return false;
         static bool attr4 = false;
         if (!attr4) {
             if (cudaFuncSetAttribute(gemm_q4_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesQ4) != cudaSuccess)
@@ -1052,27 +1122,7 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
         note_launch();
         return check_launch("gemm_q4_tn");
     }
-    if (!make_map(&tmA, Wh, N, K, BM)) return false;
-    static bool attr = false;
-    if (!attr) {
-        if (cudaFuncSetAttribute(gemm_f16_tn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
-            return check_launch("gemm: shared memory attribute");
-        attr = true;
-    }
-    const unsigned tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-    unsigned grid = (unsigned)device_sm_count();
-    if (grid > tiles) grid = tiles;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreadsTma); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn,
-                           device_status_word()) != cudaSuccess)
-        return check_launch("gemm_f16_tn");
-    note_launch();
-    return check_launch("gemm_f16_tn");
+    return launch_tiles(Wh, Ah, C, ldc, M, N, K, st);
 }
 
 }  // namespace tmc

@@ -26,6 +26,7 @@
 
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -289,6 +290,9 @@ struct Layer {
     const uint8_t *q, *k, *v, *o, *gate, *up, *down;            // device block streams
     float *rms1 = nullptr, *rms2 = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr;
     float *kc = nullptr, *vc = nullptr;                         // device caches
+    // fp16 copies of the static weights (Stack::resident): q|k|v rows stacked [QD + 2 KVD][D], o [D][QD],
+    // gate|up stacked [2 F][D], down [D][F]
+    void *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr;
     float *kc_host = nullptr, *vc_host = nullptr;               // the caller's arrays
     bool pinned_k = false, pinned_v = false;
     cudaEvent_t kv_ready = nullptr, kv_done = nullptr;
@@ -299,6 +303,8 @@ struct Stack {
     unsigned dtype = DT_Q4_0;
     std::vector<Layer> layers;
     float *x = nullptr, *h = nullptr, *qkv = nullptr, *ao = nullptr, *h2 = nullptr, *g = nullptr, *u = nullptr;
+    float* gu = nullptr;                                        // resident form: gate|up of the batch, [T][2 F]
+    bool resident = false;                                      // the layers hold fp16 copies of their weights
     void* ws = nullptr;
     size_t ws_bytes = 0;
     int cap_T = 0;
@@ -310,6 +316,7 @@ struct Stack {
         if (copy) { cudaStreamSynchronize(copy); cudaStreamDestroy(copy); }
         for (Layer& l : layers) {
             for (float* p : {l.rms1, l.rms2, l.qb, l.kb, l.vb, l.kc, l.vc}) if (p) cudaFree(p);
+            for (void* p : {l.wqkv, l.wo, l.wgu, l.wdown}) if (p) cudaFree(p);
             if (l.pinned_k) cudaHostUnregister(l.kc_host);
             if (l.pinned_v) cudaHostUnregister(l.vc_host);
             if (l.kv_ready) cudaEventDestroy(l.kv_ready);
@@ -321,7 +328,7 @@ struct Stack {
         cudaGetLastError();
     }
     void free_scratch() {
-        for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u}) if (*p) { cudaFree(*p); *p = nullptr; }
+        for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u, &gu}) if (*p) { cudaFree(*p); *p = nullptr; }
         if (ws) { cudaFree(ws); ws = nullptr; }
         cap_T = 0;
     }
@@ -346,13 +353,18 @@ bool ensure_scratch(Stack& c, int T) {
     auto mk = [&](size_t floats) { float* p = nullptr; if (cudaMalloc(&p, floats * 4) != cudaSuccess) { cudaGetLastError(); p = nullptr; } return p; };
     const size_t t = (size_t)T;
     c.x = mk(t * c.D); c.h = mk(t * c.D); c.h2 = mk(t * c.D); c.qkv = mk(t * (c.QD + 2 * c.KVD)); c.ao = mk(t * c.QD);
-    c.g = mk(t * c.F); c.u = mk(t * c.F);
+    c.g = mk(t * c.F);
+    if (c.resident) c.gu = mk(t * 2 * c.F); else c.u = mk(t * c.F);
     size_t need = 0;
-    for (auto nk : {std::pair<int, int>{c.QD, c.D}, {c.KVD, c.D}, {c.D, c.QD}, {c.F, c.D}, {c.D, c.F}})
-        need = std::max(need, gemm_workspace_bytes((unsigned)T, (unsigned)nk.first, (unsigned)nk.second));
+    if (c.resident) {
+        need = gemm_f16w_workspace_bytes((unsigned)T, (unsigned)std::max(std::max(c.D, c.QD), c.F));
+    } else {
+        for (auto nk : {std::pair<int, int>{c.QD, c.D}, {c.KVD, c.D}, {c.D, c.QD}, {c.F, c.D}, {c.D, c.F}})
+            need = std::max(need, gemm_workspace_bytes((unsigned)T, (unsigned)nk.first, (unsigned)nk.second));
+    }
     if (cudaMalloc(&c.ws, need) != cudaSuccess) { cudaGetLastError(); c.ws = nullptr; }
     c.ws_bytes = need;
-    if (!(c.x && c.h && c.h2 && c.qkv && c.ao && c.g && c.u && c.ws)) { c.free_scratch(); return fail("llama stack: out of device memory for a %d-token batch", T); }
+    if (!(c.x && c.h && c.h2 && c.qkv && c.ao && c.g && (c.resident ? c.gu : c.u) && c.ws)) { c.free_scratch(); return fail("llama stack: out of device memory for a %d-token batch", T); }
     c.cap_T = T;
     return true;
 }
@@ -370,6 +382,15 @@ bool attn_ready() {
     return true;
 }
 
+// act[t][f] = silu(gu[t][f]) * gu[t][F + f]: gate and up come out of ONE GEMM against the stacked gate|up rows
+__global__ void silu_mul_stacked_kernel(const float* __restrict__ gu, float* __restrict__ act, uint32_t F, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t t = i / F, f = i % F;
+    const float g = gu[t * 2 * F + f], u = gu[t * 2 * F + F + f];
+    act[i] = g / (1.0f + expf(-g)) * u;
+}
+
 bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     Layer& L = c.layers[(size_t)l];
     const unsigned D = (unsigned)c.D, QD = (unsigned)c.QD, KVD = (unsigned)c.KVD, F = (unsigned)c.F, dh = (unsigned)c.dh;
@@ -378,9 +399,16 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     auto gemm = [&](const float* A, const uint8_t* W, float* Cm, unsigned ldc, unsigned N, unsigned K) {
         return launch_gemm(A, W, Cm, ldc, Tn, N, K, c.dtype, c.ws, c.ws_bytes, st);
     };
+    auto gemm_h = [&](const float* A, const void* Wh, float* Cm, unsigned ldc, unsigned N, unsigned K) {
+        return launch_gemm_f16w(A, Wh, Cm, ldc, Tn, N, K, c.ws, c.ws_bytes, st);
+    };
     // 1. norm, q / k / v into one [T][QD + 2 KVD] buffer
     rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms1, c.h, D, c.eps); note_launch();
-    if (!gemm(c.h, L.q, c.qkv, ld, QD, D) || !gemm(c.h, L.k, c.qkv + QD, ld, KVD, D) || !gemm(c.h, L.v, c.qkv + QD + KVD, ld, KVD, D)) return false;
+    if (c.resident) {
+        if (!gemm_h(c.h, L.wqkv, c.qkv, ld, ld, D)) return false;                     // one GEMM against the stacked rows
+    } else if (!gemm(c.h, L.q, c.qkv, ld, QD, D) || !gemm(c.h, L.k, c.qkv + QD, ld, KVD, D) || !gemm(c.h, L.v, c.qkv + QD + KVD, ld, KVD, D)) {
+        return false;
+    }
     if (L.qb) {
         bias_rows_kernel<<<(unsigned)(((size_t)T * QD + 255) / 256), 256, 0, st>>>(c.qkv, L.qb, QD, ld, Tn);
         bias_rows_kernel<<<(unsigned)(((size_t)T * KVD + 255) / 256), 256, 0, st>>>(c.qkv + QD, L.kb, KVD, ld, Tn);
@@ -413,12 +441,20 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     }
     note_launch();
     // 4. o + residual, norm, gate / up, silu * up, down + residual
-    if (!gemm(c.ao, L.o, c.h2, D, D, QD)) return false;
+    if (!(c.resident ? gemm_h(c.ao, L.wo, c.h2, D, D, QD) : gemm(c.ao, L.o, c.h2, D, D, QD))) return false;
     if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
     rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms2, c.h, D, c.eps); note_launch();
-    if (!gemm(c.h, L.gate, c.g, F, F, D) || !gemm(c.h, L.up, c.u, F, F, D)) return false;
-    if (!launch_silu_mul(c.g, c.u, Tn * F, st)) return false;
-    if (!gemm(c.g, L.down, c.h2, D, D, F)) return false;
+    if (c.resident) {
+        if (!gemm_h(c.h, L.wgu, c.gu, 2 * F, 2 * F, D)) return false;
+        const size_t n = (size_t)Tn * F;
+        silu_mul_stacked_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c.gu, c.g, F, n);
+        note_launch();
+        if (!gemm_h(c.g, L.wdown, c.h2, D, D, F)) return false;
+    } else {
+        if (!gemm(c.h, L.gate, c.g, F, F, D) || !gemm(c.h, L.up, c.u, F, F, D)) return false;
+        if (!launch_silu_mul(c.g, c.u, Tn * F, st)) return false;
+        if (!gemm(c.g, L.down, c.h2, D, D, F)) return false;
+    }
     if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
     return check_launch("llama stack layer");
 }
@@ -507,6 +543,43 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
         cudaGetLastError();
         if (cudaEventCreateWithFlags(&L.kv_ready, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&L.kv_done, cudaEventDisableTiming) != cudaSuccess) { check_launch("llama stack: events"); return nullptr; }
+    }
+    // fp16 copies of the weights, made once: 2 bytes per weight of HBM buy every later prefill its weight pre-passes
+    // (a quarter of a 512-token prompt's GPU time) and let q|k|v and gate|up run as one GEMM each. Taken when they use
+    // no more than a third of the free memory; TM_CUDA_STACK_FP16=0 keeps the per-call conversion, =1 insists.
+    {
+        const char* e = std::getenv("TM_CUDA_STACK_FP16");
+        const int mode = e && *e ? std::atoi(e) : -1;
+        const size_t per_layer = 2 * ((size_t)(c->QD + 2 * c->KVD) * c->D + (size_t)c->D * c->QD + (size_t)3 * c->F * c->D);
+        size_t free_b = 0, total_b = 0;
+        if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); free_b = 0; }
+        if (mode == 1 || (mode < 0 && per_layer * (size_t)c->L <= free_b / 3)) {
+            bool ok = true;
+            for (Layer& L : c->layers) {
+                const size_t qd = (size_t)c->QD * c->D * 2, kvd = (size_t)c->KVD * c->D * 2, fd = (size_t)c->F * c->D * 2;
+                ok = ok && cudaMalloc(&L.wqkv, qd + 2 * kvd) == cudaSuccess && cudaMalloc(&L.wo, qd) == cudaSuccess &&
+                     cudaMalloc(&L.wgu, 2 * fd) == cudaSuccess && cudaMalloc(&L.wdown, fd) == cudaSuccess;
+                if (!ok) break;
+                uint8_t* qkv = (uint8_t*)L.wqkv; uint8_t* gu = (uint8_t*)L.wgu;
+                ok = launch_weights_f16(L.q, qkv, (unsigned)c->QD, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.k, qkv + qd, (unsigned)c->KVD, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.v, qkv + qd + kvd, (unsigned)c->KVD, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.o, L.wo, (unsigned)c->D, (unsigned)c->QD, dtype, s.stream) &&
+                     launch_weights_f16(L.gate, gu, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.up, gu + fd, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.down, L.wdown, (unsigned)c->D, (unsigned)c->F, dtype, s.stream);
+                if (!ok) break;
+            }
+            if (ok) {
+                c->resident = true;
+            } else {
+                cudaGetLastError();
+                cudaStreamSynchronize(s.stream);
+                for (Layer& L : c->layers)
+                    for (void** p : {&L.wqkv, &L.wo, &L.wgu, &L.wdown}) if (*p) { cudaFree(*p); *p = nullptr; }
+                if (mode == 1) { fail("llama stack: no room for the fp16 copies of the weights"); return nullptr; }
+            }
+        }
     }
     if (!sync_stream(s.stream, "llama stack: create")) return nullptr;
     return c.release();

@@ -68,6 +68,26 @@ def test_stack_matches_cpu_block_loop(cuda, orc, cfg, T):
     st.close()
 
 
+@pytest.mark.parametrize("cfg", [TINY, GQA128], ids=["dh64-rep2", "dh128-rep4"])
+def test_resident_fp16_weights_equal_per_call_conversion(cuda, orc, cfg, monkeypatch):
+    """The stack keeps fp16 copies of its weights when they fit (q|k|v and gate|up then run as one GEMM each); with
+    TM_CUDA_STACK_FP16=0 every GEMM call converts its weights again. Same fp16 operands, same order of accumulation over
+    K for every output element: the two forms must agree bit for bit."""
+    T = 300
+    w = synth.make_llama(cfg, seed=23)
+    x = _embed(orc, cfg, w, synth.make_tokens(T, cfg["V"], seed=24))
+    out = []
+    for mode in ("0", "1"):
+        monkeypatch.setenv("TM_CUDA_STACK_FP16", mode)
+        st = stack.Stack(cfg, w)
+        got = st.prefill(x, 0)
+        out.append((got, [k.copy() for k in st.kc], [v.copy() for v in st.vc]))
+        st.close()
+    assert np.array_equal(out[0][0].view(np.uint32), out[1][0].view(np.uint32))
+    for a, b in zip(out[0][1] + out[0][2], out[1][1] + out[1][2]):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 def test_chunked_prefill_and_wait_layer(cuda, orc):
     cfg = GQA128
     w = synth.make_llama(cfg, seed=23)

@@ -115,164 +115,175 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Causal GQA attention of a token batch against the fp32 caches. grid (token blocks, KVH), 256 threads = 8 warps.
+// Causal GQA attention of a token batch against the fp32 caches. grid (token blocks, KVH), 128 threads = 4 warps.
 // Row r of a CTA = token t0 + r / REP, query head g * REP + r % REP; BT = 64 / REP tokens per CTA, keys in tiles of 32.
 // Both products run on the tensor cores as m16n8k8 tf32 MMAs with fp32 accumulation: q (pre-scaled), k, v and the
 // probabilities are rounded once to tf32 (10 mantissa bits, the precision the projections' fp16 operands have, with
 // fp32's range: scores of 128-wide heads overflow fp16); scores, softmax statistics and the output stay fp32.
-//   scores: warp w -> rows [16 (w / 2), +16) x keys [16 (w % 2), +16) of the tile (2 n-tiles, DH / 8 k-steps)
-//   output: warp w -> rows [16 (w / 2), +16) x dims [DH/2 (w % 2), + DH/2)     (DH / 16 n-tiles, 4 k-steps per tile)
-// Shared-memory strides are chosen so that the 32 lanes of a fragment load (8 rows x 4 columns) hit 32 banks.
+//
+// Warp w owns rows [16 w, +16) for the whole kernel: its q fragments live in registers, the scores of a key tile
+// (16 x 32) come out of the MMAs in the accumulator layout - thread (g, t) of a warp holds, per 8 keys, columns 2t and
+// 2t + 1 of rows g and g + 8 - and the softmax runs on them in place (row maxima and sums over the four lanes of a
+// quad). The probabilities feed the second product without leaving the registers: that product sums over keys, so its
+// k index may be any fixed permutation of them, and naming key 2t "k = t" and key 2t + 1 "k = t + 4" makes the
+// accumulator layout of P the A-operand layout; V's fragments are loaded with the same naming (rows 2t and 2t + 1).
+// K and V tiles arrive by cp.async into a two-deep ring; the thread that copied a piece rounds it to tf32 in place, so
+// one barrier publishes a tile and one more protects its buffer from the copy after next: two barriers per 32 keys
+// (the previous layout, which split a tile's keys over the warps, took four and sent the scores through shared memory).
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 template <int DH>
-__global__ void __launch_bounds__(256) prefill_attn_kernel(const float* __restrict__ qkv, uint32_t ld, const float* __restrict__ kc,
-                                                           const float* __restrict__ vc, float* __restrict__ out, uint32_t QD,
-                                                           uint32_t T, uint32_t pos0, uint32_t ctx, uint32_t REP, float scale) {
-    constexpr int QS = DH + 4;                                  // Q and K rows: stride 4 (mod 32)
-    constexpr int VS = DH + 8;                                  // V rows: stride 8 (mod 32)
+__global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __restrict__ qkv, uint32_t ld, const float* __restrict__ kc,
+                                                              const float* __restrict__ vc, float* __restrict__ out, uint32_t QD,
+                                                              uint32_t T, uint32_t pos0, uint32_t ctx, uint32_t REP, float scale) {
+    constexpr int RS = DH + 4;                                  // K and V rows in shared memory: stride 4 (mod 32), conflict-free fragments
     constexpr int D4 = DH / 4;
-    constexpr int NT = DH / 16;                                 // output n-tiles per warp
-    extern __shared__ __align__(16) float sm[];
-    float* Qs = sm;                                             // [64][QS] tf32 bit patterns
-    float* Ks = Qs + 64 * QS;                                   // [32][QS]
-    float* Vs = Ks + 32 * QS;                                   // [32][VS]
-    float* Ss = Vs + 32 * VS;                                   // [64][33] scores, then probabilities (fp32)
-    float* mrow = Ss + 64 * 33;                                 // running max, sum, rescale factor per row
-    float* lrow = mrow + 64;
-    float* arow = lrow + 64;
+    constexpr int KS = DH / 8;                                  // k-steps of q k^T
+    constexpr int NT = DH / 8;                                  // output n-tiles (a warp holds all DH dims of its rows)
+    constexpr int PER = 32 * D4 / 128;                          // 16-byte pieces per thread, tile and tensor
+    extern __shared__ __align__(16) float sm[];                 // ring: [buf][K 32 x RS | V 32 x RS]
     const uint32_t BT = 64u / REP, nrows = BT * REP, g = blockIdx.y, t0 = blockIdx.x * BT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int fg = lane >> 2, ft = lane & 3;                    // fragment coordinates of this lane
-    const int rb = warp >> 1, wh = warp & 1;
-    const uint32_t t_end = min(T, t0 + BT);                     // tokens [t0, t_end)
+    const int fg = lane >> 2, ft = lane & 3;
+    const uint32_t t_end = min(T, t0 + BT);
     const uint32_t kmax = pos0 + t_end;                         // keys [0, kmax) are visible to the block's last token
+    const float* kbase = kc + (size_t)g * ctx * DH;
+    const float* vbase = vc + (size_t)g * ctx * DH;
 
-    for (int i = tid; i < 64 * D4; i += 256) {
-        const uint32_t r = i / D4, c = i % D4, t = t0 + r / REP;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < nrows && t < T) v = *reinterpret_cast<const float4*>(qkv + (size_t)t * ld + (size_t)(g * REP + r % REP) * DH + 4 * c);
-        uint4 q;
-        q.x = to_tf32(v.x * scale); q.y = to_tf32(v.y * scale); q.z = to_tf32(v.z * scale); q.w = to_tf32(v.w * scale);
-        *reinterpret_cast<uint4*>(Qs + r * QS + 4 * c) = q;
+    auto tile_k = [&](int b) { return sm + (size_t)b * 2 * 32 * RS; };
+    auto tile_v = [&](int b) { return sm + (size_t)b * 2 * 32 * RS + 32 * RS; };
+    auto copy_tile = [&](int b, uint32_t k0) {
+        float* Kd = tile_k(b);
+        float* Vd = tile_v(b);
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int i = tid + u * 128;
+            const uint32_t j = i / D4, c = i % D4, kk = k0 + j;
+            if (kk < kmax) {
+                cp_async16(Kd + j * RS + 4 * c, kbase + (size_t)kk * DH + 4 * c);
+                cp_async16(Vd + j * RS + 4 * c, vbase + (size_t)kk * DH + 4 * c);
+            } else {
+                *reinterpret_cast<float4*>(Kd + j * RS + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(Vd + j * RS + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto round_own = [&](int b) {                               // the pieces THIS thread copied, fp32 -> tf32 bit patterns
+        float* Kd = tile_k(b);
+        float* Vd = tile_v(b);
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int i = tid + u * 128;
+            const uint32_t j = i / D4, c = i % D4;
+            const float4 a = *reinterpret_cast<const float4*>(Kd + j * RS + 4 * c), v = *reinterpret_cast<const float4*>(Vd + j * RS + 4 * c);
+            uint4 ua, uv;
+            ua.x = to_tf32(a.x); ua.y = to_tf32(a.y); ua.z = to_tf32(a.z); ua.w = to_tf32(a.w);
+            uv.x = to_tf32(v.x); uv.y = to_tf32(v.y); uv.z = to_tf32(v.z); uv.w = to_tf32(v.w);
+            *reinterpret_cast<uint4*>(Kd + j * RS + 4 * c) = ua;
+            *reinterpret_cast<uint4*>(Vd + j * RS + 4 * c) = uv;
+        }
+    };
+    copy_tile(0, 0);
+
+    // this lane's rows: r0 = 16 warp + fg and r1 = r0 + 8
+    const uint32_t r0 = 16u * warp + fg, r1 = r0 + 8;
+    const uint32_t tok0 = t0 + r0 / REP, tok1 = t0 + r1 / REP;
+    const bool live0 = r0 < nrows && tok0 < T, live1 = r1 < nrows && tok1 < T;
+    // q fragments of the warp's 16 rows, pre-scaled, tf32: a0 (g, t) a1 (g + 8, t) a2 (g, t + 4) a3 (g + 8, t + 4) per k-step
+    uint32_t qf[KS][4];
+    {
+        const float* q0 = qkv + (size_t)(live0 ? tok0 : 0) * ld + (size_t)(g * REP + r0 % REP) * DH;
+        const float* q1 = qkv + (size_t)(live1 ? tok1 : 0) * ld + (size_t)(g * REP + r1 % REP) * DH;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = to_tf32(live0 ? q0[8 * ks + ft] * scale : 0.f);
+            qf[ks][1] = to_tf32(live1 ? q1[8 * ks + ft] * scale : 0.f);
+            qf[ks][2] = to_tf32(live0 ? q0[8 * ks + ft + 4] * scale : 0.f);
+            qf[ks][3] = to_tf32(live1 ? q1[8 * ks + ft + 4] * scale : 0.f);
+        }
     }
-    if (tid < 64) { mrow[tid] = -INFINITY; lrow[tid] = 0.f; arow[tid] = 1.f; }
-
     float acc[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;    // running maxima (whole row) and this lane's share of the sums
+    const uint32_t lim0 = pos0 + tok0, lim1 = pos0 + tok1;      // last visible key of each row
 
-    const float* kbase = kc + (size_t)g * ctx * DH;
-    const float* vbase = vc + (size_t)g * ctx * DH;
-    const uint32_t* Qu = reinterpret_cast<const uint32_t*>(Qs);
-    const uint32_t* Ku = reinterpret_cast<const uint32_t*>(Ks);
-    const uint32_t* Vu = reinterpret_cast<const uint32_t*>(Vs);
-    // K and V tiles travel global -> registers -> shared memory, one tile ahead: the loads of tile k0 + 32 are in flight
-    // while tile k0 is multiplied (with the loads issued where they are used, an iteration was one exposed L2/HBM round
-    // trip after the other: 8.7 us per 32 keys against ~1 us of MMA time).
-    constexpr int PF = 32 * D4 / 256;                           // float4 per thread and tensor: 4 at DH = 128, 2 at DH = 64
-    float4 kreg[PF], vreg[PF];
-    auto fetch_tile = [&](uint32_t k0) {
+    int buf = 0;
+    for (uint32_t k0 = 0; k0 < kmax; k0 += 32, buf ^= 1) {
+        if (k0 + 32 < kmax) {
+            copy_tile(buf ^ 1, k0 + 32);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        round_own(buf);
+        __syncthreads();                                        // tile k0 is in place, rounded
+        const uint32_t* Ku = reinterpret_cast<const uint32_t*>(tile_k(buf));
+        const uint32_t* Vu = reinterpret_cast<const uint32_t*>(tile_v(buf));
+        // scores of the warp's 16 rows x 32 keys: four n-tiles of 8 keys
+        float sc[4][4];
 #pragma unroll
-        for (int u = 0; u < PF; ++u) {
-            const int i = tid + u * 256;
-            const uint32_t j = i / D4, c = i % D4, kk = k0 + j;
-            kreg[u] = make_float4(0.f, 0.f, 0.f, 0.f); vreg[u] = kreg[u];
-            if (kk < kmax) {
-                kreg[u] = *reinterpret_cast<const float4*>(kbase + (size_t)kk * DH + 4 * c);
-                vreg[u] = *reinterpret_cast<const float4*>(vbase + (size_t)kk * DH + 4 * c);
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                mma_tf32(sc[j], qf[ks], Ku[(8 * j + fg) * RS + 8 * ks + ft], Ku[(8 * j + fg) * RS + 8 * ks + ft + 4]);
+        // causal mask, row maxima over the quad
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t kk = k0 + 8 * j + 2 * ft + e;
+                if (!(live0 && kk <= lim0)) sc[j][e] = -INFINITY;
+                if (!(live1 && kk <= lim1)) sc[j][2 + e] = -INFINITY;
+                mx0 = fmaxf(mx0, sc[j][e]); mx1 = fmaxf(mx1, sc[j][2 + e]);
             }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float al0 = (m0 > -INFINITY) ? expf(m0 - n0) : 1.f, al1 = (m1 > -INFINITY) ? expf(m1 - n1) : 1.f;   // nothing accumulated yet: nothing to rescale
+        m0 = n0; m1 = n1;
+        uint32_t pf[4][4];                                      // probabilities as A fragments: a0 = (g, key 2t), a2 = (g, key 2t + 1); a1, a3 the same for g + 8
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float p00 = (n0 > -INFINITY) ? expf(sc[j][0] - n0) : 0.f, p01 = (n0 > -INFINITY) ? expf(sc[j][1] - n0) : 0.f;
+            const float p10 = (n1 > -INFINITY) ? expf(sc[j][2] - n1) : 0.f, p11 = (n1 > -INFINITY) ? expf(sc[j][3] - n1) : 0.f;
+            s0 += p00 + p01; s1 += p10 + p11;
+            pf[j][0] = to_tf32(p00); pf[j][2] = to_tf32(p01); pf[j][1] = to_tf32(p10); pf[j][3] = to_tf32(p11);
         }
-    };
-    fetch_tile(0);
-    for (uint32_t k0 = 0; k0 < kmax; k0 += 32) {
-        __syncthreads();                                        // the previous tile's K, V and P are no longer read
-#pragma unroll
-        for (int u = 0; u < PF; ++u) {
-            const int i = tid + u * 256;
-            const uint32_t j = i / D4, c = i % D4;
-            uint4 a, b;
-            a.x = to_tf32(kreg[u].x); a.y = to_tf32(kreg[u].y); a.z = to_tf32(kreg[u].z); a.w = to_tf32(kreg[u].w);
-            b.x = to_tf32(vreg[u].x); b.y = to_tf32(vreg[u].y); b.z = to_tf32(vreg[u].z); b.w = to_tf32(vreg[u].w);
-            *reinterpret_cast<uint4*>(Ks + j * QS + 4 * c) = a;
-            *reinterpret_cast<uint4*>(Vs + j * VS + 4 * c) = b;
-        }
-        if (k0 + 32 < kmax) fetch_tile(k0 + 32);
-        __syncthreads();
-        // scores of rows [16 rb, +16) x keys [16 wh, +16)
-        float sc[2][4];
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) sc[n][e] = 0.f;
-#pragma unroll 4
-        for (int ks = 0; ks < DH / 8; ++ks) {
-            uint32_t a[4];
-            a[0] = Qu[(16 * rb + fg) * QS + 8 * ks + ft];
-            a[1] = Qu[(16 * rb + fg + 8) * QS + 8 * ks + ft];
-            a[2] = Qu[(16 * rb + fg) * QS + 8 * ks + ft + 4];
-            a[3] = Qu[(16 * rb + fg + 8) * QS + 8 * ks + ft + 4];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int key = 16 * wh + 8 * n + fg;
-                mma_tf32(sc[n], a, Ku[key * QS + 8 * ks + ft], Ku[key * QS + 8 * ks + ft + 4]);
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const int col = 16 * wh + 8 * n + 2 * ft;
-            Ss[(16 * rb + fg) * 33 + col] = sc[n][0];
-            Ss[(16 * rb + fg) * 33 + col + 1] = sc[n][1];
-            Ss[(16 * rb + fg + 8) * 33 + col] = sc[n][2];
-            Ss[(16 * rb + fg + 8) * 33 + col + 1] = sc[n][3];
-        }
-        __syncthreads();
-        // online softmax: warp w owns rows 8 w .. 8 w + 7, lane = key of the tile
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t r = 8 * warp + i, t = t0 + r / REP, kk = k0 + lane;
-            const bool ok = r < nrows && t < T && kk <= pos0 + t;
-            const float sv = ok ? Ss[r * 33 + lane] : -INFINITY;
-            const float m_old = mrow[r];
-            const float m_new = fmaxf(m_old, wmax(sv));
-            const float p = (ok && m_new > -INFINITY) ? expf(sv - m_new) : 0.f;
-            const float sum = wsum(p);
-            const float alpha = (m_old > -INFINITY) ? expf(m_old - m_new) : 1.f;   // nothing accumulated yet: nothing to rescale
-            Ss[r * 33 + lane] = p;
-            if (lane == 0) { mrow[r] = m_new; lrow[r] = lrow[r] * alpha + sum; arow[r] = alpha; }
-        }
-        __syncthreads();
-        // output of rows [16 rb, +16) x dims [DH/2 wh, +DH/2): rescale, then += P V
-        const float al0 = arow[16 * rb + fg], al1 = arow[16 * rb + fg + 8];
+        l0 = l0 * al0 + s0; l1 = l1 * al1 + s1;
 #pragma unroll
         for (int n = 0; n < NT; ++n) { acc[n][0] *= al0; acc[n][1] *= al0; acc[n][2] *= al1; acc[n][3] *= al1; }
+        // output += P V, keys 8 j + (2t, 2t + 1) under the names k = t, t + 4
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            uint32_t a[4];
-            a[0] = to_tf32(Ss[(16 * rb + fg) * 33 + 8 * ks + ft]);
-            a[1] = to_tf32(Ss[(16 * rb + fg + 8) * 33 + 8 * ks + ft]);
-            a[2] = to_tf32(Ss[(16 * rb + fg) * 33 + 8 * ks + ft + 4]);
-            a[3] = to_tf32(Ss[(16 * rb + fg + 8) * 33 + 8 * ks + ft + 4]);
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const int dim = (DH / 2) * wh + 8 * n + fg;
-                mma_tf32(acc[n], a, Vu[(8 * ks + ft) * VS + dim], Vu[(8 * ks + ft + 4) * VS + dim]);
-            }
-        }
-    }
-    __syncthreads();
-    {
-        const uint32_t r0 = 16 * rb + fg, r1 = r0 + 8;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint32_t row = half ? r1 : r0, t = t0 + row / REP;
-            if (row >= nrows || t >= T) continue;
-            const float inv = 1.0f / lrow[row];
-            float* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + (DH / 2) * wh + 2 * ft;
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int n = 0; n < NT; ++n)
-                *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
-        }
+                mma_tf32(acc[n], pf[j], Vu[(8 * j + 2 * ft) * RS + 8 * n + fg], Vu[(8 * j + 2 * ft + 1) * RS + 8 * n + fg]);
+        __syncthreads();                                        // every warp is done with this buffer: the copy after next may reuse it
+    }
+    // the lanes of a quad hold disjoint shares of a row's sum
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const bool live = half ? live1 : live0;
+        if (!live) continue;
+        const uint32_t row = half ? r1 : r0, t = half ? tok1 : tok0;
+        const float inv = 1.0f / (half ? l1 : l0);
+        float* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + 2 * ft;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+            *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
     }
 }
 
@@ -369,7 +380,7 @@ bool ensure_scratch(Stack& c, int T) {
     return true;
 }
 
-template <int DH> constexpr size_t attn_smem() { return (size_t)(64 * (DH + 4) + 32 * (DH + 4) + 32 * (DH + 8) + 64 * 33 + 3 * 64) * 4; }
+template <int DH> constexpr size_t attn_smem() { return (size_t)(2 * 2 * 32 * (DH + 4)) * 4; }     // two tiles of K and V
 template <int DH>
 bool attn_ready() {
     constexpr size_t smem = attn_smem<DH>();
@@ -434,10 +445,10 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     const dim3 grid((Tn + BT - 1) / BT, (unsigned)c.KVH);
     if (dh == 128) {
         if (!attn_ready<128>()) return false;
-        prefill_attn_kernel<128><<<grid, 256, attn_smem<128>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+        prefill_attn_kernel<128><<<grid, 128, attn_smem<128>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
     } else {
         if (!attn_ready<64>()) return false;
-        prefill_attn_kernel<64><<<grid, 256, attn_smem<64>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+        prefill_attn_kernel<64><<<grid, 128, attn_smem<64>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
     }
     note_launch();
     // 4. o + residual, norm, gate / up, silu * up, down + residual

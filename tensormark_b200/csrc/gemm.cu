@@ -191,7 +191,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 // the bytes in flight per SM, which is what covers the L2 latency, stay the same. The TMEM stride stays 256 columns.
 __global__ void __launch_bounds__(kThreadsTma, 1)
 gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
+            float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, uint32_t accumulate,
+            int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + kTileRegion);
@@ -283,6 +284,16 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 uint32_t v[32];
                 tmem_ld32(taddr + c0, v);               // a 16-column remainder reads 16 stale columns of the buffer: masked below
                 if (row < n_rows) {
+                    if (accumulate) {                   // C += A W^T (a residual add folded in): all 32 old values are requested before the first is used
+                        float old[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t m = m0 + c0 + j;
+                            old[j] = (c0 + j < bn && m < m_tok) ? __ldcg(C + (size_t)m * ldc + row) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(old[j] + __uint_as_float(v[j]));
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + c0 + j;
@@ -405,7 +416,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {        // arri
 // then two token atoms (2 x bn/2 x 128 B); three stages at bn = 256.
 __global__ void __launch_bounds__(kThreadsTma, 1)
 gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, int* status) {
+                 float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, uint32_t accumulate,
+                 int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // the same offset in both CTAs
     uint64_t* full = (uint64_t*)(smem + kTileRegion);
@@ -508,6 +520,16 @@ gemm_f16_tn_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 uint32_t v[32];
                 tmem_ld32(taddr + c0, v);
                 if (row < n_rows) {
+                    if (accumulate) {
+                        float old[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t m = m0 + c0 + j;
+                            old[j] = m < m_tok ? __ldcg(C + (size_t)m * ldc + row) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(old[j] + __uint_as_float(v[j]));
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t m = m0 + c0 + j;
@@ -958,7 +980,8 @@ unsigned pick_token_tile_pair(unsigned M, unsigned N, unsigned sms) {
 
 // The TMA-fed kernels over fp16 operands that are in place (or being written by the launch just before this one):
 // weights Wh [N][K], activations Ah [M][K].
-static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, cudaStream_t st) {
+static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, cudaStream_t st,
+                         bool accumulate = false) {
     CUtensorMap tmA, tmB;
     // Two SMs per tile (gemm_f16_tn_pair) where it measured faster: four or more waves of pair tiles. TM_GEMM_PAIR=0
     // keeps one SM per tile everywhere, TM_GEMM_PAIR=1 pairs wherever there are 256 weight rows.
@@ -986,7 +1009,7 @@ static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned 
         at[1].val.clusterDim.x = 2; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 2;
         if (cudaLaunchKernelEx(&cfg, gemm_f16_tn_pair, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn2,
-                               device_status_word()) != cudaSuccess)
+                               accumulate ? 1u : 0u, device_status_word()) != cudaSuccess)
             return check_launch("gemm_f16_tn_pair");
         note_launch();
         return check_launch("gemm_f16_tn_pair");
@@ -1009,7 +1032,7 @@ static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn,
-                           device_status_word()) != cudaSuccess)
+                           accumulate ? 1u : 0u, device_status_word()) != cudaSuccess)
         return check_launch("gemm_f16_tn");
     note_launch();
     return check_launch("gemm_f16_tn");
@@ -1036,6 +1059,17 @@ bool launch_weights_f16(const uint8_t* W, void* Wh_out, unsigned N, unsigned K, 
     }
     note_launch();
     return check_launch("weights_f16");
+}
+
+// Both operands already fp16 (weights from launch_weights_f16, activations written as fp16 by the kernel that made
+// them): no pre-pass and no workspace at all. accumulate: C += A W^T.
+bool launch_gemm_hh(const void* Ah, const void* Wh, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, bool accumulate, cudaStream_t st) {
+    if (!Ah || !Wh || !C) return fail("gemm: null pointer");
+    if (M == 0 || N == 0) return true;
+    if (ldc < N) return fail("gemm: ldc=%u is smaller than N=%u", ldc, N);
+    if (K == 0 || K % 8) return fail("gemm: K must be a multiple of 8");
+    if ((uintptr_t)Ah % 16 || (uintptr_t)C % 4 || (uintptr_t)Wh % 16) return fail("gemm: the fp16 operands must be 16-byte aligned");
+    return launch_tiles((const __half*)Wh, (const __half*)Ah, C, ldc, M, N, K, st, accumulate);
 }
 
 size_t gemm_f16w_workspace_bytes(unsigned M, unsigned K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }

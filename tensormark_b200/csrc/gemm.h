@@ -16,6 +16,7 @@ bool launch_gemm(const float* A, const uint8_t* W, float* C, unsigned ldc, unsig
 // For callers that keep an fp16 copy of static weights: the copy (exact fp32 value of every weight rounded once, as the
 // GEMM's own pre-pass writes it), and the GEMM against it, whose workspace only holds the rounded activations.
 bool launch_weights_f16(const uint8_t* W, void* Wh, unsigned N, unsigned K, unsigned dtype, cudaStream_t st);
+bool launch_gemm_hh(const void* Ah, const void* Wh, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, bool accumulate, cudaStream_t st);
 size_t gemm_f16w_workspace_bytes(unsigned M, unsigned K);
 bool launch_gemm_f16w(const float* A, const void* Wh, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K,
                       void* workspace, size_t workspace_bytes, cudaStream_t st);

@@ -29,6 +29,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <type_traits>
 #include <vector>
 
 namespace tmc {
@@ -46,12 +47,15 @@ __device__ __forceinline__ float wmax(float v) {
 }
 
 // out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * w, one CTA per token row (ll_rmsnorm, metal_llama.h:35-54).
+// OT = __half: the row goes straight into the next GEMM as its fp16 operand (the same value that GEMM's pre-pass would
+// make of the fp32 row: one rounding).
+template <typename OT>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                           float* __restrict__ out, uint32_t D, float eps) {
+                                                           OT* __restrict__ out, uint32_t D, float eps) {
     __shared__ float part[8];
     __shared__ float inv_s;
     const float* xr = x + (size_t)blockIdx.x * D;
-    float* o = out + (size_t)blockIdx.x * D;
+    OT* o = out + (size_t)blockIdx.x * D;
     float p = 0.f;
     for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i]; p = fmaf(v, v, p); }
     p = wsum(p);
@@ -64,7 +68,10 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
     }
     __syncthreads();
     const float inv = inv_s;
-    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) o[i] = xr[i] * inv * w[i];
+    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = xr[i] * inv * w[i];
+        if constexpr (sizeof(OT) == 2) o[i] = __float2half_rn(v); else o[i] = v;
+    }
 }
 
 // y[t][c] += bias[c] (ll_bias, metal_llama.h:420-426); y rows have stride ld.
@@ -133,9 +140,9 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
-template <int DH>
+template <int DH, typename OT>
 __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __restrict__ qkv, uint32_t ld, const float* __restrict__ kc,
-                                                              const float* __restrict__ vc, float* __restrict__ out, uint32_t QD,
+                                                              const float* __restrict__ vc, OT* __restrict__ out, uint32_t QD,
                                                               uint32_t T, uint32_t pos0, uint32_t ctx, uint32_t REP, float scale) {
     constexpr int RS = DH + 4;                                  // K and V rows in shared memory: stride 4 (mod 32), conflict-free fragments
     constexpr int D4 = DH / 4;
@@ -280,10 +287,12 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
         if (!live) continue;
         const uint32_t row = half ? r1 : r0, t = half ? tok1 : tok0;
         const float inv = 1.0f / (half ? l1 : l0);
-        float* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + 2 * ft;
+        OT* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + 2 * ft;
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-            *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+        for (int n = 0; n < NT; ++n) {
+            if constexpr (sizeof(OT) == 2) *reinterpret_cast<__half2*>(o + 8 * n) = __floats2half2_rn(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+            else *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+        }
     }
 }
 
@@ -315,6 +324,7 @@ struct Stack {
     std::vector<Layer> layers;
     float *x = nullptr, *h = nullptr, *qkv = nullptr, *ao = nullptr, *h2 = nullptr, *g = nullptr, *u = nullptr;
     float* gu = nullptr;                                        // resident form: gate|up of the batch, [T][2 F]
+    __half *hh = nullptr, *aoh = nullptr, *acth = nullptr;      // resident form: fp16 activations [T][D], [T][QD], [T][F]
     bool resident = false;                                      // the layers hold fp16 copies of their weights
     void* ws = nullptr;
     size_t ws_bytes = 0;
@@ -340,6 +350,7 @@ struct Stack {
     }
     void free_scratch() {
         for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u, &gu}) if (*p) { cudaFree(*p); *p = nullptr; }
+        for (__half** p : {&hh, &aoh, &acth}) if (*p) { cudaFree(*p); *p = nullptr; }
         if (ws) { cudaFree(ws); ws = nullptr; }
         cap_T = 0;
     }
@@ -363,43 +374,50 @@ bool ensure_scratch(Stack& c, int T) {
     c.free_scratch();
     auto mk = [&](size_t floats) { float* p = nullptr; if (cudaMalloc(&p, floats * 4) != cudaSuccess) { cudaGetLastError(); p = nullptr; } return p; };
     const size_t t = (size_t)T;
-    c.x = mk(t * c.D); c.h = mk(t * c.D); c.h2 = mk(t * c.D); c.qkv = mk(t * (c.QD + 2 * c.KVD)); c.ao = mk(t * c.QD);
-    c.g = mk(t * c.F);
-    if (c.resident) c.gu = mk(t * 2 * c.F); else c.u = mk(t * c.F);
-    size_t need = 0;
+    auto mkh = [&](size_t halves) { __half* p = nullptr; if (cudaMalloc(&p, halves * 2) != cudaSuccess) { cudaGetLastError(); p = nullptr; } return p; };
+    c.x = mk(t * c.D); c.qkv = mk(t * (c.QD + 2 * c.KVD));
+    bool ok;
     if (c.resident) {
-        need = gemm_f16w_workspace_bytes((unsigned)T, (unsigned)std::max(std::max(c.D, c.QD), c.F));
+        if ((c.F % 4) || (c.D % 8) || (c.QD % 8)) return fail("llama stack: row widths must be multiples of 8 (F of 4) for the fp16 activations");
+        c.gu = mk(t * 2 * c.F); c.hh = mkh(t * c.D); c.aoh = mkh(t * c.QD); c.acth = mkh(t * c.F);
+        ok = c.x && c.qkv && c.gu && c.hh && c.aoh && c.acth;
     } else {
+        c.h = mk(t * c.D); c.h2 = mk(t * c.D); c.ao = mk(t * c.QD); c.g = mk(t * c.F); c.u = mk(t * c.F);
+        size_t need = 0;
         for (auto nk : {std::pair<int, int>{c.QD, c.D}, {c.KVD, c.D}, {c.D, c.QD}, {c.F, c.D}, {c.D, c.F}})
             need = std::max(need, gemm_workspace_bytes((unsigned)T, (unsigned)nk.first, (unsigned)nk.second));
+        if (cudaMalloc(&c.ws, need) != cudaSuccess) { cudaGetLastError(); c.ws = nullptr; }
+        c.ws_bytes = need;
+        ok = c.x && c.qkv && c.h && c.h2 && c.ao && c.g && c.u && c.ws;
     }
-    if (cudaMalloc(&c.ws, need) != cudaSuccess) { cudaGetLastError(); c.ws = nullptr; }
-    c.ws_bytes = need;
-    if (!(c.x && c.h && c.h2 && c.qkv && c.ao && c.g && (c.resident ? c.gu : c.u) && c.ws)) { c.free_scratch(); return fail("llama stack: out of device memory for a %d-token batch", T); }
+    if (!ok) { c.free_scratch(); return fail("llama stack: out of device memory for a %d-token batch", T); }
     c.cap_T = T;
     return true;
 }
 
 template <int DH> constexpr size_t attn_smem() { return (size_t)(2 * 2 * 32 * (DH + 4)) * 4; }     // two tiles of K and V
-template <int DH>
+template <int DH, typename OT>
 bool attn_ready() {
     constexpr size_t smem = attn_smem<DH>();
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(prefill_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(prefill_attn_kernel<DH, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return fail("llama stack: cannot raise the attention kernel's shared memory limit");
         attr = true;
     }
     return true;
 }
 
-// act[t][f] = silu(gu[t][f]) * gu[t][F + f]: gate and up come out of ONE GEMM against the stacked gate|up rows
-__global__ void silu_mul_stacked_kernel(const float* __restrict__ gu, float* __restrict__ act, uint32_t F, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const size_t t = i / F, f = i % F;
-    const float g = gu[t * 2 * F + f], u = gu[t * 2 * F + F + f];
-    act[i] = g / (1.0f + expf(-g)) * u;
+// act[t][f] = silu(gu[t][f]) * gu[t][F + f], straight to fp16 (the down projection's operand): gate and up come out of
+// ONE GEMM against the stacked gate|up rows. Four columns per thread; F % 4 == 0.
+__global__ void silu_mul_stacked_half_kernel(const float* __restrict__ gu, __half* __restrict__ act, uint32_t F) {
+    const uint32_t t = blockIdx.y, f4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f4 * 4 >= F) return;
+    const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + 4 * f4);
+    const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + F + 4 * f4);
+    const __half2 a = __floats2half2_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    const __half2 b = __floats2half2_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+    *reinterpret_cast<uint2*>(act + (size_t)t * F + 4 * f4) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
 bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
@@ -410,13 +428,15 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     auto gemm = [&](const float* A, const uint8_t* W, float* Cm, unsigned ldc, unsigned N, unsigned K) {
         return launch_gemm(A, W, Cm, ldc, Tn, N, K, c.dtype, c.ws, c.ws_bytes, st);
     };
-    auto gemm_h = [&](const float* A, const void* Wh, float* Cm, unsigned ldc, unsigned N, unsigned K) {
-        return launch_gemm_f16w(A, Wh, Cm, ldc, Tn, N, K, c.ws, c.ws_bytes, st);
+    auto gemm_h = [&](const __half* Ah, const void* Wh, float* Cm, unsigned ldc, unsigned N, unsigned K, bool accumulate) {
+        return launch_gemm_hh(Ah, Wh, Cm, ldc, Tn, N, K, accumulate, st);
     };
     // 1. norm, q / k / v into one [T][QD + 2 KVD] buffer
-    rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms1, c.h, D, c.eps); note_launch();
+    if (c.resident) rmsnorm_rows_kernel<__half><<<Tn, 256, 0, st>>>(c.x, L.rms1, c.hh, D, c.eps);
+    else rmsnorm_rows_kernel<float><<<Tn, 256, 0, st>>>(c.x, L.rms1, c.h, D, c.eps);
+    note_launch();
     if (c.resident) {
-        if (!gemm_h(c.h, L.wqkv, c.qkv, ld, ld, D)) return false;                     // one GEMM against the stacked rows
+        if (!gemm_h(c.hh, L.wqkv, c.qkv, ld, ld, D, false)) return false;            // one GEMM against the stacked rows
     } else if (!gemm(c.h, L.q, c.qkv, ld, QD, D) || !gemm(c.h, L.k, c.qkv + QD, ld, KVD, D) || !gemm(c.h, L.v, c.qkv + QD + KVD, ld, KVD, D)) {
         return false;
     }
@@ -443,30 +463,35 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     // 3. causal attention of the batch over [0, pos]
     const unsigned BT = 64u / (unsigned)c.REP;
     const dim3 grid((Tn + BT - 1) / BT, (unsigned)c.KVH);
-    if (dh == 128) {
-        if (!attn_ready<128>()) return false;
-        prefill_attn_kernel<128><<<grid, 128, attn_smem<128>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
-    } else {
-        if (!attn_ready<64>()) return false;
-        prefill_attn_kernel<64><<<grid, 128, attn_smem<64>(), st>>>(c.qkv, ld, L.kc, L.vc, c.ao, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
-    }
+    auto attend = [&](auto dhc, auto* dst) -> bool {
+        constexpr int DHC = decltype(dhc)::value;
+        using OT = std::remove_pointer_t<decltype(dst)>;
+        if (!attn_ready<DHC, OT>()) return false;
+        prefill_attn_kernel<DHC, OT><<<grid, 128, attn_smem<DHC>(), st>>>(c.qkv, ld, L.kc, L.vc, dst, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+        return true;
+    };
+    using I128 = std::integral_constant<int, 128>; using I64 = std::integral_constant<int, 64>;
+    if (!(dh == 128 ? (c.resident ? attend(I128{}, c.aoh) : attend(I128{}, c.ao)) : (c.resident ? attend(I64{}, c.aoh) : attend(I64{}, c.ao)))) return false;
     note_launch();
     // 4. o + residual, norm, gate / up, silu * up, down + residual
-    if (!(c.resident ? gemm_h(c.ao, L.wo, c.h2, D, D, QD) : gemm(c.ao, L.o, c.h2, D, D, QD))) return false;
-    if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
-    rmsnorm_rows_kernel<<<Tn, 256, 0, st>>>(c.x, L.rms2, c.h, D, c.eps); note_launch();
     if (c.resident) {
-        if (!gemm_h(c.h, L.wgu, c.gu, 2 * F, 2 * F, D)) return false;
-        const size_t n = (size_t)Tn * F;
-        silu_mul_stacked_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(c.gu, c.g, F, n);
+        // activations travel as fp16 between the kernels that make them and the GEMMs that read them (one rounding, the
+        // one the GEMM's pre-pass would apply), and the residual adds are the GEMMs' own epilogues
+        if (!gemm_h(c.aoh, L.wo, c.x, D, D, QD, true)) return false;
+        rmsnorm_rows_kernel<__half><<<Tn, 256, 0, st>>>(c.x, L.rms2, c.hh, D, c.eps); note_launch();
+        if (!gemm_h(c.hh, L.wgu, c.gu, 2 * F, 2 * F, D, false)) return false;
+        silu_mul_stacked_half_kernel<<<dim3((F / 4 + 255) / 256, Tn), 256, 0, st>>>(c.gu, c.acth, F);
         note_launch();
-        if (!gemm_h(c.g, L.wdown, c.h2, D, D, F)) return false;
+        if (!gemm_h(c.acth, L.wdown, c.x, D, D, F, true)) return false;
     } else {
+        if (!gemm(c.ao, L.o, c.h2, D, D, QD)) return false;
+        if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
+        rmsnorm_rows_kernel<float><<<Tn, 256, 0, st>>>(c.x, L.rms2, c.h, D, c.eps); note_launch();
         if (!gemm(c.h, L.gate, c.g, F, F, D) || !gemm(c.h, L.up, c.u, F, F, D)) return false;
         if (!launch_silu_mul(c.g, c.u, Tn * F, st)) return false;
         if (!gemm(c.g, L.down, c.h2, D, D, F)) return false;
+        if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
     }
-    if (!launch_add(c.x, c.h2, Tn * D, st)) return false;
     return check_launch("llama stack layer");
 }
 

@@ -56,8 +56,23 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
     __shared__ float inv_s;
     const float* xr = x + (size_t)blockIdx.x * D;
     OT* o = out + (size_t)blockIdx.x * D;
+    // rows of up to 8192 values stay in registers between the two passes (16-byte loads, all requested at once)
+    constexpr int MAXV = 8;
+    const uint32_t n4 = D / 4;
+    const bool fits = (D % 4 == 0) && n4 <= 256u * MAXV;
+    float4 v[MAXV];
     float p = 0.f;
-    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) { const float v = xr[i]; p = fmaf(v, v, p); }
+    if (fits) {
+#pragma unroll
+        for (int u = 0; u < MAXV; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            v[u] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < MAXV; ++u) { p = fmaf(v[u].x, v[u].x, p); p = fmaf(v[u].y, v[u].y, p); p = fmaf(v[u].z, v[u].z, p); p = fmaf(v[u].w, v[u].w, p); }
+    } else {
+        for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) { const float t = xr[i]; p = fmaf(t, t, p); }
+    }
     p = wsum(p);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = p;
     __syncthreads();
@@ -68,9 +83,25 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
     }
     __syncthreads();
     const float inv = inv_s;
-    for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) {
-        const float v = xr[i] * inv * w[i];
-        if constexpr (sizeof(OT) == 2) o[i] = __float2half_rn(v); else o[i] = v;
+    if (fits) {
+#pragma unroll
+        for (int u = 0; u < MAXV; ++u) {
+            const uint32_t i = threadIdx.x + u * 256;
+            if (i >= n4) continue;
+            const float4 ww = reinterpret_cast<const float4*>(w)[i];
+            const float a0 = v[u].x * inv * ww.x, a1 = v[u].y * inv * ww.y, a2 = v[u].z * inv * ww.z, a3 = v[u].w * inv * ww.w;
+            if constexpr (sizeof(OT) == 2) {
+                const __half2 lo = __floats2half2_rn(a0, a1), hi = __floats2half2_rn(a2, a3);
+                reinterpret_cast<uint2*>(o)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            } else {
+                reinterpret_cast<float4*>(o)[i] = make_float4(a0, a1, a2, a3);
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < D; i += blockDim.x) {
+            const float t = xr[i] * inv * w[i];
+            if constexpr (sizeof(OT) == 2) o[i] = __float2half_rn(t); else o[i] = t;
+        }
     }
 }
 

@@ -338,6 +338,7 @@ public:
         if (tok < 0 || tok >= d_.V) throw std::invalid_argument("llama: token id out of range");
         if (seen >= d_.ctx) throw std::invalid_argument("llama: context is full");
         gpu_token_prologue();
+        if (seen < stack_rows_) stack_rows_ = seen;     // the decode lane writes K/V rows from here on: the layer stack's own rows beyond are stale
         const unsigned t = (unsigned)tok;
         if (!tm_cuda_tok_upload(SLOT_TOK, 0, &t, sizeof t)) throw std::runtime_error("cuda: token upload failed");
         if (!tm_cuda_tok_begin()) throw std::runtime_error("cuda: token begin failed");
@@ -365,6 +366,7 @@ public:
         if (seen + n > d_.ctx) throw std::invalid_argument("llama: chain exceeds context");
         if (chain_n_) throw std::runtime_error("llama: chain already running");
         gpu_token_prologue();
+        if (seen < stack_rows_) stack_rows_ = seen;     // the decode lane writes K/V rows from here on: the layer stack's own rows beyond are stale
         const unsigned cap = (unsigned)d_.ctx + 1;
         std::vector<unsigned> toks((size_t)cap, 0xFFFFFFFFu);
         toks[0] = (unsigned)first;
@@ -394,6 +396,7 @@ public:
         if (seen + n > d_.ctx) throw std::invalid_argument("llama: prompt exceeds context");
         if (chain_n_) throw std::runtime_error("llama: chain already running");
         gpu_token_prologue();
+        if (seen < stack_rows_) stack_rows_ = seen;     // the decode lane writes K/V rows from here on: the layer stack's own rows beyond are stale
         const unsigned cap = (unsigned)d_.ctx + 1;
         std::vector<unsigned> t((size_t)cap, 0xFFFFFFFFu);
         for (int i = 0; i < n; ++i) {
@@ -422,6 +425,9 @@ public:
         if (chain_n_) throw std::runtime_error("llama: chain already running");
         gpu_token_prologue();
         ensure_stack();
+        // The stack's caches hold the rows the stack itself computed ([0, stack_rows_)). After tokens that went through the
+        // decode lane its rows are behind: such a prompt continues token by token.
+        if (seen > stack_rows_) return gpu_feed(toks, n);
         const int m = n - 1;
         const size_t D = (size_t)d_.D, row_bytes = tm_cuda_weight_bytes(d_.dt_embed, 1, D);
         std::vector<float> x((size_t)m * D);
@@ -435,6 +441,7 @@ public:
             if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, m))
                 throw std::runtime_error(std::string("cuda: K/V hand-over failed: ") + tm_cuda_last_error());
         seen += m;
+        stack_rows_ = seen;
         return gpu_feed(toks + m, 1);
     }
     double last_prefill_gpu_ms() const { return tm_cuda_llama_prefill_gpu_ms(); }
@@ -474,21 +481,17 @@ public:
     }
 
 private:
-    // The layer stack of this model, with the fp32 host K/V arrays its contract asks the caller to own.
+    // The layer stack of this model. Its K/V rows stay on the device (null kc / vc: tm_cuda_llama_kv_to_slots hands them to
+    // the decode lane), which spares a prompt the copy of every row to host arrays nobody reads.
     void ensure_stack() {
         if (stack_) return;
-        const size_t kv = (size_t)d_.KVH * d_.ctx * d_.dh;
-        host_kc_.assign((size_t)d_.L, std::vector<float>());
-        host_vc_.assign((size_t)d_.L, std::vector<float>());
         stack_layers_.resize((size_t)d_.L);
         for (int l = 0; l < d_.L; ++l) {
-            host_kc_[(size_t)l].assign(kv, 0.f); host_vc_[(size_t)l].assign(kv, 0.f);
             const CudaLlamaLayer& s = layers_[(size_t)l];
             tm_llama_gpu_layer& g = stack_layers_[(size_t)l];
             g = tm_llama_gpu_layer{};
             g.q = s.q; g.k = s.k; g.v = s.v; g.o = s.o; g.gate = s.gate; g.up = s.up; g.down = s.down;
             g.rms1 = s.rms1; g.rms2 = s.rms2;
-            g.kc = host_kc_[(size_t)l].data(); g.vc = host_vc_[(size_t)l].data();
         }
         tm_llama_gpu_desc gd{};
         gd.L = d_.L; gd.D = d_.D; gd.H = d_.H; gd.KVH = d_.KVH; gd.dh = d_.dh; gd.F = d_.F; gd.ctx = d_.ctx;
@@ -536,7 +539,7 @@ private:
     int graph_ = -1, sgraph_ = -1, chain_n_ = 0, chain_seen0_ = 0;
     void* stack_ = nullptr;
     std::vector<tm_llama_gpu_layer> stack_layers_;
-    std::vector<std::vector<float>> host_kc_, host_vc_;
+    int stack_rows_ = 0;                                       // positions [0, stack_rows_) of the stack's K/V caches match this sequence
     float inv_temp_ = 0.f, sg_inv_temp_ = 0.f;                 // > 0 only while a sampled chain is being encoded
     // Peer-gather chain: true = the LM head's rows are gathered on every rank before the choice (every rank then holds
     // all logits of the last step), false = only the ranks' (value, index) keys travel. TM_CUDA_GATHER_LOGITS=1 selects

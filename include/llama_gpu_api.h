@@ -18,6 +18,9 @@
  * device copies and writes the rows it computes back into the caller's arrays (prefill: before it returns;
  * begin/wait_layer: layer l's rows are there when wait_layer(l) returns 1). Rows [0, pos0) are read from the
  * caller's arrays at the start of every call with pos0 > 0, as unified memory would show them.
+ * Not in the reference: a layer whose kc and vc are both NULL keeps its rows on the device only (nothing is copied
+ * either way; a call with pos0 > 0 continues from the rows earlier calls left there); tm_cuda_llama_kv_to_slots
+ * hands them to the decode lane.
  * Constraints: dh even (64 or 128 for the attention kernel), H % KVH == 0, T >= 2, pos0 + T <= ctx; blocks are Q4_0
  * unless the *_create_dt form names another block format.
  * Errors: create returns NULL, the int entries return 0, and tm_cuda_last_error() names the reason. */

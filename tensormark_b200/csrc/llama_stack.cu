@@ -487,9 +487,11 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     note_launch();
     cudaEventRecord(L.kv_ready, st);
     cudaStreamWaitEvent(c.copy, L.kv_ready, 0);
-    const size_t pitch = (size_t)c.ctx * dh * 4, width = (size_t)T * dh * 4, first = (size_t)pos0 * dh;
-    cudaMemcpy2DAsync(L.kc_host + first, pitch, L.kc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
-    cudaMemcpy2DAsync(L.vc_host + first, pitch, L.vc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
+    if (L.kc_host) {
+        const size_t pitch = (size_t)c.ctx * dh * 4, width = (size_t)T * dh * 4, first = (size_t)pos0 * dh;
+        cudaMemcpy2DAsync(L.kc_host + first, pitch, L.kc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
+        cudaMemcpy2DAsync(L.vc_host + first, pitch, L.vc + first, pitch, width, (size_t)c.KVH, cudaMemcpyDeviceToHost, c.copy);
+    }
     cudaEventRecord(L.kv_done, c.copy);
     // 3. causal attention of the batch over [0, pos]
     const unsigned BT = 64u / (unsigned)c.REP;
@@ -539,6 +541,7 @@ bool enqueue(Stack& c, const float* x, int T, int pos0) {
         // what unified memory would show the reference's GPU: the caller's earlier rows, whoever wrote them
         const size_t pitch = (size_t)c.ctx * c.dh * 4, width = (size_t)pos0 * c.dh * 4;
         for (Layer& L : c.layers) {
+            if (!L.kc_host) continue;                               // device-only caches: the earlier rows are where the stack left them
             cudaMemcpy2DAsync(L.kc, pitch, L.kc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
             cudaMemcpy2DAsync(L.vc, pitch, L.vc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
         }
@@ -582,7 +585,9 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
     for (int l = 0; l < c->L; ++l) {
         const tm_llama_gpu_layer& src = d->layers[l];
         Layer& L = c->layers[(size_t)l];
-        if (!src.q || !src.k || !src.v || !src.o || !src.gate || !src.up || !src.down || !src.rms1 || !src.rms2 || !src.kc || !src.vc) {
+        // kc and vc both null: the K/V rows stay on the device (tm_cuda_llama_kv_to_slots hands them to the decode lane);
+        // the reference, on unified memory, always has the caller's arrays
+        if (!src.q || !src.k || !src.v || !src.o || !src.gate || !src.up || !src.down || !src.rms1 || !src.rms2 || (!src.kc != !src.vc)) {
             fail("llama stack: layer %d has a null pointer", l); return nullptr;
         }
         auto reg = [&](const void* p, int rows, int cols) -> const uint8_t* {
@@ -604,10 +609,12 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
         }
         cudaMemsetAsync(L.kc, 0, cache_floats * 4, s.stream); cudaMemsetAsync(L.vc, 0, cache_floats * 4, s.stream);
         L.kc_host = src.kc; L.vc_host = src.vc;
-        // page-locking the caller's arrays makes the row copies asynchronous; where it is refused they are staged
-        L.pinned_k = cudaHostRegister(L.kc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
-        L.pinned_v = cudaHostRegister(L.vc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
-        cudaGetLastError();
+        if (L.kc_host) {
+            // page-locking the caller's arrays makes the row copies asynchronous; where it is refused they are staged
+            L.pinned_k = cudaHostRegister(L.kc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
+            L.pinned_v = cudaHostRegister(L.vc_host, cache_floats * 4, cudaHostRegisterDefault) == cudaSuccess;
+            cudaGetLastError();
+        }
         if (cudaEventCreateWithFlags(&L.kv_ready, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&L.kv_done, cudaEventDisableTiming) != cudaSuccess) { check_launch("llama stack: events"); return nullptr; }
     }

@@ -26,7 +26,7 @@ class Stack:
     """The layer stack of a model made by synth.make_llama. Owns the host K/V arrays the contract asks the caller for:
     kc[l], vc[l] are float32 [KVH, ctx, dh]."""
 
-    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True, biases: dict | None = None):
+    def __init__(self, cfg: dict, weights: dict, shared_mapping: bool = True, biases: dict | None = None, device_only: bool = False):
         self.L = lib.load()
         self.cfg, self.weights = cfg, weights
         n = cfg["L"]
@@ -45,8 +45,9 @@ class Stack:
                     a = np.ascontiguousarray(biases[f"l{l}.{name}"], np.float32)
                     self._keep.append(a)
                     setattr(s, name, a.ctypes.data_as(_f32p))
-            s.kc = self.kc[l].ctypes.data_as(_f32p)
-            s.vc = self.vc[l].ctypes.data_as(_f32p)
+            if not device_only:                         # else: NULL, the K/V rows stay on the device
+                s.kc = self.kc[l].ctypes.data_as(_f32p)
+                s.vc = self.vc[l].ctypes.data_as(_f32p)
         d = GpuDesc()
         for k in ("L", "D", "H", "KVH", "dh", "F", "ctx"):
             setattr(d, k, cfg[k])

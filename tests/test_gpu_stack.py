@@ -88,6 +88,41 @@ def test_resident_fp16_weights_equal_per_call_conversion(cuda, orc, cfg, monkeyp
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
+def test_device_only_caches_and_prompt_after_decode_steps(cuda, orc):
+    """kc = vc = NULL keeps the K/V rows on the device: same residual stream, chunks continue from the device rows. And a
+    prompt that follows tokens of the decode lane (whose rows the stack does not have) must still give the decode lane's
+    answer: the chain driver then feeds it token by token."""
+    cfg = GQA128
+    w = synth.make_llama(cfg, seed=25)
+    toks = synth.make_tokens(300, cfg["V"], seed=26)
+    x = _embed(orc, cfg, w, toks)
+    ref = stack.Stack(cfg, w)
+    want = ref.prefill(x, 0)
+    ref.close()
+    st = stack.Stack(cfg, w, device_only=True)
+    a = st.prefill(x[:200], 0)
+    b = st.prefill(x[200:], 200)
+    st.close()
+    assert np.array_equal(a.view(np.uint32), want[:200].view(np.uint32))
+    _close(b, want[200:], "second chunk on device rows", STREAM_BAR)
+    cfg2 = dict(synth.TINY_CHAIN)
+    w2 = synth.make_llama(cfg2, seed=5)
+    t2 = synth.make_tokens(40, cfg2["V"], seed=33).astype(np.int32)
+    one = chain.Chain(cfg2, w2)
+    nxt_one = one.feed(t2)
+    lg_one = one.logits()
+    one.close()
+    two = chain.Chain(cfg2, w2)
+    two.prefill(t2[:20])                                  # through the stack
+    two.feed(t2[20:25])                                   # decode lane: the stack's caches do not see these rows
+    nxt_two = two.prefill(t2[25:])                        # must not use the stack's stale rows
+    lg_two = two.logits()
+    two.close()
+    scale = max(1.0, float(np.abs(lg_one).max()))
+    assert float(np.abs(lg_one - lg_two).max()) <= 2e-3 * scale
+    assert nxt_one == nxt_two or np.sort(lg_one)[-1] - np.sort(lg_one)[-2] <= 2e-3 * scale
+
+
 def test_chunked_prefill_and_wait_layer(cuda, orc):
     cfg = GQA128
     w = synth.make_llama(cfg, seed=23)

@@ -435,7 +435,9 @@ public:
             if (toks[i] < 0 || toks[i] >= d_.V) throw std::invalid_argument("llama: token id out of range");
         for (int i = 0; i < m; ++i)
             tmq::dequantize_row(d_.dt_embed, (const uint8_t*)d_.embed + (size_t)toks[i] * row_bytes, x.data() + (size_t)i * D, D);
-        if (!tm_cuda_llama_prefill(stack_, x.data(), m, seen))
+        // begin + end instead of prefill: the residual stream after the last layer is of no use here (the prompt's last
+        // token goes through the decode lane), so it is not copied back
+        if (!tm_cuda_llama_prefill_begin(stack_, x.data(), m, seen) || !tm_cuda_llama_prefill_end())
             throw std::runtime_error(std::string("cuda: layer stack prefill failed: ") + tm_cuda_last_error());
         for (int l = 0; l < d_.L; ++l)
             if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, m))
@@ -446,9 +448,11 @@ public:
     }
     double last_prefill_gpu_ms() const { return tm_cuda_llama_prefill_gpu_ms(); }
     // Creates the layer stack ahead of the first gpu_prefill (it is otherwise created by it).
-    void gpu_prefill_prepare() {
+    void gpu_prefill_prepare(int max_tokens = 0) {
         gpu_token_prologue();
         ensure_stack();
+        if (max_tokens >= 3 && !tm_cuda_llama_reserve(stack_, max_tokens - 1))
+            throw std::runtime_error(std::string("cuda: layer stack buffers: ") + tm_cuda_last_error());
     }
 
     // Chosen token i as soon as it has landed, -1 while pending.

@@ -50,6 +50,8 @@ int tm_cuda_llama_prefill_begin(void* h, const float* x, int T, int pos0);     /
 int tm_cuda_llama_prefill_wait_layer(int l);                                   /* layer l's K/V rows are in the caller's arrays */
 int tm_cuda_llama_prefill_end(void);
 double tm_cuda_llama_prefill_gpu_ms(void);                                     /* GPU time of the last finished prefill */
+/* Not in the reference: the batch buffers for prompts of up to T tokens now instead of inside the first prefill. */
+int tm_cuda_llama_reserve(void* h, int T);
 void tm_cuda_llama_destroy(void* h);
 
 void* tm_metal_llama_create(const tm_llama_gpu_desc* d);

@@ -37,7 +37,7 @@ def load() -> C.CDLL:
         L.tmchain_logit_rows.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
         L.tmchain_logit_rows.restype = None
         L.tmchain_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
-        L.tmchain_prefill_prepare.argtypes = [C.c_void_p]
+        L.tmchain_prefill_prepare.argtypes = [C.c_void_p, C.c_int]
         L.tmchain_prefill_gpu_ms.argtypes = [C.c_void_p]
         L.tmchain_prefill_gpu_ms.restype = C.c_double
         _lib = L
@@ -160,9 +160,9 @@ class Chain:
         self._check(nxt >= 0)
         return nxt
 
-    def prefill_prepare(self) -> None:
+    def prefill_prepare(self, max_tokens: int = 0) -> None:
         """Create the layer stack ahead of the first prefill (device K/V caches, page-locked host arrays)."""
-        self._check(self.L.tmchain_prefill_prepare(self.h))
+        self._check(self.L.tmchain_prefill_prepare(self.h, int(max_tokens)))
 
     def prefill_gpu_ms(self) -> float:
         return float(self.L.tmchain_prefill_gpu_ms(self.h))

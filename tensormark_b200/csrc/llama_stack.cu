@@ -710,6 +710,12 @@ int tm_cuda_llama_prefill_end(void) {
 
 double tm_cuda_llama_prefill_gpu_ms(void) { return g_gpu_ms; }
 
+int tm_cuda_llama_reserve(void* h, int T) {
+    Stack* c = static_cast<Stack*>(h);
+    if (!c || T < 2 || T > c->ctx) { fail("llama stack: cannot reserve buffers for %d tokens", T); return 0; }
+    return ensure_scratch(*c, T) ? 1 : 0;
+}
+
 int tm_cuda_llama_prefill(void* h, float* x, int T, int pos0) {
     Stack* c = static_cast<Stack*>(h);
     if (!c) { fail("llama stack: null handle"); return 0; }

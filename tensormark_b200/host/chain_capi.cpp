@@ -120,8 +120,8 @@ TMCHAIN_API int tmchain_prefill(void* p, const int* toks, int n) {
     try { return static_cast<Holder*>(p)->m->gpu_prefill(toks, n); }
     catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
-TMCHAIN_API int tmchain_prefill_prepare(void* p) {
-    try { static_cast<Holder*>(p)->m->gpu_prefill_prepare(); return 1; }
+TMCHAIN_API int tmchain_prefill_prepare(void* p, int max_tokens) {
+    try { static_cast<Holder*>(p)->m->gpu_prefill_prepare(max_tokens); return 1; }
     catch (const std::exception& e) { g_err = e.what(); return 0; }
 }
 TMCHAIN_API double tmchain_prefill_gpu_ms(void* p) { return static_cast<Holder*>(p)->m->last_prefill_gpu_ms(); }

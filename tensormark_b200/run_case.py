@@ -90,7 +90,7 @@ def measure_chain(L, torch, cfg: dict, w: dict, prompt_n: int, steps: int, rank:
     t0 = time.perf_counter()
     prefill_gpu_ms = None
     if prefill == "stack" and prompt_n >= 3:
-        m.prefill_prepare()                                # one-time set-up (device caches, page-locked host arrays) is not prompt time
+        m.prefill_prepare(prompt_n)                        # one-time set-up (device caches, fp16 weight copies, batch buffers) is not prompt time
         t0 = time.perf_counter()
         nxt = m.prefill(prompt)                            # the batched layer stack (tensor-core GEMMs)
         prefill_gpu_ms = m.prefill_gpu_ms()

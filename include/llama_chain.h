@@ -429,15 +429,12 @@ public:
         // decode lane its rows are behind: such a prompt continues token by token.
         if (seen > stack_rows_) return gpu_feed(toks, n);
         const int m = n - 1;
-        const size_t D = (size_t)d_.D, row_bytes = tm_cuda_weight_bytes(d_.dt_embed, 1, D);
-        std::vector<float> x((size_t)m * D);
         for (int i = 0; i < n; ++i)
             if (toks[i] < 0 || toks[i] >= d_.V) throw std::invalid_argument("llama: token id out of range");
-        for (int i = 0; i < m; ++i)
-            tmq::dequantize_row(d_.dt_embed, (const uint8_t*)d_.embed + (size_t)toks[i] * row_bytes, x.data() + (size_t)i * D, D);
-        // begin + end instead of prefill: the residual stream after the last layer is of no use here (the prompt's last
-        // token goes through the decode lane), so it is not copied back
-        if (!tm_cuda_llama_prefill_begin(stack_, x.data(), m, seen) || !tm_cuda_llama_prefill_end())
+        // The embedding rows are gathered on the device from the table the decode lane has registered, and the residual
+        // stream after the last layer is of no use here (the prompt's last token goes through the decode lane), so
+        // nothing but the token ids crosses the bus.
+        if (!tm_cuda_llama_prefill_begin_tokens(stack_, toks, m, seen, embed_.id, embed_.woff, d_.V, d_.dt_embed) || !tm_cuda_llama_prefill_end())
             throw std::runtime_error(std::string("cuda: layer stack prefill failed: ") + tm_cuda_last_error());
         for (int l = 0; l < d_.L; ++l)
             if (!tm_cuda_llama_kv_to_slots(stack_, l, SLOT_KC + l, SLOT_VC + l, seen, m))

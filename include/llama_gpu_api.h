@@ -52,6 +52,10 @@ int tm_cuda_llama_prefill_end(void);
 double tm_cuda_llama_prefill_gpu_ms(void);                                     /* GPU time of the last finished prefill */
 /* Not in the reference: the batch buffers for prompts of up to T tokens now instead of inside the first prefill. */
 int tm_cuda_llama_reserve(void* h, int T);
+/* Not in the reference: prefill_begin whose residual stream is gathered on the device - row toks[t] of the
+ * block-quantized embedding table registered with the decode lane as (wid, woff), `vocab` rows of D values in block
+ * format `dtype`, dequantized exactly - instead of uploaded from host rows. */
+int tm_cuda_llama_prefill_begin_tokens(void* h, const int* toks, int T, int pos0, int wid, unsigned long long woff, int vocab, unsigned dtype);
 void tm_cuda_llama_destroy(void* h);
 
 void* tm_metal_llama_create(const tm_llama_gpu_desc* d);

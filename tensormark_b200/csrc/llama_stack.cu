@@ -18,6 +18,7 @@
 #include "cuda_shim.h"
 #include "llama_gpu_api.h"
 #include "common.cuh"
+#include "qdecode.cuh"
 #include "gemm.h"
 #include "glue.h"
 #include "state.h"
@@ -528,15 +529,38 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     return check_launch("llama stack layer");
 }
 
-// Enqueue the whole batch: x up, rows [0, pos0) of the caches up, every layer.
-bool enqueue(Stack& c, const float* x, int T, int pos0) {
+// x[t] = row toks[t] of a block-quantized embedding table, dequantized exactly (the decode lane's embed op for a batch)
+__global__ void embed_rows_kernel(const int* __restrict__ toks, const uint8_t* __restrict__ W, float* __restrict__ x, uint32_t D,
+                                  uint32_t row_bytes, unsigned dtype) {
+    const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (k >= D) return;
+    x[(size_t)t * D + k] = decode_weight_dt(dtype, W + (size_t)toks[t] * row_bytes, k);
+}
+
+// Where a batch's residual stream comes from: the caller's host rows, or rows of an embedding table on the device.
+struct Source { const float* x = nullptr; const int* toks = nullptr; const uint8_t* table = nullptr; unsigned dtype = 0; int vocab = 0; };
+
+// Enqueue the whole batch: x up (or gathered), rows [0, pos0) of the caches up, every layer.
+bool enqueue(Stack& c, const Source& src, int T, int pos0) {
     State& s = state();
     if (T < 2 || pos0 < 0 || pos0 + T > c.ctx) return fail("llama stack: batch of %d tokens at position %d does not fit (T >= 2, context %d)", T, pos0, c.ctx);
-    if (!x) return fail("llama stack: null activations");
+    if (!src.x && !(src.toks && src.table)) return fail("llama stack: null activations");
     if ((size_t)T * (size_t)c.F > 0xffffffffull) return fail("llama stack: batch too long");
     if (!ensure_scratch(c, T)) return false;
     cudaEventRecord(c.t0, s.stream);
-    if (cudaMemcpyAsync(c.x, x, (size_t)T * c.D * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("llama stack: x upload");
+    if (src.x) {
+        if (cudaMemcpyAsync(c.x, src.x, (size_t)T * c.D * 4, cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("llama stack: x upload");
+    } else {
+        for (int i = 0; i < T; ++i)
+            if (src.toks[i] < 0 || src.toks[i] >= src.vocab) return fail("llama stack: token %d is outside the table of %d rows", src.toks[i], src.vocab);
+        // the token ids ride in the tail of the qkv buffer's first row block until the first layer overwrites it
+        int* dtoks = reinterpret_cast<int*>(c.qkv);
+        if (cudaMemcpyAsync(dtoks, src.toks, (size_t)T * sizeof(int), cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return check_launch("llama stack: token upload");
+        const unsigned be = block_elems(src.dtype);
+        const uint32_t row_bytes = ((uint32_t)c.D / be) * block_bytes(src.dtype);
+        embed_rows_kernel<<<dim3(((unsigned)c.D + 255) / 256, (unsigned)T), 256, 0, s.stream>>>(dtoks, src.table, c.x, (uint32_t)c.D, row_bytes, src.dtype);
+        note_launch();
+    }
     if (pos0 > 0) {
         // what unified memory would show the reference's GPU: the caller's earlier rows, whoever wrote them
         const size_t pitch = (size_t)c.ctx * c.dh * 4, width = (size_t)pos0 * c.dh * 4;
@@ -682,7 +706,24 @@ int tm_cuda_llama_prefill_begin(void* h, const float* x, int T, int pos0) {
     Stack* c = static_cast<Stack*>(h);
     if (!c) { fail("llama stack: null handle"); return 0; }
     if (g_live.n) (void)tm_cuda_llama_prefill_end();               // drain an unfinished one, best effort (metal_llama.h:971)
-    if (!enqueue(*c, x, T, pos0)) return 0;
+    Source src;
+    src.x = x;
+    if (!enqueue(*c, src, T, pos0)) return 0;
+    g_live.c = c; g_live.n = c->L; g_live.failed = false;
+    return 1;
+}
+
+int tm_cuda_llama_prefill_begin_tokens(void* h, const int* toks, int T, int pos0, int wid, unsigned long long woff, int vocab, unsigned dtype) {
+    Stack* c = static_cast<Stack*>(h);
+    if (!c || !toks) { fail("llama stack: null handle or tokens"); return 0; }
+    const unsigned be = block_elems(dtype);
+    if (!be || dtype == DT_F16 || dtype == DT_BF16 || c->D % (int)be || vocab <= 0) { fail("llama stack: embedding table of dtype %u does not fit rows of %d", dtype, c->D); return 0; }
+    Source src;
+    src.toks = toks; src.dtype = dtype; src.vocab = vocab;
+    src.table = lane_weight_ptr(wid, woff, weight_bytes(dtype, (size_t)vocab, (size_t)c->D));
+    if (!src.table) return 0;
+    if (g_live.n) (void)tm_cuda_llama_prefill_end();
+    if (!enqueue(*c, src, T, pos0)) return 0;
     g_live.c = c; g_live.n = c->L; g_live.failed = false;
     return 1;
 }

@@ -91,6 +91,7 @@ SIGNATURES = {
     "tm_cuda_llama_prefill_end": (C.c_int, []),
     "tm_cuda_llama_prefill_gpu_ms": (C.c_double, []),
     "tm_cuda_llama_reserve": (C.c_int, [_vp, C.c_int]),
+    "tm_cuda_llama_prefill_begin_tokens": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_ulonglong, C.c_int, _u]),
     "tm_cuda_llama_destroy": (None, [_vp]),
     "tm_cuda_llama_kv_to_slots": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tm_cuda_tok_qkv_post_at": (None, [C.c_int, C.c_int, C.c_int, _u, _u, _u, _u, C.c_float, C.c_int]),

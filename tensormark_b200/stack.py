@@ -71,6 +71,19 @@ class Stack:
             raise RuntimeError(lib.last_error())
         return x
 
+    def begin_tokens(self, toks: np.ndarray, pos0: int) -> None:
+        """prefill_begin whose residual stream is gathered on the device from the model's embedding table."""
+        w = self.weights["embed"]
+        woff = C.c_uint64(0)
+        blob = self.weights["blob"]
+        wid = self.L.tm_cuda_tok_wbuf(w.ctypes.data, w.nbytes, blob.ctypes.data, blob.nbytes, 1, C.byref(woff))
+        if wid < 0:
+            raise RuntimeError(lib.last_error())
+        self._toks = np.ascontiguousarray(toks, np.int32)
+        if not self.L.tm_cuda_llama_prefill_begin_tokens(self.h, self._toks.ctypes.data, self._toks.size, pos0, wid, woff.value,
+                                                         self.cfg["V"], self.cfg["dt_embed"]):
+            raise RuntimeError(lib.last_error())
+
     def begin(self, x: np.ndarray, pos0: int) -> None:
         self._x_in = np.ascontiguousarray(x, np.float32)
         if not self.L.tm_cuda_llama_prefill_begin(self.h, self._x_in.ctypes.data, self._x_in.shape[0], pos0):

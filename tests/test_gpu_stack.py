@@ -123,6 +123,28 @@ def test_device_only_caches_and_prompt_after_decode_steps(cuda, orc):
     assert nxt_one == nxt_two or np.sort(lg_one)[-1] - np.sort(lg_one)[-2] <= 2e-3 * scale
 
 
+def test_residual_stream_gathered_on_the_device(cuda, orc):
+    """prefill_begin_tokens embeds the tokens on the device (rows of the block-quantized table, dequantized exactly): the
+    K/V rows of every layer must equal those of the same batch uploaded as host rows, bit for bit."""
+    cfg = GQA128
+    w = synth.make_llama(cfg, seed=27)
+    toks = synth.make_tokens(150, cfg["V"], seed=28)
+    a = stack.Stack(cfg, w)
+    a.prefill(_embed(orc, cfg, w, toks), 0)
+    b = stack.Stack(cfg, w)
+    b.begin_tokens(toks, 0)
+    assert b.end(), lib.last_error()
+    for l in range(cfg["L"]):
+        assert np.array_equal(a.kc[l].view(np.uint32), b.kc[l].view(np.uint32)), l
+        assert np.array_equal(a.vc[l].view(np.uint32), b.vc[l].view(np.uint32)), l
+    bad = toks.copy()
+    bad[3] = cfg["V"]
+    with pytest.raises(RuntimeError):
+        b.begin_tokens(bad, 0)
+    a.close()
+    b.close()
+
+
 def test_chunked_prefill_and_wait_layer(cuda, orc):
     cfg = GQA128
     w = synth.make_llama(cfg, seed=23)

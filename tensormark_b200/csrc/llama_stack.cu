@@ -116,7 +116,9 @@ __global__ void bias_rows_kernel(float* __restrict__ y, const float* __restrict_
 
 // For every token t of the batch (position pos0 + t): rotate q in place, rotate k into the K cache row, copy v into the
 // V cache row (ll_rope + ll_kv_append, metal_llama.h:61-87; pairs (j, j + dh/2), angles from the shared table).
+// kh / vh (both or neither): fp16 copies of the same cache rows, the operands of prefill_attn_h_kernel.
 __global__ void rope_append_kernel(float* __restrict__ qkv, uint32_t ld, float* __restrict__ kc, float* __restrict__ vc,
+                                   __half* __restrict__ kh, __half* __restrict__ vh,
                                    uint32_t H, uint32_t KVH, uint32_t dh, uint32_t ctx, uint32_t pos0, uint32_t T,
                                    const float2* __restrict__ tbl, uint32_t tbl_n) {
     const uint32_t half = dh / 2, per_tok = (H + KVH) * half + KVH * dh;
@@ -133,12 +135,15 @@ __global__ void rope_append_kernel(float* __restrict__ qkv, uint32_t ld, float* 
         const float ra = a * cs.x - b * cs.y, rb = b * cs.x + a * cs.y;
         if (h < H) { r[j] = ra; r[j + half] = rb; }
         else {
-            float* dst = kc + ((size_t)(h - H) * ctx + pos) * dh;
-            dst[j] = ra; dst[j + half] = rb;
+            const size_t at = ((size_t)(h - H) * ctx + pos) * dh;
+            kc[at + j] = ra; kc[at + j + half] = rb;
+            if (kh) { kh[at + j] = __float2half_rn(ra); kh[at + j + half] = __float2half_rn(rb); }
         }
     } else {
         const uint32_t i = e - (H + KVH) * half, kv = i / dh, l = i % dh;
-        vc[((size_t)kv * ctx + pos) * dh + l] = row[(size_t)(H + KVH) * dh + i];
+        const float v = row[(size_t)(H + KVH) * dh + i];
+        vc[((size_t)kv * ctx + pos) * dh + l] = v;
+        if (vh) vh[((size_t)kv * ctx + pos) * dh + l] = __float2half_rn(v);
     }
 }
 
@@ -328,6 +333,194 @@ __global__ void __launch_bounds__(128, 3) prefill_attn_kernel(const float* __res
     }
 }
 
+// D += A (16x16, row) * B (16x8, col), fp16 operands, fp32 accumulate.
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// four 8x8 fp16 matrices, row addresses from lanes 8 i .. 8 i + 7; thread (g, t) gets [g][2t, 2t + 1] of each
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+}
+// the same, transposed: thread (g, t) gets [2t][g] and [2t + 1][g]
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const __half* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// The same attention over fp16 copies of the cache rows (rope_append_kernel writes them beside the fp32 rows): rows,
+// warps and softmax as in prefill_attn_kernel, but both products are m16n8k16 fp16 MMAs with fp32 accumulation - half
+// the MMAs per key tile - and the B fragments come out of shared memory by ldmatrix, four 8x8 blocks per instruction
+// (K as stored, V transposed), instead of two 32-bit loads per MMA; the tiles need no rounding pass after the copy.
+// q (pre-scaled), k, v and the probabilities carry fp16's 10 mantissa bits, as tf32 does; what fp16 lacks is range, and
+// a cache value beyond 65504 becomes inf here as it does in the decode lane's fp16 K/V slots. Scores, softmax
+// statistics and the output stay fp32. Three 32-key tiles of K and V ride a cp.async ring: one barrier per tile.
+template <int DH, typename OT>
+__global__ void __launch_bounds__(128, 3) prefill_attn_h_kernel(const float* __restrict__ qkv, uint32_t ld, const __half* __restrict__ kh,
+                                                                const __half* __restrict__ vh, OT* __restrict__ out, uint32_t QD,
+                                                                uint32_t T, uint32_t pos0, uint32_t ctx, uint32_t REP, float scale) {
+    constexpr int RSH = DH + 8;                                 // halves per row in shared memory: 16-byte rows, conflict-free ldmatrix
+    constexpr int KS = DH / 16;                                 // k-steps of q k^T
+    constexpr int NT = DH / 8;                                  // output n-tiles
+    constexpr int NS = 3;                                       // ring depth
+    constexpr int C8 = DH / 8;                                  // 16-byte pieces per row
+    constexpr int PER = 32 * C8 / 128;                          // pieces per thread, tile and tensor
+    extern __shared__ __align__(16) unsigned char sm_raw[];     // ring: [NS][K 32 x RSH | V 32 x RSH] halves
+    __half* smh = reinterpret_cast<__half*>(sm_raw);
+    const uint32_t BT = 64u / REP, nrows = BT * REP, g = blockIdx.y, t0 = blockIdx.x * BT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int fg = lane >> 2, ft = lane & 3;
+    const uint32_t t_end = min(T, t0 + BT);
+    const uint32_t kmax = pos0 + t_end;                         // keys [0, kmax) are visible to the block's last token
+    const uint32_t ntiles = (kmax + 31) / 32;
+    const __half* kbase = kh + (size_t)g * ctx * DH;
+    const __half* vbase = vh + (size_t)g * ctx * DH;
+
+    auto tile_k = [&](int b) { return smh + (size_t)b * 2 * 32 * RSH; };
+    auto tile_v = [&](int b) { return smh + (size_t)b * 2 * 32 * RSH + 32 * RSH; };
+    auto copy_tile = [&](int b, uint32_t k0) {
+        __half* Kd = tile_k(b);
+        __half* Vd = tile_v(b);
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int i = tid + u * 128;
+            const uint32_t j = i / C8, c = i % C8, kk = k0 + j;
+            if (kk < kmax) {
+                cp_async16(Kd + j * RSH + 8 * c, kbase + (size_t)kk * DH + 8 * c);
+                cp_async16(Vd + j * RSH + 8 * c, vbase + (size_t)kk * DH + 8 * c);
+            } else {
+                *reinterpret_cast<uint4*>(Kd + j * RSH + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(Vd + j * RSH + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < NS - 1; ++s) {                          // one group per ring slot, empty or not: the counts below rely on it
+        if ((uint32_t)s < ntiles) copy_tile(s, 32u * s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
+    // this lane's rows: r0 = 16 warp + fg and r1 = r0 + 8
+    const uint32_t r0 = 16u * warp + fg, r1 = r0 + 8;
+    const uint32_t tok0 = t0 + r0 / REP, tok1 = t0 + r1 / REP;
+    const bool live0 = r0 < nrows && tok0 < T, live1 = r1 < nrows && tok1 < T;
+    // q fragments of the warp's 16 rows, pre-scaled: a0 (g, 2t..) a1 (g + 8, 2t..) a2 (g, 2t + 8..) a3 (g + 8, 2t + 8..) per k-step
+    uint32_t qf[KS][4];
+    {
+        const float* q0 = qkv + (size_t)(live0 ? tok0 : 0) * ld + (size_t)(g * REP + r0 % REP) * DH + 2 * ft;
+        const float* q1 = qkv + (size_t)(live1 ? tok1 : 0) * ld + (size_t)(g * REP + r1 % REP) * DH + 2 * ft;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const float2 a = *reinterpret_cast<const float2*>(q0 + 16 * ks), b = *reinterpret_cast<const float2*>(q1 + 16 * ks);
+            const float2 c = *reinterpret_cast<const float2*>(q0 + 16 * ks + 8), d = *reinterpret_cast<const float2*>(q1 + 16 * ks + 8);
+            qf[ks][0] = live0 ? pack_h2(a.x * scale, a.y * scale) : 0u;
+            qf[ks][1] = live1 ? pack_h2(b.x * scale, b.y * scale) : 0u;
+            qf[ks][2] = live0 ? pack_h2(c.x * scale, c.y * scale) : 0u;
+            qf[ks][3] = live1 ? pack_h2(d.x * scale, d.y * scale) : 0u;
+        }
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;    // running maxima (whole row) and this lane's share of the sums
+    const uint32_t lim0 = pos0 + tok0, lim1 = pos0 + tok1;      // last visible key of each row
+    // ldmatrix row of this lane inside a 16 x 16 block: K blocks (keys 0-7 | dims 0-7, 8-15), (keys 8-15 | ...);
+    // V blocks (keys 0-7, 8-15 | dims 0-7), (... | dims 8-15)
+    const uint32_t k_lane = ((lane >> 4) * 8 + (lane & 7)) * RSH + ((lane >> 3) & 1) * 8;
+    const uint32_t v_lane = (((lane >> 3) & 1) * 8 + (lane & 7)) * RSH + (lane >> 4) * 8;
+
+    for (uint32_t it = 0; it < ntiles; ++it) {
+        const uint32_t k0 = 32u * it;
+        const int buf = (int)(it % NS);
+        asm volatile("cp.async.wait_group %0;" ::"n"(NS - 2) : "memory");
+        __syncthreads();                                        // tile `it` is in place; every warp is done with tile it - 1
+        if (it + NS - 1 < ntiles) copy_tile((int)((it + NS - 1) % NS), k0 + 32u * (NS - 1));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __half* Kt = tile_k(buf);
+        const __half* Vt = tile_v(buf);
+        // scores of the warp's 16 rows x 32 keys: four n-tiles of 8 keys
+        float sc[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {
+                uint32_t b[4];
+                ldsm_x4(b, Kt + 16 * jp * RSH + 16 * ks + k_lane);
+                mma_f16(sc[2 * jp], qf[ks], b[0], b[1]);
+                mma_f16(sc[2 * jp + 1], qf[ks], b[2], b[3]);
+            }
+        // causal mask, row maxima over the quad
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t kk = k0 + 8 * j + 2 * ft + e;
+                if (!(live0 && kk <= lim0)) sc[j][e] = -INFINITY;
+                if (!(live1 && kk <= lim1)) sc[j][2 + e] = -INFINITY;
+                mx0 = fmaxf(mx0, sc[j][e]); mx1 = fmaxf(mx1, sc[j][2 + e]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float al0 = (m0 > -INFINITY) ? expf(m0 - n0) : 1.f, al1 = (m1 > -INFINITY) ? expf(m1 - n1) : 1.f;   // nothing accumulated yet: nothing to rescale
+        m0 = n0; m1 = n1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sc[j][0] = (n0 > -INFINITY) ? expf(sc[j][0] - n0) : 0.f; sc[j][1] = (n0 > -INFINITY) ? expf(sc[j][1] - n0) : 0.f;
+            sc[j][2] = (n1 > -INFINITY) ? expf(sc[j][2] - n1) : 0.f; sc[j][3] = (n1 > -INFINITY) ? expf(sc[j][3] - n1) : 0.f;
+            s0 += sc[j][0] + sc[j][1]; s1 += sc[j][2] + sc[j][3];
+        }
+        l0 = l0 * al0 + s0; l1 = l1 * al1 + s1;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { acc[n][0] *= al0; acc[n][1] *= al0; acc[n][2] *= al1; acc[n][3] *= al1; }
+        // output += P V: the accumulator layout of two 8-key score tiles is the A layout of one 16-key step
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t pf[4];
+            pf[0] = pack_h2(sc[2 * i][0], sc[2 * i][1]); pf[1] = pack_h2(sc[2 * i][2], sc[2 * i][3]);
+            pf[2] = pack_h2(sc[2 * i + 1][0], sc[2 * i + 1][1]); pf[3] = pack_h2(sc[2 * i + 1][2], sc[2 * i + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b[4];
+                ldsm_x4_t(b, Vt + 16 * i * RSH + 16 * np + v_lane);
+                mma_f16(acc[2 * np], pf, b[0], b[1]);
+                mma_f16(acc[2 * np + 1], pf, b[2], b[3]);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // the lanes of a quad hold disjoint shares of a row's sum
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const bool live = half ? live1 : live0;
+        if (!live) continue;
+        const uint32_t row = half ? r1 : r0, t = half ? tok1 : tok0;
+        const float inv = 1.0f / (half ? l1 : l0);
+        OT* o = out + (size_t)t * QD + (size_t)(g * REP + row % REP) * DH + 2 * ft;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            if constexpr (sizeof(OT) == 2) *reinterpret_cast<__half2*>(o + 8 * n) = __floats2half2_rn(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+            else *reinterpret_cast<float2*>(o + 8 * n) = make_float2(acc[n][2 * half] * inv, acc[n][2 * half + 1] * inv);
+        }
+    }
+}
+
 // rows [pos0, pos0 + T) of an fp32 cache [KVH][ctx][dh] into a lane K/V slot of the same shape (half or fp32)
 template <typename TO>
 __global__ void kv_rows_to_slot_kernel(const float* __restrict__ src, TO* __restrict__ dst, uint32_t KVH, uint32_t ctx, uint32_t dh,
@@ -338,10 +531,21 @@ __global__ void kv_rows_to_slot_kernel(const float* __restrict__ src, TO* __rest
     if constexpr (sizeof(TO) == 2) dst[off] = __float2half_rn(src[off]); else dst[off] = src[off];
 }
 
+// rows [pos0, pos0 + T) of the fp16 K and V copies into fp16 lane slots of the same shape, both tensors in one launch
+// (blockIdx.y picks one), 16 bytes per thread; dh % 8 == 0
+__global__ void kv_half_rows_to_slots_kernel(const uint4* __restrict__ ks, const uint4* __restrict__ vs, uint4* __restrict__ kd, uint4* __restrict__ vd,
+                                             uint32_t KVH, uint32_t ctx, uint32_t dh8, uint32_t pos0, uint32_t T) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per = (size_t)T * dh8;
+    if (i >= (size_t)KVH * per) return;
+    const size_t off = ((i / per) * ctx + pos0) * dh8 + i % per;
+    if (blockIdx.y == 0) kd[off] = ks[off]; else vd[off] = vs[off];
+}
+
 struct Layer {
     const uint8_t *q, *k, *v, *o, *gate, *up, *down;            // device block streams
     float *rms1 = nullptr, *rms2 = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr;
     float *kc = nullptr, *vc = nullptr;                         // device caches
+    __half *kh = nullptr, *vh = nullptr;                        // fp16 copies of their rows, the attention's operands (both or neither)
     // fp16 copies of the static weights (Stack::resident): q|k|v rows stacked [QD + 2 KVD][D], o [D][QD],
     // gate|up stacked [2 F][D], down [D][F]
     void *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr;
@@ -369,7 +573,7 @@ struct Stack {
         if (copy) { cudaStreamSynchronize(copy); cudaStreamDestroy(copy); }
         for (Layer& l : layers) {
             for (float* p : {l.rms1, l.rms2, l.qb, l.kb, l.vb, l.kc, l.vc}) if (p) cudaFree(p);
-            for (void* p : {l.wqkv, l.wo, l.wgu, l.wdown}) if (p) cudaFree(p);
+            for (void* p : {l.wqkv, l.wo, l.wgu, l.wdown, (void*)l.kh, (void*)l.vh}) if (p) cudaFree(p);
             if (l.pinned_k) cudaHostUnregister(l.kc_host);
             if (l.pinned_v) cudaHostUnregister(l.vc_host);
             if (l.kv_ready) cudaEventDestroy(l.kv_ready);
@@ -440,6 +644,18 @@ bool attn_ready() {
     return true;
 }
 
+template <int DH> constexpr size_t attn_h_smem() { return (size_t)(3 * 2 * 32 * (DH + 8)) * 2; }   // three tiles of K and V, fp16
+template <int DH, typename OT>
+bool attn_h_ready() {
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(prefill_attn_h_kernel<DH, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_h_smem<DH>()) != cudaSuccess)
+            return fail("llama stack: cannot raise the attention kernel's shared memory limit");
+        attr = true;
+    }
+    return true;
+}
+
 // act[t][f] = silu(gu[t][f]) * gu[t][F + f], straight to fp16 (the down projection's operand): gate and up come out of
 // ONE GEMM against the stacked gate|up rows. Four columns per thread; F % 4 == 0.
 __global__ void silu_mul_stacked_half_kernel(const float* __restrict__ gu, __half* __restrict__ act, uint32_t F) {
@@ -483,7 +699,7 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     const float* tbl = lane_rope_table(dh, (unsigned)(pos0 + T), c.theta, &tbl_n);
     if (!tbl) return false;
     const size_t per_tok = (size_t)(c.H + c.KVH) * (dh / 2) + (size_t)c.KVH * dh;
-    rope_append_kernel<<<(unsigned)(((size_t)T * per_tok + 255) / 256), 256, 0, st>>>(c.qkv, ld, L.kc, L.vc, (unsigned)c.H, (unsigned)c.KVH, dh,
+    rope_append_kernel<<<(unsigned)(((size_t)T * per_tok + 255) / 256), 256, 0, st>>>(c.qkv, ld, L.kc, L.vc, L.kh, L.vh, (unsigned)c.H, (unsigned)c.KVH, dh,
                                                                                      (unsigned)c.ctx, (unsigned)pos0, Tn, (const float2*)tbl, tbl_n);
     note_launch();
     cudaEventRecord(L.kv_ready, st);
@@ -500,6 +716,11 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
     auto attend = [&](auto dhc, auto* dst) -> bool {
         constexpr int DHC = decltype(dhc)::value;
         using OT = std::remove_pointer_t<decltype(dst)>;
+        if (L.kh) {
+            if (!attn_h_ready<DHC, OT>()) return false;
+            prefill_attn_h_kernel<DHC, OT><<<grid, 128, attn_h_smem<DHC>(), st>>>(c.qkv, ld, L.kh, L.vh, dst, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
+            return true;
+        }
         if (!attn_ready<DHC, OT>()) return false;
         prefill_attn_kernel<DHC, OT><<<grid, 128, attn_smem<DHC>(), st>>>(c.qkv, ld, L.kc, L.vc, dst, QD, Tn, (unsigned)pos0, (unsigned)c.ctx, (unsigned)c.REP, scale);
         return true;
@@ -568,6 +789,12 @@ bool enqueue(Stack& c, const Source& src, int T, int pos0) {
             if (!L.kc_host) continue;                               // device-only caches: the earlier rows are where the stack left them
             cudaMemcpy2DAsync(L.kc, pitch, L.kc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
             cudaMemcpy2DAsync(L.vc, pitch, L.vc_host, pitch, width, (size_t)c.KVH, cudaMemcpyHostToDevice, s.stream);
+            if (L.kh) {
+                const unsigned blocks = (unsigned)(((size_t)c.KVH * pos0 * c.dh + 255) / 256);
+                kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.kc, L.kh, (unsigned)c.KVH, (unsigned)c.ctx, (unsigned)c.dh, 0u, (unsigned)pos0);
+                kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.vc, L.vh, (unsigned)c.KVH, (unsigned)c.ctx, (unsigned)c.dh, 0u, (unsigned)pos0);
+                note_launch(2);
+            }
         }
         if (!check_launch("llama stack: cache upload")) return false;
     }
@@ -606,6 +833,8 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
         cudaEventCreate(&c->t1) != cudaSuccess) { check_launch("llama stack: stream"); return nullptr; }
     c->layers.resize((size_t)c->L);
     const size_t cache_floats = (size_t)c->KVD * c->ctx;
+    const char* attn_env = std::getenv("TM_CUDA_STACK_ATTN");
+    bool attn_fp16 = !(attn_env && std::strcmp(attn_env, "tf32") == 0);
     for (int l = 0; l < c->L; ++l) {
         const tm_llama_gpu_layer& src = d->layers[l];
         Layer& L = c->layers[(size_t)l];
@@ -632,6 +861,17 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
             cudaGetLastError(); fail("llama stack: out of device memory for the K/V caches"); return nullptr;
         }
         cudaMemsetAsync(L.kc, 0, cache_floats * 4, s.stream); cudaMemsetAsync(L.vc, 0, cache_floats * 4, s.stream);
+        // fp16 copies of the rows for the attention's MMAs (half the caches again); TM_CUDA_STACK_ATTN=tf32 does without
+        // them and runs the attention on the fp32 rows as tf32, as does a device that has no room for them
+        if (attn_fp16) {
+            if (cudaMalloc(&L.kh, cache_floats * 2) != cudaSuccess || cudaMalloc(&L.vh, cache_floats * 2) != cudaSuccess) {
+                cudaGetLastError();
+                for (Layer& M : c->layers) { if (M.kh) cudaFree(M.kh); if (M.vh) cudaFree(M.vh); M.kh = M.vh = nullptr; }
+                attn_fp16 = false;
+            } else {
+                cudaMemsetAsync(L.kh, 0, cache_floats * 2, s.stream); cudaMemsetAsync(L.vh, 0, cache_floats * 2, s.stream);
+            }
+        }
         L.kc_host = src.kc; L.vc_host = src.vc;
         if (L.kc_host) {
             // page-locking the caller's arrays makes the row copies asynchronous; where it is refused they are staged
@@ -778,6 +1018,14 @@ int tm_cuda_llama_kv_to_slots(void* h, int l, int kcslot, int vcslot, int pos0, 
     if (!kd || !vd) return 0;
     const Layer& L = c->layers[(size_t)l];
     const unsigned blocks = (unsigned)(((size_t)c->KVH * T * c->dh + 255) / 256);
+    if (s.kv_half && L.kh && c->dh % 8 == 0) {
+        // the attention's fp16 rows are the slot's rows already (the same rounding of the same fp32 values)
+        const unsigned b8 = (unsigned)(((size_t)c->KVH * T * (c->dh / 8) + 255) / 256);
+        kv_half_rows_to_slots_kernel<<<dim3(b8, 2), 256, 0, s.stream>>>((const uint4*)L.kh, (const uint4*)L.vh, (uint4*)kd, (uint4*)vd, (unsigned)c->KVH,
+                                                                        (unsigned)c->ctx, (unsigned)c->dh / 8, (unsigned)pos0, (unsigned)T);
+        note_launch();
+        return check_launch("llama_kv_to_slots") ? 1 : 0;
+    }
     if (s.kv_half) {
         kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.kc, (__half*)kd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);
         kv_rows_to_slot_kernel<__half><<<blocks, 256, 0, s.stream>>>(L.vc, (__half*)vd, (unsigned)c->KVH, (unsigned)c->ctx, (unsigned)c->dh, (unsigned)pos0, (unsigned)T);

@@ -88,6 +88,33 @@ def test_resident_fp16_weights_equal_per_call_conversion(cuda, orc, cfg, monkeyp
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
+@pytest.mark.parametrize("cfg", [TINY, GQA128], ids=["dh64-rep2", "dh128-rep4"])
+def test_attention_on_fp16_rows_and_on_tf32_rows(cuda, orc, cfg, monkeypatch):
+    """The attention reads fp16 copies of the cache rows (m16n8k16 MMAs); TM_CUDA_STACK_ATTN=tf32 runs it on the fp32 rows
+    rounded to tf32 instead. Both meet the CPU block loop, whole and chunked (the second chunk's earlier rows come back
+    from the caller's arrays and are converted again), and they differ from each other by less than either bar."""
+    T = 300
+    w = synth.make_llama(cfg, seed=29)
+    toks = synth.make_tokens(T, cfg["V"], seed=30)
+    x = _embed(orc, cfg, w, toks)
+    want, _ = _cpu_rows(orc, cfg, w, toks, 0)
+    got = {}
+    for mode in ("fp16", "tf32"):
+        monkeypatch.setenv("TM_CUDA_STACK_ATTN", mode)
+        st = stack.Stack(cfg, w)
+        whole = st.prefill(x, 0)
+        st.close()
+        st = stack.Stack(cfg, w)
+        a = st.prefill(x[:200], 0)
+        b = st.prefill(x[200:], 200)
+        st.close()
+        _close(whole, want, f"{mode}: residual stream", STREAM_BAR)
+        assert np.array_equal(a.view(np.uint32), whole[:200].view(np.uint32)), mode
+        _close(b, whole[200:], f"{mode}: second chunk", ROW_BAR)
+        got[mode] = whole
+    _close(got["fp16"], got["tf32"], "fp16 rows against tf32 rows", ROW_BAR)
+
+
 def test_device_only_caches_and_prompt_after_decode_steps(cuda, orc):
     """kc = vc = NULL keeps the K/V rows on the device: same residual stream, chunks continue from the device rows. And a
     prompt that follows tokens of the decode lane (whose rows the stack does not have) must still give the decode lane's

@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
     if (csize > 1) cluster_arrive();                        // this CTA is done with its peers' shared memory
     const uint32_t wchunk = min((uint32_t)L::STEP_W, p.K - myc * L::STEP_W);
     const int valid = lane_valid<DT>(lane, (int)(wchunk / L::UNIT_W));
+    const bool full_chunk = wchunk == (uint32_t)L::STEP_W;  // every lane then has all of its units
     bool landed = false;                                    // the probe of this item's stage, made while the previous item was summed
     for (uint32_t t = 0; t < items; ++t) {
         float acc[R];
@@ -462,7 +463,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) gemv_stream(const Ge
         if (!landed && !mbar_wait(&mybar[slot], phase)) { dead = true; break; }
         const uint8_t* st = mystage + (size_t)slot * R * ROWCAP;
         const uint32_t rows = min((uint32_t)R, cta_hi - row0);
-        if (L::LANE_UNITS == 2 ? valid > 0 : true) {
+        if (full_chunk && rows == (uint32_t)R) {
+            // the common item - R rows of a whole step - without the per-row and per-block tests (both warp-uniform
+            // here, but a branch each in the general form below); same arithmetic, same bits
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                acc[r] = L::dot(st + r * ROWCAP + (L::LANE_UNITS == 2 ? lane * L::LANE_BYTES : 0), xr, lane, L::LANE_UNITS == 2 ? 2 : L::STEP_W / L::UNIT_W);
+        } else if (L::LANE_UNITS == 2 ? valid > 0 : true) {
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 if ((uint32_t)r < rows) {                   // warp-uniform: rows past the range were never copied

@@ -192,7 +192,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 __global__ void __launch_bounds__(kThreadsTma, 1)
 gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             float* __restrict__ C, uint32_t ldc, uint32_t m_tok, uint32_t n_rows, uint32_t K, uint32_t bn, uint32_t accumulate,
-            int* status) {
+            int* status, __half* __restrict__ act) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + kTileRegion);
@@ -283,6 +283,31 @@ gemm_f16_tn(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (m0 + c0 >= m_tok) break;            // warp-uniform: whole column block past the last token
                 uint32_t v[32];
                 tmem_ld32(taddr + c0, v);               // a 16-column remainder reads 16 stale columns of the buffer: masked below
+                if (act) {
+                    // Gated FFN: weight row 2f is gate row f and row 2f + 1 is up row f, so the two lanes of a pair hold
+                    // gate and up of the same f for the same 32 tokens. They trade halves - the even lane keeps tokens
+                    // 0-15 and gets their up values, the odd lane keeps 16-31 and gets their gate values - and each
+                    // writes silu(gate) * up for its 16 tokens as fp16 into act[token][f] (ldc = F): the gate|up values
+                    // never reach memory. Same expression and rounding as the separate kernel this replaces.
+                    const bool odd = lane & 1;
+                    float res[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float mine_lo = __uint_as_float(v[j]), mine_hi = __uint_as_float(v[16 + j]);
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? mine_lo : mine_hi, 1);
+                        const float g = odd ? got : mine_lo, u = odd ? mine_hi : got;
+                        res[j] = g / (1.0f + expf(-g)) * u;
+                    }
+                    if (row < n_rows) {
+                        const uint32_t f = row >> 1, cb = c0 + (odd ? 16u : 0u);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const uint32_t m = m0 + cb + j;
+                            if (cb + j < bn && m < m_tok) act[(size_t)m * ldc + f] = __float2half_rn(res[j]);
+                        }
+                    }
+                    continue;
+                }
                 if (row < n_rows) {
                     if (accumulate) {                   // C += A W^T (a residual add folded in): all 32 old values are requested before the first is used
                         float old[32];
@@ -980,8 +1005,10 @@ unsigned pick_token_tile_pair(unsigned M, unsigned N, unsigned sms) {
 
 // The TMA-fed kernels over fp16 operands that are in place (or being written by the launch just before this one):
 // weights Wh [N][K], activations Ah [M][K].
+// act (instead of C): the weights are gate and up rows interleaved and the output is act[M][ldc] = silu(gate) * up in
+// fp16 (the one-SM kernel's fused epilogue; such calls do not take the CTA-pair kernel).
 static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned ldc, unsigned M, unsigned N, unsigned K, cudaStream_t st,
-                         bool accumulate = false) {
+                         bool accumulate = false, __half* act = nullptr) {
     CUtensorMap tmA, tmB;
     // Two SMs per tile (gemm_f16_tn_pair) where it measured faster: four or more waves of pair tiles. TM_GEMM_PAIR=0
     // keeps one SM per tile everywhere, TM_GEMM_PAIR=1 pairs wherever there are 256 weight rows.
@@ -989,7 +1016,7 @@ static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned 
     const unsigned sms = (unsigned)device_sm_count();
     const unsigned bn2 = pick_token_tile_pair(M, N, sms);
     const unsigned long long pair_tiles = (unsigned long long)((N + 2 * BM - 1) / (2 * BM)) * ((M + bn2 - 1) / bn2);
-    const bool paired = N >= 2 * BM && sms >= 2 && (pair_mode == 1 || (pair_mode < 0 && pair_tiles >= 4ull * (sms / 2)));
+    const bool paired = !act && N >= 2 * BM && sms >= 2 && (pair_mode == 1 || (pair_mode < 0 && pair_tiles >= 4ull * (sms / 2)));
     if (paired) {
         if (!make_map(&tmB, Ah, M, K, bn2 / 2) || !make_map(&tmA, Wh, N, K, BM)) return false;
         static bool attr2 = false;
@@ -1032,7 +1059,7 @@ static bool launch_tiles(const __half* Wh, const __half* Ah, float* C, unsigned 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, gemm_f16_tn, tmA, tmB, C, (uint32_t)ldc, (uint32_t)M, (uint32_t)N, (uint32_t)K, (uint32_t)bn,
-                           accumulate ? 1u : 0u, device_status_word()) != cudaSuccess)
+                           accumulate ? 1u : 0u, device_status_word(), act) != cudaSuccess)
         return check_launch("gemm_f16_tn");
     note_launch();
     return check_launch("gemm_f16_tn");
@@ -1070,6 +1097,15 @@ bool launch_gemm_hh(const void* Ah, const void* Wh, float* C, unsigned ldc, unsi
     if (K == 0 || K % 8) return fail("gemm: K must be a multiple of 8");
     if ((uintptr_t)Ah % 16 || (uintptr_t)C % 4 || (uintptr_t)Wh % 16) return fail("gemm: the fp16 operands must be 16-byte aligned");
     return launch_tiles((const __half*)Wh, (const __half*)Ah, C, ldc, M, N, K, st, accumulate);
+}
+
+// act[M][F] = silu(A Wg^T) * (A Wu^T) in fp16, where Wgu [2 F][K] holds gate row f at row 2f and up row f at row 2f + 1.
+bool launch_gemm_hh_silu_mul(const void* Ah, const void* Wgu, void* act, unsigned M, unsigned F, unsigned K, cudaStream_t st) {
+    if (!Ah || !Wgu || !act) return fail("gemm: null pointer");
+    if (M == 0 || F == 0) return true;
+    if (K == 0 || K % 8) return fail("gemm: K must be a multiple of 8");
+    if ((uintptr_t)Ah % 16 || (uintptr_t)act % 2 || (uintptr_t)Wgu % 16) return fail("gemm: the fp16 operands must be 16-byte aligned");
+    return launch_tiles((const __half*)Wgu, (const __half*)Ah, nullptr, F, M, 2 * F, K, st, false, (__half*)act);
 }
 
 size_t gemm_f16w_workspace_bytes(unsigned M, unsigned K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }

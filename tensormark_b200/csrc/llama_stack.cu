@@ -547,7 +547,7 @@ struct Layer {
     float *kc = nullptr, *vc = nullptr;                         // device caches
     __half *kh = nullptr, *vh = nullptr;                        // fp16 copies of their rows, the attention's operands (both or neither)
     // fp16 copies of the static weights (Stack::resident): q|k|v rows stacked [QD + 2 KVD][D], o [D][QD],
-    // gate|up stacked [2 F][D], down [D][F]
+    // gate and up rows interleaved [2 F][D] (row 2f = gate f, row 2f + 1 = up f), down [D][F]
     void *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr;
     float *kc_host = nullptr, *vc_host = nullptr;               // the caller's arrays
     bool pinned_k = false, pinned_v = false;
@@ -559,7 +559,6 @@ struct Stack {
     unsigned dtype = DT_Q4_0;
     std::vector<Layer> layers;
     float *x = nullptr, *h = nullptr, *qkv = nullptr, *ao = nullptr, *h2 = nullptr, *g = nullptr, *u = nullptr;
-    float* gu = nullptr;                                        // resident form: gate|up of the batch, [T][2 F]
     __half *hh = nullptr, *aoh = nullptr, *acth = nullptr;      // resident form: fp16 activations [T][D], [T][QD], [T][F]
     bool resident = false;                                      // the layers hold fp16 copies of their weights
     void* ws = nullptr;
@@ -585,7 +584,7 @@ struct Stack {
         cudaGetLastError();
     }
     void free_scratch() {
-        for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u, &gu}) if (*p) { cudaFree(*p); *p = nullptr; }
+        for (float** p : {&x, &h, &qkv, &ao, &h2, &g, &u}) if (*p) { cudaFree(*p); *p = nullptr; }
         for (__half** p : {&hh, &aoh, &acth}) if (*p) { cudaFree(*p); *p = nullptr; }
         if (ws) { cudaFree(ws); ws = nullptr; }
         cap_T = 0;
@@ -615,8 +614,8 @@ bool ensure_scratch(Stack& c, int T) {
     bool ok;
     if (c.resident) {
         if ((c.F % 4) || (c.D % 8) || (c.QD % 8)) return fail("llama stack: row widths must be multiples of 8 (F of 4) for the fp16 activations");
-        c.gu = mk(t * 2 * c.F); c.hh = mkh(t * c.D); c.aoh = mkh(t * c.QD); c.acth = mkh(t * c.F);
-        ok = c.x && c.qkv && c.gu && c.hh && c.aoh && c.acth;
+        c.hh = mkh(t * c.D); c.aoh = mkh(t * c.QD); c.acth = mkh(t * c.F);
+        ok = c.x && c.qkv && c.hh && c.aoh && c.acth;
     } else {
         c.h = mk(t * c.D); c.h2 = mk(t * c.D); c.ao = mk(t * c.QD); c.g = mk(t * c.F); c.u = mk(t * c.F);
         size_t need = 0;
@@ -654,18 +653,6 @@ bool attn_h_ready() {
         attr = true;
     }
     return true;
-}
-
-// act[t][f] = silu(gu[t][f]) * gu[t][F + f], straight to fp16 (the down projection's operand): gate and up come out of
-// ONE GEMM against the stacked gate|up rows. Four columns per thread; F % 4 == 0.
-__global__ void silu_mul_stacked_half_kernel(const float* __restrict__ gu, __half* __restrict__ act, uint32_t F) {
-    const uint32_t t = blockIdx.y, f4 = blockIdx.x * blockDim.x + threadIdx.x;
-    if (f4 * 4 >= F) return;
-    const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + 4 * f4);
-    const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * 2 * F + F + 4 * f4);
-    const __half2 a = __floats2half2_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
-    const __half2 b = __floats2half2_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
-    *reinterpret_cast<uint2*>(act + (size_t)t * F + 4 * f4) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
 bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
@@ -734,9 +721,8 @@ bool encode_layer(Stack& c, int l, int T, int pos0, cudaStream_t st) {
         // one the GEMM's pre-pass would apply), and the residual adds are the GEMMs' own epilogues
         if (!gemm_h(c.aoh, L.wo, c.x, D, D, QD, true)) return false;
         rmsnorm_rows_kernel<__half><<<Tn, 256, 0, st>>>(c.x, L.rms2, c.hh, D, c.eps); note_launch();
-        if (!gemm_h(c.hh, L.wgu, c.gu, 2 * F, 2 * F, D, false)) return false;
-        silu_mul_stacked_half_kernel<<<dim3((F / 4 + 255) / 256, Tn), 256, 0, st>>>(c.gu, c.acth, F);
-        note_launch();
+        // gate and up rows are interleaved in wgu: one GEMM whose epilogue writes silu(gate) * up as the fp16 operand
+        if (!launch_gemm_hh_silu_mul(c.hh, L.wgu, c.acth, Tn, F, D, st)) return false;
         if (!gemm_h(c.acth, L.wdown, c.x, D, D, F, true)) return false;
     } else {
         if (!gemm(c.ao, L.o, c.h2, D, D, QD)) return false;
@@ -893,7 +879,12 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
         if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) { cudaGetLastError(); free_b = 0; }
         if (mode == 1 || (mode < 0 && per_layer * (size_t)c->L <= free_b / 3)) {
             bool ok = true;
+            // gate and up are converted into a staging buffer and copied into alternating rows of wgu
+            const size_t row_b = (size_t)c->D * 2;
+            void* stage = nullptr;
+            ok = cudaMalloc(&stage, (size_t)c->F * row_b) == cudaSuccess;
             for (Layer& L : c->layers) {
+                if (!ok) break;
                 const size_t qd = (size_t)c->QD * c->D * 2, kvd = (size_t)c->KVD * c->D * 2, fd = (size_t)c->F * c->D * 2;
                 ok = ok && cudaMalloc(&L.wqkv, qd + 2 * kvd) == cudaSuccess && cudaMalloc(&L.wo, qd) == cudaSuccess &&
                      cudaMalloc(&L.wgu, 2 * fd) == cudaSuccess && cudaMalloc(&L.wdown, fd) == cudaSuccess;
@@ -903,11 +894,14 @@ void* create(const tm_llama_gpu_desc* d, unsigned dtype) {
                      launch_weights_f16(L.k, qkv + qd, (unsigned)c->KVD, (unsigned)c->D, dtype, s.stream) &&
                      launch_weights_f16(L.v, qkv + qd + kvd, (unsigned)c->KVD, (unsigned)c->D, dtype, s.stream) &&
                      launch_weights_f16(L.o, L.wo, (unsigned)c->D, (unsigned)c->QD, dtype, s.stream) &&
-                     launch_weights_f16(L.gate, gu, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
-                     launch_weights_f16(L.up, gu + fd, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
+                     launch_weights_f16(L.gate, stage, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
+                     cudaMemcpy2DAsync(gu, 2 * row_b, stage, row_b, row_b, (size_t)c->F, cudaMemcpyDeviceToDevice, s.stream) == cudaSuccess &&
+                     launch_weights_f16(L.up, stage, (unsigned)c->F, (unsigned)c->D, dtype, s.stream) &&
+                     cudaMemcpy2DAsync(gu + row_b, 2 * row_b, stage, row_b, row_b, (size_t)c->F, cudaMemcpyDeviceToDevice, s.stream) == cudaSuccess &&
                      launch_weights_f16(L.down, L.wdown, (unsigned)c->D, (unsigned)c->F, dtype, s.stream);
                 if (!ok) break;
             }
+            if (stage) { cudaStreamSynchronize(s.stream); cudaFree(stage); }
             if (ok) {
                 c->resident = true;
             } else {
